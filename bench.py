@@ -1,0 +1,402 @@
+#!/usr/bin/env python
+"""Benchmark of the DSQG attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1|cfg2|cfg2_4k|cfg3]
+    python bench.py --impl reference ...      # the reference's PyTorch path on the host cores
+
+A "step" is one forward+backward pass of the DSQG op over one batch of synthetic input
+(cfg3: one decode token across 10 layers).  Prints ONE JSON line on rank 0.
+
+  value      whole-job tokens/s, inputs resident in HBM, CUDA-event timed, MAX over ranks
+  e2e        same metric through the public Python API with pinned HOST buffers: the H2D copy
+             of q,k,v,dout and the D2H copy of out,dq,dk,dv are inside the timed region
+  roofline   the longest kernel of the step: algorithmic bytes per launch / its CUDA-event
+             duration, against the measured HBM copy bandwidth in MEASURED_PEAKS.json
+  cpu_baseline  the PyTorch restatement of the reference (oracle/) timed on the host cores on
+             a bounded sample of the same workload (rank 0, N=1 only)
+
+Multi-GPU: one process per GPU (torchrun); the batch is replicated per rank (weak scaling),
+there is no data-path collective; torch.distributed only carries the barrier and the MAX of
+the timings.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return FALLBACK_HBM_GBS, "fallback (no MEASURED_PEAKS.json)"
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the GPU works."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(5)
+        except Exception:
+            self.proc.kill()
+        self.file.flush(); self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        self.file.close()
+        try:
+            os.unlink(self.file.name)
+        except OSError:
+            pass
+        # "under load": the upper half of the samples (idle samples before/after sit at low clocks)
+        load = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(load) if load else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- op workloads
+def op_bytes(cfg):
+    esz = 2 if cfg.dtype == torch.bfloat16 else 4
+    return cfg.B * cfg.H * cfg.N * cfg.D * esz          # T: one [B,H,N,D] tensor
+
+
+def run_op_workload(args, cfg, rank, local_rank, world):
+    import dwarf_b200
+    from dwarf_b200 import _lib, dist as ddist, synth
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    lib = _lib.load()
+    x = synth.make_op_inputs(cfg)                       # CPU, seeded; every rank runs a full batch
+    host = {nm: x[nm].pin_memory() for nm in ("q", "k", "v", "dout")}
+    q, k, v, dout = (host[nm].to(dev, non_blocking=True) for nm in ("q", "k", "v", "dout"))
+    pb = x["pos_bias"].to(dev); gain = x["head_gain"].to(dev)
+    B, H, N, D = cfg.B, cfg.H, cfg.N, cfg.D
+    off, J = _lib.offsets_array(cfg.offsets)
+    out = torch.empty_like(q); lse = torch.empty(B, H, N, device=dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    dpb = torch.empty(J, H, device=dev); dg = torch.empty(H, device=dev)
+    nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, 0)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream()
+    sp = stream.cuda_stream
+    dt = 0 if cfg.dtype == torch.bfloat16 else 1
+
+    def fwd():
+        _lib.check(lib.dsqg_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), None, gain.data_ptr(),
+                                off, J, out.data_ptr(), lse.data_ptr(), B, H, N, D, dt, sp), "dsqg_fwd")
+
+    def bwd(stages):
+        _lib.check(lib.dsqg_bwd_stages(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), None,
+                                       gain.data_ptr(), off, J, out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
+                                       dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dpb.data_ptr(), None,
+                                       dg.data_ptr(), scratch.data_ptr(), nbytes, B, H, N, D, dt, sp, stages),
+                   "dsqg_bwd_stages")
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    # ---- device-resident timing: W warm-up steps, then exactly K timed steps -------------
+    for _ in range(args.warmup):
+        fwd(); bwd(1); bwd(2); bwd(4)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    ddist.barrier(); torch.cuda.synchronize()
+    t_wall = time.perf_counter()
+    for i in range(args.steps):
+        ev[i][0].record(stream); fwd()
+        ev[i][1].record(stream); bwd(1)
+        ev[i][2].record(stream); bwd(2)
+        ev[i][3].record(stream); bwd(4)
+        ev[i][4].record(stream)
+    torch.cuda.synchronize(); ddist.barrier()
+    wall_ms = (time.perf_counter() - t_wall) * 1e3
+    total_ms = ev[0][0].elapsed_time(ev[-1][4])
+    kern_ms = [sum(ev[i][s].elapsed_time(ev[i][s + 1]) for i in range(args.steps)) / args.steps for s in range(4)]
+    total_ms = ddist.max_over_ranks(total_ms, dev if world > 1 else "cpu")
+    ms_per_step = total_ms / args.steps
+    tokens_per_step = B * N * world
+    value = tokens_per_step / (ms_per_step * 1e-3)
+
+    # ---- end to end: pinned host buffers in, pinned host buffers out ----------------------
+    res_host = {nm: torch.empty(q.shape, dtype=q.dtype).pin_memory() for nm in ("out", "dq", "dk", "dv")}
+    pbp = pb.detach().clone().requires_grad_(True); gp = gain.detach().clone().requires_grad_(True)
+    e2e_steps = max(3, min(args.steps, 20))
+
+    def e2e_step():
+        qd, kd, vd = (host[nm].to(dev, non_blocking=True).requires_grad_(True) for nm in ("q", "k", "v"))
+        dod = host["dout"].to(dev, non_blocking=True)
+        o = dwarf_b200.dsqg_attention(qd, kd, vd, pbp, gp, None, cfg.offsets)
+        o.backward(dod)
+        res_host["out"].copy_(o.detach(), non_blocking=True)
+        res_host["dq"].copy_(qd.grad, non_blocking=True)
+        res_host["dk"].copy_(kd.grad, non_blocking=True)
+        res_host["dv"].copy_(vd.grad, non_blocking=True)
+        pbp.grad = None; gp.grad = None
+
+    for _ in range(2):
+        e2e_step()
+    ddist.barrier(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    torch.cuda.synchronize(); ddist.barrier()
+    e2e_ms = ddist.max_over_ranks(e0.elapsed_time(e1), dev if world > 1 else "cpu") / e2e_steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    T = op_bytes(cfg)
+    peak, peak_src = measured_peaks()
+    names = ["dsqg_fwd", "dsqg_bwd_dq", "dsqg_bwd_dkdv", "dsqg_bwd_reduce_params"]
+    alg = [4 * T, 6 * T, 6 * T, 0]        # per launch: fwd Q,K,V->O ; dq Q,K,V,O,dO->dQ ; dkdv Q,K,V,dO->dK,dV
+    top = max(range(3), key=lambda s: kern_ms[s])
+    achieved = alg[top] / (kern_ms[top] * 1e-3) / 1e9
+    step_achieved = 12 * T / (ms_per_step * 1e-3) / 1e9
+    line = {
+        "metric": "DSQG fwd+bwd tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if cfg.dtype == torch.bfloat16 else "f32", "data": "synthetic",
+        "config": {"workload": cfg.name, "tokens_per_step_per_gpu": B * N,
+                   "l2": "inputs+outputs per step (>= 400 MB) exceed the 126 MB L2; no flush",
+                   "parallelism": f"batch replicated x{world}, no collective"},
+        "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": 4 * T, "d2h_bytes_per_step": 4 * T, "ms_per_step": e2e_ms,
+                "steps": e2e_steps},
+        "gpu_launches": 4 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": names[top], "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": alg[top], "ms_per_launch": kern_ms[top]},
+        "step_roofline": {"algorithmic_bytes_per_step": 12 * T, "achieved": step_achieved,
+                          "frac": step_achieved / peak, "unit": "GB/s"},
+        "kernels": [{"name": names[s], "ms": kern_ms[s], "algorithmic_bytes": alg[s],
+                     "gbs": (alg[s] / (kern_ms[s] * 1e-3) / 1e9) if alg[s] else None} for s in range(4)],
+        "wall_ms_timed_region": wall_ms,
+        "clocks": clocks,
+    }
+    return line
+
+
+def run_decode_workload(args, rank, local_rank, world):
+    import dwarf_b200
+    from dwarf_b200 import dist as ddist, synth
+
+    cfg = synth.DecodeConfig()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    x = synth.make_decode_inputs(cfg, device="cpu")
+    host = {nm: x[nm].pin_memory() for nm in ("q", "k_new", "v_new")}
+    kr, vr = x["k_ring"].to(dev), x["v_ring"].to(dev)
+    q, kn, vn = (host[nm].to(dev) for nm in ("q", "k_new", "v_new"))
+    head = x["head"].to(dev); pb = x["pos_bias"].to(dev); gain = x["head_gain"].to(dev)
+    out = torch.empty_like(q)
+    L = cfg.layers
+    stream = torch.cuda.current_stream()
+
+    def step():
+        for l in range(L):
+            dwarf_b200.dsqg_decode_step(q[l], kn[l], vn[l], kr[l], vr[l], head, pb, gain, None, cfg.offsets,
+                                        None, out[l])
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ddist.barrier(); torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize(); ddist.barrier()
+    ms = ddist.max_over_ranks(e0.elapsed_time(e1), dev if world > 1 else "cpu") / args.steps
+
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    e2e_steps = max(3, min(args.steps, 50))
+
+    def e2e_step():
+        for nm, dst in (("q", q), ("k_new", kn), ("v_new", vn)):
+            dst.copy_(host[nm], non_blocking=True)
+        step()
+        out_host.copy_(out, non_blocking=True)
+    e2e_step()
+    torch.cuda.synchronize(); ddist.barrier()
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    torch.cuda.synchronize(); ddist.barrier()
+    e2e_ms = ddist.max_over_ranks(e0.elapsed_time(e1), dev if world > 1 else "cpu") / e2e_steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    J = len(cfg.offsets)
+    esz = 2
+    per_pair = 2 * J * cfg.D * esz + 2 * cfg.D * esz + 2 * cfg.D * esz   # taps K+V, ring write, q + out
+    layer_bytes = per_pair * cfg.S * cfg.H
+    peak, peak_src = measured_peaks()
+    achieved = layer_bytes * L / (ms * 1e-3) / 1e9
+    tokens = cfg.S * world
+    small = 3 * cfg.S * cfg.H * cfg.D * esz * L
+    return {
+        "metric": "DSQG decode tokens/s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": cfg.name, "l2": f"ring footprint {2 * L * cfg.S * cfg.H * cfg.R * cfg.D * esz / 1e9:.1f} GB >> L2",
+                   "parallelism": f"sequences replicated x{world}, no collective"},
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": small,
+                "d2h_bytes_per_step": small // 3, "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": L * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "dsqg_decode", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": layer_bytes, "ms_per_launch": ms / L},
+        "clocks": clocks,
+    }
+
+
+# ----------------------------------------------------------------------------- CPU legs
+def cpu_reference_time(cfg, sample_B, repeats, fwd_bwd=True):
+    """Times the PyTorch restatement of the reference's DSQG path (oracle/dsqg_oracle.py, a
+    line-for-line generalisation of kernels/dsqg_attention_v3.py:543-561) on the host cores.
+    This is the one place outside tests/ where oracle/ is executed: as the measured baseline."""
+    from dwarf_b200 import synth
+    from oracle import dsqg_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    x = synth.make_op_inputs(cfg, B=sample_B)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        if fwd_bwd:
+            O.dsqg_reference_grads(x["q"], x["k"], x["v"], x["pos_bias"], x["dout"], None, x["head_gain"],
+                                   cfg.offsets, chunk=1)
+        else:
+            O.dsqg_reference_chunked(x["q"], x["k"], x["v"], x["pos_bias"], None, x["head_gain"], cfg.offsets, 1)
+        best = min(best, time.perf_counter() - t0)
+    return sample_B * cfg.N / best, best
+
+
+def run_reference_arm(args, cfg):
+    """--impl reference: the reference's own (CPU, PyTorch) implementation of the path.  The
+    reference checkout does not travel with the repository, so its restatement in oracle/ is
+    timed (bit-identical to the reference functions on their 44-offset set)."""
+    sample_B = 2
+    from dwarf_b200 import synth
+    from oracle import dsqg_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    x = synth.make_op_inputs(cfg, B=sample_B)
+
+    def step():
+        O.dsqg_reference_grads(x["q"], x["k"], x["v"], x["pos_bias"], x["dout"], None, x["head_gain"],
+                               cfg.offsets, chunk=1)
+    for _ in range(min(args.warmup, 1)):
+        step()
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    el = (time.perf_counter() - t0) / steps
+    val = sample_B * cfg.N / el
+    sample = f"{sample_B} of {cfg.B} batch entries per step ({sample_B * cfg.N} tokens), fwd+bwd via autograd, fp32"
+    return {
+        "impl": "reference", "metric": "DSQG fwd+bwd tokens/s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": el * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cfg.name, "tokens_per_step_per_gpu": cfg.B * cfg.N},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="cfg1", choices=["cfg1", "cfg2", "cfg2_4k", "cfg3"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    from dwarf_b200 import dist as ddist, synth
+    rank, local_rank, world = ddist.env_world()
+
+    if args.impl == "reference":
+        if rank == 0:
+            cfg = synth.OP_CONFIGS["cfg1" if args.workload == "cfg3" else args.workload]
+            print(json.dumps(run_reference_arm(args, cfg)), flush=True)
+        return 0
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the DSQG kernels have no CPU fallback")
+    ddist.init_process_group("nccl")
+    if args.workload == "cfg3":
+        line = run_decode_workload(args, rank, local_rank, world)
+    else:
+        cfg = synth.OP_CONFIGS[args.workload]
+        line = run_op_workload(args, cfg, rank, local_rank, world)
+        if rank == 0 and world == 1 and not args.no_cpu_baseline:
+            sample_B = 8
+            val, secs = cpu_reference_time(cfg, sample_B, repeats=4)
+            line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                                    "kind": "port",
+                                    "sample": f"{sample_B} of {cfg.B} batch entries ({sample_B * cfg.N} tokens), "
+                                              f"fwd+bwd via autograd in fp32, best of 4 ({secs:.2f} s)"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if torch.distributed.is_initialized():
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,6 @@
+"""Import shim: `from dsqg_attention_v2 import ...` resolves to the B200 implementation
+when this directory replaces the reference's kernels/ directory on sys.path."""
+from dwarf_b200.modules import DSQGAttentionN_Fused, dsqg_attention_v2  # noqa: F401
+from dwarf_b200.ops import ALL_OFFSETS as _ALL
+
+ALL_OFFSETS = list(_ALL)

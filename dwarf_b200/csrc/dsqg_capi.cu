@@ -1,0 +1,189 @@
+// C ABI of libdsqg_b200.so: argument validation on the host, then dispatch to the
+// sm_100a kernels.  Declarations and the reference interfaces they replace are in
+// include/dsqg_b200.h.  Nothing here allocates, throws, or keeps state between calls.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+
+#include "dsqg_common.cuh"
+
+namespace dsqg {
+
+static thread_local char g_cuda_err[256] = "";
+
+static int cuda_fail(cudaError_t e) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+    return DSQG_ERR_CUDA;
+}
+
+static inline bool misaligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
+
+// Validates the offsets and splits them into the dense run and the sparse taps.
+static int build_taps(const int32_t* offsets, int J, Taps* t) {
+    if (!offsets) return DSQG_ERR_NULL_POINTER;
+    if (J < 1 || J > DSQG_MAX_TAPS) return DSQG_ERR_BAD_SHAPE;
+    if (offsets[0] < 0) return DSQG_ERR_BAD_OFFSETS;
+    for (int j = 1; j < J; ++j)
+        if (offsets[j] <= offsets[j - 1]) return DSQG_ERR_BAD_OFFSETS;
+    memset(t, 0, sizeof(*t));
+    t->J = J;
+    t->d_lo = offsets[0];
+    int nd = 1;
+    while (nd < J && offsets[nd] == offsets[nd - 1] + 1) ++nd;
+    t->n_dense = nd;
+    t->n_sparse = J - nd;
+    for (int j = nd; j < J; ++j) t->sparse[j - nd] = offsets[j];
+    return DSQG_OK;
+}
+
+static int check_shape(int B, int H, int N, int D, int dtype) {
+    if (dtype != DSQG_DTYPE_BF16 && dtype != DSQG_DTYPE_F32) return DSQG_ERR_BAD_DTYPE;
+    if (B < 1 || H < 1 || N < 1 || D < 8 || D > 128 || (D % 8) != 0) return DSQG_ERR_BAD_SHAPE;
+    if ((long long)B * H > 0x7fffffffLL / 2 || (long long)B * H * N > 0x7fffffffLL) return DSQG_ERR_BAD_SHAPE;
+    return DSQG_OK;
+}
+
+}  // namespace dsqg
+
+using namespace dsqg;
+
+extern "C" {
+
+const char* dsqg_status_str(int status) {
+    switch (status) {
+        case DSQG_OK: return "ok";
+        case DSQG_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case DSQG_ERR_BAD_SHAPE: return "shape out of range (need B,H,N >= 1; D a multiple of 8 in [8,128]; 1 <= J <= 128)";
+        case DSQG_ERR_BAD_OFFSETS: return "offsets must be non-negative and strictly ascending (and < R for decode)";
+        case DSQG_ERR_BAD_DTYPE: return "dtype must be DSQG_DTYPE_BF16 (0) or DSQG_DTYPE_F32 (1)";
+        case DSQG_ERR_MISALIGNED: return "tensor pointers must be 16-byte aligned";
+        case DSQG_ERR_SCRATCH_TOO_SMALL: return "scratch buffer smaller than dsqg_bwd_scratch_bytes()";
+        case DSQG_ERR_CUDA: return "CUDA error (see dsqg_last_cuda_error)";
+        case DSQG_ERR_UNSUPPORTED: return "no kernel for this configuration";
+        default: return "unknown status";
+    }
+}
+
+const char* dsqg_last_cuda_error(void) { return g_cuda_err; }
+
+int dsqg_version(void) { return 100; }
+
+int dsqg_fwd(const void* q, const void* k, const void* v,
+             const float* pos_bias, const float* scale_embed, const float* head_gain,
+             const int32_t* offsets, int J, void* out, float* lse,
+             int B, int H, int N, int D, int dtype, void* stream) {
+    if (!q || !k || !v || !pos_bias || !out || !lse) return DSQG_ERR_NULL_POINTER;
+    int rc = check_shape(B, H, N, D, dtype);
+    if (rc) return rc;
+    Taps t;
+    rc = build_taps(offsets, J, &t);
+    if (rc) return rc;
+    if (misaligned16(q) || misaligned16(k) || misaligned16(v) || misaligned16(out) ||
+        (scale_embed && misaligned16(scale_embed)))
+        return DSQG_ERR_MISALIGNED;
+    FwdArgs a;
+    a.q = q; a.k = k; a.v = v; a.pos_bias = pos_bias; a.scale_embed = scale_embed;
+    a.head_gain = head_gain; a.out = out; a.lse = lse;
+    a.B = B; a.H = H; a.N = N; a.D = D;
+    a.scale = 1.0f / sqrtf((float)D);
+    cudaError_t e = launch_fwd(a, t, dtype, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
+}
+
+size_t dsqg_bwd_scratch_bytes(int J, int B, int H, int N, int D, int has_scale_embed) {
+    if (J < 1 || J > DSQG_MAX_TAPS || check_shape(B, H, N, D, DSQG_DTYPE_BF16)) return 0;
+    const BwdGeometry g = bwd_geometry(B, H, N, D);
+    size_t floats = (size_t)B * H * N                       // delta
+                  + (size_t)g.n_tiles * J                    // dpos_bias partials
+                  + (size_t)g.n_tiles                        // dhead_gain partials
+                  + (has_scale_embed ? (size_t)g.n_dse_blocks * J * D : 0);
+    return ((floats * sizeof(float) + 255) / 256) * 256 + 1024;   // room for 256-byte carving
+}
+
+int dsqg_bwd(const void* q, const void* k, const void* v,
+             const float* pos_bias, const float* scale_embed, const float* head_gain,
+             const int32_t* offsets, int J,
+             const void* out, const float* lse, const void* dout,
+             void* dq, void* dk, void* dv,
+             float* dpos_bias, float* dscale_embed, float* dhead_gain,
+             void* scratch, size_t scratch_bytes,
+             int B, int H, int N, int D, int dtype, void* stream) {
+    return dsqg_bwd_stages(q, k, v, pos_bias, scale_embed, head_gain, offsets, J, out, lse, dout,
+                           dq, dk, dv, dpos_bias, dscale_embed, dhead_gain, scratch, scratch_bytes,
+                           B, H, N, D, dtype, stream, DSQG_BWD_STAGE_ALL);
+}
+
+int dsqg_bwd_stages(const void* q, const void* k, const void* v,
+                    const float* pos_bias, const float* scale_embed, const float* head_gain,
+                    const int32_t* offsets, int J,
+                    const void* out, const float* lse, const void* dout,
+                    void* dq, void* dk, void* dv,
+                    float* dpos_bias, float* dscale_embed, float* dhead_gain,
+                    void* scratch, size_t scratch_bytes,
+                    int B, int H, int N, int D, int dtype, void* stream, int stages) {
+    if (stages < 1 || stages > DSQG_BWD_STAGE_ALL) return DSQG_ERR_UNSUPPORTED;
+    if (!q || !k || !v || !pos_bias || !out || !lse || !dout || !dq || !dk || !dv || !dpos_bias || !scratch)
+        return DSQG_ERR_NULL_POINTER;
+    if (scale_embed && !dscale_embed) return DSQG_ERR_NULL_POINTER;
+    if (head_gain && !dhead_gain) return DSQG_ERR_NULL_POINTER;
+    int rc = check_shape(B, H, N, D, dtype);
+    if (rc) return rc;
+    Taps t;
+    rc = build_taps(offsets, J, &t);
+    if (rc) return rc;
+    if (misaligned16(q) || misaligned16(k) || misaligned16(v) || misaligned16(out) || misaligned16(dout) ||
+        misaligned16(dq) || misaligned16(dk) || misaligned16(dv) || misaligned16(scratch) ||
+        (scale_embed && misaligned16(scale_embed)))
+        return DSQG_ERR_MISALIGNED;
+    if (scratch_bytes < dsqg_bwd_scratch_bytes(J, B, H, N, D, scale_embed != nullptr))
+        return DSQG_ERR_SCRATCH_TOO_SMALL;
+
+    const BwdGeometry g = bwd_geometry(B, H, N, D);
+    BwdArgs a;
+    a.q = q; a.k = k; a.v = v; a.pos_bias = pos_bias; a.scale_embed = scale_embed; a.head_gain = head_gain;
+    a.out = out; a.lse = lse; a.dout = dout; a.dq = dq; a.dk = dk; a.dv = dv;
+    a.dpos_bias = dpos_bias; a.dscale_embed = dscale_embed; a.dhead_gain = head_gain ? dhead_gain : nullptr;
+    auto carve = [](char*& p, size_t floats) {
+        float* r = reinterpret_cast<float*>(p);
+        p += ((floats * sizeof(float) + 255) / 256) * 256;
+        return r;
+    };
+    char* p = static_cast<char*>(scratch);
+    // carve() rounds every block up to 256 bytes; the size query reserves the slack.
+    a.delta = carve(p, (size_t)B * H * N);
+    a.dpb_part = carve(p, (size_t)g.n_tiles * J);
+    a.dg_part = carve(p, (size_t)g.n_tiles);
+    a.dse_part = scale_embed ? carve(p, (size_t)g.n_dse_blocks * J * D) : nullptr;
+    a.n_tiles = g.n_tiles; a.tiles_per_bh = g.tiles_per_bh; a.n_dse_blocks = g.n_dse_blocks;
+    a.B = B; a.H = H; a.N = N; a.D = D;
+    a.scale = 1.0f / sqrtf((float)D);
+    cudaError_t e = launch_bwd(a, t, dtype, static_cast<cudaStream_t>(stream), stages);
+    return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
+}
+
+int dsqg_decode(const void* q, const void* k_new, const void* v_new,
+                void* k_ring, void* v_ring, const int32_t* head, const int32_t* fill,
+                const float* pos_bias, const float* scale_embed, const float* head_gain,
+                const int32_t* offsets, int J, int R,
+                void* out, int S, int H, int D, int dtype, void* stream) {
+    if (!q || !k_new || !v_new || !k_ring || !v_ring || !head || !pos_bias || !out) return DSQG_ERR_NULL_POINTER;
+    int rc = check_shape(S, H, 1, D, dtype);
+    if (rc) return rc;
+    if (R < 1 || (long long)S * H * R > 0x7fffffffLL) return DSQG_ERR_BAD_SHAPE;
+    Taps t;
+    rc = build_taps(offsets, J, &t);
+    if (rc) return rc;
+    if (offsets[J - 1] >= R) return DSQG_ERR_BAD_OFFSETS;
+    if (misaligned16(q) || misaligned16(k_new) || misaligned16(v_new) || misaligned16(k_ring) ||
+        misaligned16(v_ring) || misaligned16(out) || (scale_embed && misaligned16(scale_embed)))
+        return DSQG_ERR_MISALIGNED;
+    DecodeArgs a;
+    a.q = q; a.k_new = k_new; a.v_new = v_new; a.k_ring = k_ring; a.v_ring = v_ring;
+    a.head = head; a.fill = fill; a.pos_bias = pos_bias; a.scale_embed = scale_embed;
+    a.head_gain = head_gain; a.out = out; a.S = S; a.H = H; a.D = D; a.R = R;
+    a.scale = 1.0f / sqrtf((float)D);
+    cudaError_t e = launch_decode(a, t, dtype, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
+}
+
+}  // extern "C"

@@ -1,0 +1,113 @@
+// Shared declarations for the DSQG CUDA sources (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "dsqg_b200.h"
+
+namespace dsqg {
+
+// The tap set, passed to every kernel by value (constant parameter space): no global
+// state, so launches are re-entrant.  The leading run of consecutive offsets
+// d_lo, d_lo+1, ..., d_lo+n_dense-1 is the dense window; sparse[] holds the rest.
+struct Taps {
+    int J;         // total number of taps
+    int n_dense;   // taps 0 .. n_dense-1 are d_lo + j
+    int d_lo;      // first (smallest) offset
+    int n_sparse;  // J - n_dense
+    int sparse[DSQG_MAX_TAPS];
+
+    __host__ __device__ __forceinline__ int delta(int j) const {
+        return j < n_dense ? d_lo + j : sparse[j - n_dense];
+    }
+};
+
+struct FwdArgs {
+    const void* q; const void* k; const void* v;
+    const float* pos_bias; const float* scale_embed; const float* head_gain;
+    void* out; float* lse;
+    int B, H, N, D;
+    float scale;   // 1/sqrt(D)
+};
+
+struct BwdArgs {
+    const void* q; const void* k; const void* v;
+    const float* pos_bias; const float* scale_embed; const float* head_gain;
+    const void* out; const float* lse; const void* dout;
+    void* dq; void* dk; void* dv;
+    float* dpos_bias; float* dscale_embed; float* dhead_gain;
+    // scratch carve-up (all fp32)
+    float* delta;      // [B*H*N]    sum_d dout*out per row
+    float* dpb_part;   // [n_tiles, J]
+    float* dg_part;    // [n_tiles]
+    float* dse_part;   // [n_dse_blocks, J, D]
+    int n_tiles, tiles_per_bh, n_dse_blocks;
+    int B, H, N, D;
+    float scale;
+};
+
+struct DecodeArgs {
+    const void* q; const void* k_new; const void* v_new;
+    void* k_ring; void* v_ring;
+    const int32_t* head; const int32_t* fill;
+    const float* pos_bias; const float* scale_embed; const float* head_gain;
+    void* out;
+    int S, H, D, R;
+    float scale;
+};
+
+// Launchers (defined in the .cu files; return a cudaError_t from the launch).
+cudaError_t launch_fwd(const FwdArgs& a, const Taps& t, int dtype, cudaStream_t s);   // dispatcher
+cudaError_t launch_bwd(const BwdArgs& a, const Taps& t, int dtype, cudaStream_t s, int stages);   // dispatcher
+cudaError_t launch_fwd_generic(const FwdArgs& a, const Taps& t, int dtype, cudaStream_t s);
+cudaError_t launch_bwd_generic(const BwdArgs& a, const Taps& t, int dtype, cudaStream_t s, int stages);
+cudaError_t launch_reduce_params(const BwdArgs& a, int J, cudaStream_t s);
+cudaError_t launch_decode(const DecodeArgs& a, const Taps& t, int dtype, cudaStream_t s);
+
+// Geometry of the generic backward's scratch, shared by the size query and the launcher.
+struct BwdGeometry { int rows_per_tile, tiles_per_bh, n_tiles, n_dse_blocks; };
+BwdGeometry bwd_geometry(int B, int H, int N, int D);
+
+// ---------------------------------------------------------------------------------
+// Device helpers: 8-element row slices in fp32 registers, from bf16 or fp32 storage.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&x)[8]) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        x[2 * i]     = __uint_as_float(w[i] << 16);
+        x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void load8(const float* p, float (&x)[8]) {
+    float4 a = *reinterpret_cast<const float4*>(p);
+    float4 b = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+    x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&x)[8]) {
+    uint4 u;
+    u.x = pack_bf16x2(x[0], x[1]); u.y = pack_bf16x2(x[2], x[3]);
+    u.z = pack_bf16x2(x[4], x[5]); u.w = pack_bf16x2(x[6], x[7]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void store8(float* p, const float (&x)[8]) {
+    *reinterpret_cast<float4*>(p)     = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(x[4], x[5], x[6], x[7]);
+}
+
+template <int WIDTH>
+__device__ __forceinline__ float group_sum(float x) {
+#pragma unroll
+    for (int o = WIDTH / 2; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+}
+
+}  // namespace dsqg

@@ -1,0 +1,133 @@
+// Single-token DSQG decode over a circular K/V ring buffer.
+//
+// The DWARF reference describes this cache only in prose (README.md:175-179): because the
+// tap set is fixed, a layer needs the last max(delta)+1 keys/values and nothing else.
+// One warp serves one (sequence, head) pair: it stores the new k, v in slot head[s], then
+// each group of TPR lanes reads one tap row (slot (head - delta_j) mod R) per round, keeps
+// an online-softmax state over the taps it saw, and the groups are merged with shuffles.
+// Pure streaming: 2*J rows of D elements are read per (sequence, head) and nothing is reused.
+#include "dsqg_common.cuh"
+
+namespace dsqg {
+namespace {
+
+constexpr int kWarpsPerBlock = 4;
+
+template <typename T, int TPR>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+decode_kernel(const DecodeArgs a, const Taps t) {
+    constexpr int GROUPS = 32 / TPR;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sh = blockIdx.x * kWarpsPerBlock + warp;      // (sequence, head) pair
+    if (sh >= a.S * a.H) return;                            // whole warp leaves together
+    const int s = sh / a.H, h = sh - s * a.H;
+    const int g = lane / TPR, li = lane % TPR;
+    const int d0 = li * 8, D = a.D;
+    const bool active = d0 < D;
+
+    const int head = a.head[s];
+    const int fill = a.fill ? a.fill[s] : a.R;
+    const T* q = static_cast<const T*>(a.q) + (size_t)sh * D;
+    const T* kn = static_cast<const T*>(a.k_new) + (size_t)sh * D;
+    const T* vn = static_cast<const T*>(a.v_new) + (size_t)sh * D;
+    T* kr = static_cast<T*>(a.k_ring) + (size_t)sh * a.R * D;
+    T* vr = static_cast<T*>(a.v_ring) + (size_t)sh * a.R * D;
+    const bool has_se = a.scale_embed != nullptr;
+
+    float qx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (active) load8(q + d0, qx);
+    // Store the new token; taps with delta == 0 read k_new / v_new directly, so no lane
+    // depends on this store becoming visible inside the kernel.
+    if (g == 0 && active) {
+        float t8[8];
+        load8(kn + d0, t8); store8(kr + (size_t)head * D + d0, t8);   // bf16->fp32->bf16 is exact
+        load8(vn + d0, t8); store8(vr + (size_t)head * D + d0, t8);
+    }
+
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float m = -INFINITY, l = 0.f;
+    const int rounds = (t.J + GROUPS - 1) / GROUPS;
+#pragma unroll 4
+    for (int r = 0; r < rounds; ++r) {
+        const int j = r * GROUPS + g;
+        const int delta = j < t.J ? t.delta(j) : 0;
+        const bool valid = j < t.J && delta < fill;
+        int slot = head - delta;
+        if (slot < 0) slot += a.R;
+        float kx[8] = {0, 0, 0, 0, 0, 0, 0, 0}, vx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (valid && active) {
+            const T* kp = delta == 0 ? kn : kr + (size_t)slot * D;
+            const T* vp = delta == 0 ? vn : vr + (size_t)slot * D;
+            load8(kp + d0, kx);
+            load8(vp + d0, vx);
+            if (has_se) {
+                float se[8];
+                load8(a.scale_embed + (size_t)j * D + d0, se);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) kx[i] += se[i];
+            }
+        }
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot = fmaf(qx[i], kx[i], dot);
+        dot = group_sum<TPR>(dot);
+        if (valid) {
+            const float sc = dot * a.scale + a.pos_bias[j * a.H + h];
+            const float mn = fmaxf(m, sc);
+            const float cor = __expf(m - mn), p = __expf(sc - mn);
+            l = l * cor + p;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = acc[i] * cor + p * vx[i];
+            m = mn;
+        }
+    }
+    // Merge the GROUPS partial softmax states.
+#pragma unroll
+    for (int o = TPR; o < 32; o <<= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+        const float l2 = __shfl_xor_sync(0xffffffffu, l, o);
+        const float mn = fmaxf(m, m2);
+        const float c1 = (m == -INFINITY) ? 0.f : __expf(m - mn);
+        const float c2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
+        l = l * c1 + l2 * c2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float a2 = __shfl_xor_sync(0xffffffffu, acc[i], o);
+            acc[i] = acc[i] * c1 + a2 * c2;
+        }
+        m = mn;
+    }
+    if (g == 0 && active) {
+        const float gain = a.head_gain ? a.head_gain[h] : 1.f;
+        const float inv = l > 0.f ? gain / l : 0.f;
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = acc[i] * inv;
+        store8(static_cast<T*>(a.out) + (size_t)sh * D + d0, o);
+    }
+}
+
+template <typename T, int TPR>
+cudaError_t decode_launch(const DecodeArgs& a, const Taps& t, cudaStream_t s) {
+    const int pairs = a.S * a.H;
+    decode_kernel<T, TPR><<<(pairs + kWarpsPerBlock - 1) / kWarpsPerBlock, kWarpsPerBlock * 32, 0, s>>>(a, t);
+    return cudaGetLastError();
+}
+}  // namespace
+
+#define DSQG_DECODE_TPR(T)                                              \
+    do {                                                                \
+        const int chunks_ = a.D / 8;                                    \
+        if (chunks_ <= 1) return decode_launch<T, 1>(a, t, s);          \
+        if (chunks_ <= 2) return decode_launch<T, 2>(a, t, s);          \
+        if (chunks_ <= 4) return decode_launch<T, 4>(a, t, s);          \
+        if (chunks_ <= 8) return decode_launch<T, 8>(a, t, s);          \
+        return decode_launch<T, 16>(a, t, s);                           \
+    } while (0)
+
+cudaError_t launch_decode(const DecodeArgs& a, const Taps& t, int dtype, cudaStream_t s) {
+    if (dtype == DSQG_DTYPE_BF16) DSQG_DECODE_TPR(__nv_bfloat16);
+    DSQG_DECODE_TPR(float);
+}
+
+}  // namespace dsqg

@@ -1,0 +1,132 @@
+"""Drop-in operator functions and attention modules with the DWARF reference's names.
+
+* ``dsqg_attention_v2(q, k, v, pos_bias)``               kernels/dsqg_attention_v2.py:417-427
+* ``dsqg_attention_v3(q, k, v, pos_bias, scale_embed)``  kernels/dsqg_attention_v3.py:445-456
+* ``DSQGAttentionN_Fused``                               kernels/dsqg_attention_v2.py:434-477
+* ``DSQGAttentionV3``                                    kernels/dsqg_attention_v3.py:463-536
+* ``DSQGAttentionQW`` (V3 + per-head ``if_gain``)        train/train_2048_condU.py:116-205
+
+Parameter names and shapes (``qkv_proj``, ``out_proj``, ``gate_proj``, ``pos_bias [J,H]``,
+``scale_embed [J,HD]``, ``if_gain [H]``) match the reference so its state dicts load.
+Unlike the reference, any ascending offset set is accepted and the ``if_gain`` multiply is
+fused into the kernel epilogue.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence
+
+import torch
+import torch.nn as nn
+
+from .ops import ALL_OFFSETS, dsqg_attention
+
+
+def dsqg_attention_v2(q, k, v, pos_bias, offsets: Sequence[int] = ALL_OFFSETS):
+    """condM op.  q, k, v [B,H,N,HD] (non-bf16 inputs are computed in bf16 and the result is
+    cast back, as in the reference); pos_bias [J,H] fp32."""
+    orig = q.dtype
+    if orig != torch.bfloat16:
+        q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    out = dsqg_attention(q, k, v, pos_bias, None, None, offsets)
+    return out if orig == torch.bfloat16 else out.to(orig)
+
+
+def dsqg_attention_v3(q, k, v, pos_bias, scale_embed, offsets: Sequence[int] = ALL_OFFSETS):
+    """condU op: adds the Q-weighted scale term q.scale_embed[j]/sqrt(HD) to every score."""
+    orig = q.dtype
+    if orig != torch.bfloat16:
+        q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    out = dsqg_attention(q, k, v, pos_bias, None, scale_embed, offsets)
+    return out if orig == torch.bfloat16 else out.to(orig)
+
+
+def _log_linear_bias(offsets, num_heads):
+    # pos_bias[j,h] = -log(1+delta_j) * alpha_h  (kernels/dsqg_attention_v2.py:454-456)
+    alphas = torch.linspace(0.2, 2.0, num_heads)
+    logs = torch.tensor([math.log(1.0 + d) for d in offsets], dtype=torch.float32)
+    return -logs[:, None] * alphas[None, :]
+
+
+class _DSQGAttentionBase(nn.Module):
+    """qkv projection -> DSQG op -> sigmoid gate -> output projection."""
+
+    def __init__(self, embedding_dim, num_heads, seq_len=2048, offsets=None, dropout=0.1,
+                 gate_bias=2.0, with_scale_embed=False, with_if_gain=False):
+        super().__init__()
+        if embedding_dim % num_heads:
+            raise ValueError("embedding_dim must be divisible by num_heads")
+        self.embedding_dim, self.num_heads = embedding_dim, num_heads
+        self.head_dim = embedding_dim // num_heads
+        self.seq_len = seq_len
+        offsets = list(ALL_OFFSETS if offsets is None else offsets)
+        self.register_buffer("offsets", torch.tensor(offsets, dtype=torch.long))
+        self._offsets = tuple(offsets)
+        self.n_offsets = len(offsets)
+        self.qkv_proj = nn.Linear(embedding_dim, 3 * embedding_dim, bias=True)
+        self.out_proj = nn.Linear(embedding_dim, embedding_dim, bias=True)
+        self.gate_proj = nn.Linear(embedding_dim, embedding_dim, bias=True)
+        nn.init.constant_(self.gate_proj.bias, gate_bias)
+        self.pos_bias = nn.Parameter(_log_linear_bias(offsets, num_heads))
+        if with_scale_embed:
+            self.scale_embed = nn.Parameter(torch.zeros(self.n_offsets, self.head_dim))
+        if with_if_gain:
+            self.if_gain = nn.Parameter(torch.ones(num_heads))
+        self.dropout = nn.Dropout(dropout)
+
+    def forward(self, x, kv_inject=None):
+        B, N, D = x.shape
+        H, HD = self.num_heads, self.head_dim
+        q, k, v = (t.view(B, N, H, HD).permute(0, 2, 1, 3).contiguous()
+                   for t in self.qkv_proj(x).split(D, dim=-1))
+        if kv_inject is not None:          # Huygens K/V injection, train_2048_condU.py:178-181
+            k = k + kv_inject[0]
+            v = v + kv_inject[1]
+        orig = q.dtype
+        if orig != torch.bfloat16:
+            q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+        out = dsqg_attention(q, k, v, self.pos_bias, getattr(self, "if_gain", None),
+                             getattr(self, "scale_embed", None), self._offsets)
+        out = out if orig == torch.bfloat16 else out.to(orig)
+        flat = out.permute(0, 2, 1, 3).reshape(B, N, D)
+        return self.dropout(self.out_proj(flat * torch.sigmoid(self.gate_proj(x))))
+
+    def attn_summary(self):
+        with torch.no_grad():
+            pb = self.pos_bias.detach().float().cpu()
+            info = {"pos_bias_abs_mean": pb.abs().mean().item(),
+                    "pos_bias_abs_max": pb.abs().max().item(),
+                    "pos_bias_mean_per_head": pb.mean(0).tolist()}
+            if hasattr(self, "scale_embed"):
+                se = self.scale_embed.detach().float().cpu()
+                info["scale_embed_abs_mean"] = se.abs().mean().item()
+                info["scale_embed_abs_max"] = se.abs().max().item()
+            if hasattr(self, "if_gain"):
+                info["if_gain"] = self.if_gain.detach().float().cpu().tolist()
+        return info
+
+
+class DSQGAttentionN_Fused(_DSQGAttentionBase):
+    """condM attention (pos_bias only; gate bias 2.0)."""
+
+    def __init__(self, embedding_dim, num_heads, seq_len=2048, offsets=None, dropout=0.1):
+        super().__init__(embedding_dim, num_heads, seq_len, offsets, dropout, gate_bias=2.0)
+
+    def forward(self, x):                      # the reference signature has no kv_inject here
+        return super().forward(x)
+
+
+class DSQGAttentionV3(_DSQGAttentionBase):
+    """condU attention: pos_bias + scale_embed (zero-init), gate bias 0."""
+
+    def __init__(self, embedding_dim, num_heads, seq_len=2048, offsets=None, dropout=0.1):
+        super().__init__(embedding_dim, num_heads, seq_len, offsets, dropout, gate_bias=0.0,
+                         with_scale_embed=True)
+
+
+class DSQGAttentionQW(_DSQGAttentionBase):
+    """condU attention with the per-head IF gain; the gain multiply runs inside the kernel."""
+
+    def __init__(self, embedding_dim, num_heads, seq_len=2048, dropout=0.1, offsets=None):
+        super().__init__(embedding_dim, num_heads, seq_len, offsets, dropout, gate_bias=0.0,
+                         with_scale_embed=True, with_if_gain=True)

@@ -1,0 +1,146 @@
+"""DSQG attention as a torch.autograd.Function over the native C ABI.
+
+Mirrors the operator layer of the DWARF reference:
+``_DSQGFn`` / ``_DSQGFnV3`` (kernels/dsqg_attention_v2.py:337-414,
+kernels/dsqg_attention_v3.py:359-442) and their functional wrappers
+(:417-427, :445-456).  PyTorch is used for device memory and streams only; all
+arithmetic happens in libdsqg_b200.so.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+
+SPARSE_TAPS = (48, 64, 96, 128, 192, 256, 384, 512, 768, 1024, 1536)
+#: The reference's 44-offset set (kernels/dsqg_attention_v3.py:47-49): dense 0..32 + 11 taps.
+ALL_OFFSETS = tuple(range(33)) + SPARSE_TAPS
+#: Dense 0..31 + the same 11 taps: the 43-offset set the benchmark configurations name.
+OFFSETS_43 = tuple(range(32)) + SPARSE_TAPS
+#: 43-set extended for N = 4096.
+OFFSETS_45 = OFFSETS_43 + (2048, 3072)
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _lib.DSQG_DTYPE_BF16
+    if t.dtype == torch.float32:
+        return _lib.DSQG_DTYPE_F32
+    raise TypeError(f"dsqg: q/k/v must be bfloat16 or float32, got {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _check_inputs(q, k, v, pos_bias, head_gain, scale_embed, J):
+    if not q.is_cuda:
+        raise RuntimeError("dsqg: tensors must live on a CUDA device (there is no CPU path)")
+    if q.dim() != 4:
+        raise ValueError(f"dsqg: q must be [B,H,N,HD], got {tuple(q.shape)}")
+    B, H, N, D = q.shape
+    for name, t in (("k", k), ("v", v)):
+        if t.shape != q.shape or t.dtype != q.dtype or t.device != q.device:
+            raise ValueError(f"dsqg: {name} must match q in shape, dtype and device")
+    if tuple(pos_bias.shape) != (J, H):
+        raise ValueError(f"dsqg: pos_bias must be [{J},{H}], got {tuple(pos_bias.shape)}")
+    if scale_embed is not None and tuple(scale_embed.shape) != (J, D):
+        raise ValueError(f"dsqg: scale_embed must be [{J},{D}], got {tuple(scale_embed.shape)}")
+    if head_gain is not None and tuple(head_gain.shape) != (H,):
+        raise ValueError(f"dsqg: head_gain must be [{H}], got {tuple(head_gain.shape)}")
+
+
+def _f32c(t):
+    return None if t is None else t.detach().to(torch.float32).contiguous()
+
+
+class DSQGFunction(torch.autograd.Function):
+    """out = DSQG(q, k, v; pos_bias, head_gain, scale_embed, offsets) with autograd.
+
+    Saves (q, k, v, pos_bias, head_gain, scale_embed, out, lse) like the reference
+    (kernels/dsqg_attention_v3.py:384) and returns gradients for the six tensors.
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, pos_bias, head_gain, scale_embed, offsets):
+        lib = _lib.load()
+        off, J = _lib.offsets_array(offsets)
+        _check_inputs(q, k, v, pos_bias, head_gain, scale_embed, J)
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        pb, hg, se = _f32c(pos_bias), _f32c(head_gain), _f32c(scale_embed)
+        B, H, N, D = q.shape
+        out = torch.empty_like(q)
+        lse = torch.empty(B, H, N, device=q.device, dtype=torch.float32)
+        with torch.cuda.device(q.device):
+            stream = torch.cuda.current_stream(q.device).cuda_stream
+            _lib.check(lib.dsqg_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), _ptr(se),
+                                    _ptr(hg), off, J, out.data_ptr(), lse.data_ptr(),
+                                    B, H, N, D, _dtype_code(q), stream), "dsqg_fwd")
+        ctx.save_for_backward(q, k, v, pb, hg, se, out, lse)
+        ctx.offsets = tuple(offsets)
+        ctx.param_dtypes = (pos_bias.dtype, None if head_gain is None else head_gain.dtype,
+                            None if scale_embed is None else scale_embed.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        lib = _lib.load()
+        q, k, v, pb, hg, se, out, lse = ctx.saved_tensors
+        off, J = _lib.offsets_array(ctx.offsets)
+        B, H, N, D = q.shape
+        dout = dout.contiguous()                      # kernels/dsqg_attention_v3.py:394
+        if dout.dtype != q.dtype:
+            dout = dout.to(q.dtype)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dpb = torch.empty_like(pb)
+        dse = None if se is None else torch.empty_like(se)
+        dhg = None if hg is None else torch.empty_like(hg)
+        nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, int(se is not None))
+        scratch = torch.empty(nbytes, device=q.device, dtype=torch.uint8)
+        with torch.cuda.device(q.device):
+            stream = torch.cuda.current_stream(q.device).cuda_stream
+            _lib.check(lib.dsqg_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), _ptr(se),
+                                    _ptr(hg), off, J, out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
+                                    dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                    dpb.data_ptr(), _ptr(dse), _ptr(dhg),
+                                    scratch.data_ptr(), nbytes, B, H, N, D, _dtype_code(q), stream),
+                       "dsqg_bwd")
+        pb_dt, hg_dt, se_dt = ctx.param_dtypes
+        return (dq, dk, dv, dpb.to(pb_dt),
+                None if dhg is None else dhg.to(hg_dt),
+                None if dse is None else dse.to(se_dt), None)
+
+
+def dsqg_attention(q, k, v, pos_bias, head_gain=None, scale_embed=None,
+                   offsets: Sequence[int] = ALL_OFFSETS):
+    """General DSQG entry: any ascending offset set, optional per-head output gain and
+    Q-weighted scale embedding.  q, k, v: [B,H,N,HD] bf16 (fast path) or fp32; fp16 inputs
+    are computed in bf16 as the reference does (kernels/dsqg_attention_v3.py:452-456) and
+    the result is returned in the caller's dtype."""
+    orig_dtype = q.dtype
+    if orig_dtype not in (torch.bfloat16, torch.float32):
+        q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    out = DSQGFunction.apply(q, k, v, pos_bias, head_gain, scale_embed, tuple(int(o) for o in offsets))
+    return out if out.dtype == orig_dtype else out.to(orig_dtype)
+
+
+def dsqg_forward_lse(q, k, v, pos_bias, head_gain=None, scale_embed=None,
+                     offsets: Sequence[int] = ALL_OFFSETS):
+    """Forward without autograd; returns (out, lse).  lse is the natural-log softmax
+    denominator per row, the tensor the reference saves for backward."""
+    lib = _lib.load()
+    off, J = _lib.offsets_array(offsets)
+    _check_inputs(q, k, v, pos_bias, head_gain, scale_embed, J)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    pb, hg, se = _f32c(pos_bias), _f32c(head_gain), _f32c(scale_embed)
+    B, H, N, D = q.shape
+    out = torch.empty_like(q)
+    lse = torch.empty(B, H, N, device=q.device, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        _lib.check(lib.dsqg_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), _ptr(se),
+                                _ptr(hg), off, J, out.data_ptr(), lse.data_ptr(),
+                                B, H, N, D, _dtype_code(q), stream), "dsqg_fwd")
+    return out, lse

@@ -1,0 +1,137 @@
+/* dsqg_b200.h -- C ABI of the B200-native DSQG attention library (libdsqg_b200.so).
+ *
+ * DSQG = Dyadic Sparse Q-K Gather attention, the hot operator of Lanerra/DWARF: for
+ * every query row n of every (batch, head) pair, score a fixed ascending set of J causal
+ * offsets delta_j,
+ *
+ *     s_j = q[n].k[n-delta_j] / sqrt(D) + pos_bias[j,h] (+ q[n].scale_embed[j] / sqrt(D)),
+ *     s_j = -inf where n - delta_j < 0,
+ *     out[n] = head_gain[h] * sum_j softmax_j(s)_j * v[n-delta_j].
+ *
+ * Conventions shared by every entry point
+ *   - q, k, v, out, dout, dq, dk, dv: DEVICE pointers, contiguous [B,H,N,D], element type
+ *     selected by `dtype` (DSQG_DTYPE_BF16 or DSQG_DTYPE_F32), 16-byte aligned.
+ *   - pos_bias [J,H], scale_embed [J,D] (nullable), head_gain [H] (nullable), lse [B,H,N]:
+ *     DEVICE pointers to fp32.
+ *   - offsets: HOST pointer to J int32 values, strictly ascending, >= 0.  The leading run
+ *     of consecutive integers is treated as the dense window, the rest as sparse taps.
+ *   - stream: a cudaStream_t passed as void* (NULL = legacy default stream).
+ *   - The caller owns every buffer; the library allocates nothing and keeps no state
+ *     between calls.  The caller makes the device current (cudaSetDevice) before calling.
+ *   - Every function returns DSQG_OK (0) or a negative dsqg_status; nothing throws, traps
+ *     or aborts.  Argument errors are detected on the host before any launch.
+ *   - D must be a multiple of 8, 8 <= D <= 128; J <= DSQG_MAX_TAPS.
+ */
+#ifndef DSQG_B200_H
+#define DSQG_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSQG_MAX_TAPS 128
+
+typedef enum {
+    DSQG_OK = 0,
+    DSQG_ERR_NULL_POINTER = -1,   /* a required pointer is NULL */
+    DSQG_ERR_BAD_SHAPE = -2,      /* B,H,N,D,J,R,S out of the supported range */
+    DSQG_ERR_BAD_OFFSETS = -3,    /* offsets not strictly ascending / negative */
+    DSQG_ERR_BAD_DTYPE = -4,      /* dtype is neither DSQG_DTYPE_BF16 nor DSQG_DTYPE_F32 */
+    DSQG_ERR_MISALIGNED = -5,     /* a tensor pointer is not 16-byte aligned */
+    DSQG_ERR_SCRATCH_TOO_SMALL = -6,
+    DSQG_ERR_CUDA = -7,           /* a CUDA runtime/driver call failed (see dsqg_last_cuda_error) */
+    DSQG_ERR_UNSUPPORTED = -8     /* valid request that this build has no kernel for */
+} dsqg_status;
+
+enum { DSQG_DTYPE_BF16 = 0, DSQG_DTYPE_F32 = 1 };
+
+/* Human-readable text for a status code.  Never NULL. */
+const char* dsqg_status_str(int status);
+
+/* Text of the last CUDA error seen by the calling thread inside this library ("" if none). */
+const char* dsqg_last_cuda_error(void);
+
+/* Library version, major*10000 + minor*100 + patch. */
+int dsqg_version(void);
+
+/* Testing knob with no counterpart in the reference: 0 = choose kernels automatically
+ * (default), 1 = always use the generic CUDA-core kernels.  Process-wide. */
+int dsqg_set_kernel_path(int path);
+
+/* Forward.
+ * Replaces: _DSQGFn.forward / _DSQGFnV3.forward + the _fwd/_fwd_v3 kernels
+ *   (DWARF kernels/dsqg_attention_v2.py:337-363, kernels/dsqg_attention_v3.py:359-387,
+ *   :60-163) and the native precedent dsqg_forward_cuda
+ *   (kernels/dsqg_cuda/dsqg_cuda_kernel.cu:496-519); the `* if_gain` of
+ *   train/train_2048_condU.py:187 is fused into the epilogue through head_gain.
+ * Writes out [B,H,N,D] (dtype) and lse [B,H,N] fp32 (natural log of the softmax
+ * denominator, as the reference saves it).  A row with no valid tap gets out = 0 and
+ * lse = -inf. */
+int dsqg_fwd(const void* q, const void* k, const void* v,
+             const float* pos_bias, const float* scale_embed, const float* head_gain,
+             const int32_t* offsets, int J,
+             void* out, float* lse,
+             int B, int H, int N, int D, int dtype, void* stream);
+
+/* Bytes of device scratch dsqg_bwd needs for this problem (0 on invalid arguments). */
+size_t dsqg_bwd_scratch_bytes(int J, int B, int H, int N, int D, int has_scale_embed);
+
+/* Backward.
+ * Replaces: _DSQGFn.backward / _DSQGFnV3.backward and their three kernels _compute_D,
+ *   _bwd_dq, _bwd_dkdv (kernels/dsqg_attention_v3.py:170-352, :389-442) and
+ *   dsqg_backward_cuda (kernels/dsqg_cuda/dsqg_cuda_kernel.cu:582-609).
+ * Inputs: the forward's inputs, its out and lse, and the upstream gradient dout.
+ * Writes dq, dk, dv (dtype), dpos_bias [J,H] fp32, and, when the matching input is
+ * given, dscale_embed [J,D] fp32 and dhead_gain [H] fp32.  Parameter gradients are
+ * produced by per-block partial sums in `scratch` followed by a fixed-order reduction:
+ * no atomics, bitwise reproducible from run to run. */
+int dsqg_bwd(const void* q, const void* k, const void* v,
+             const float* pos_bias, const float* scale_embed, const float* head_gain,
+             const int32_t* offsets, int J,
+             const void* out, const float* lse, const void* dout,
+             void* dq, void* dk, void* dv,
+             float* dpos_bias, float* dscale_embed, float* dhead_gain,
+             void* scratch, size_t scratch_bytes,
+             int B, int H, int N, int D, int dtype, void* stream);
+
+/* dsqg_bwd restricted to some of its kernels: a profiling aid with no counterpart in the
+ * reference.  `stages` is a bit mask: DSQG_BWD_STAGE_DQ (dQ, delta and the parameter-gradient
+ * partials), DSQG_BWD_STAGE_DKDV (dK, dV; needs the delta a previous DQ stage left in the same
+ * scratch), DSQG_BWD_STAGE_REDUCE (fixed-order reduction of the partials into dpos_bias,
+ * dscale_embed, dhead_gain).  Running the three stages one after the other on one stream with
+ * the same scratch is exactly dsqg_bwd. */
+#define DSQG_BWD_STAGE_DQ 1
+#define DSQG_BWD_STAGE_DKDV 2
+#define DSQG_BWD_STAGE_REDUCE 4
+#define DSQG_BWD_STAGE_ALL 7
+int dsqg_bwd_stages(const void* q, const void* k, const void* v,
+                    const float* pos_bias, const float* scale_embed, const float* head_gain,
+                    const int32_t* offsets, int J,
+                    const void* out, const float* lse, const void* dout,
+                    void* dq, void* dk, void* dv,
+                    float* dpos_bias, float* dscale_embed, float* dhead_gain,
+                    void* scratch, size_t scratch_bytes,
+                    int B, int H, int N, int D, int dtype, void* stream, int stages);
+
+/* Single-token decode over a circular K/V ring buffer.
+ * Replaces: nothing executable -- the reference only describes the O(1) cache in prose
+ *   (DWARF README.md:175-179; generate() in train/train_2048_condU.py:463-487 re-runs the
+ *   whole prefix).  Semantics are those of dsqg_fwd's last row on the time-ordered ring.
+ * q, k_new, v_new, out: [S,H,D]; k_ring, v_ring: [S,H,R,D] (updated in place: the new
+ * k, v are stored in slot head[s] before the taps are read); head: DEVICE int32 [S],
+ * 0 <= head[s] < R; fill: DEVICE int32 [S] = number of valid tokens in the ring counting
+ * the new one, or NULL for a full ring.  Tap j reads slot (head - delta_j) mod R and is
+ * valid iff delta_j < fill[s].  Requires max(offsets) < R. */
+int dsqg_decode(const void* q, const void* k_new, const void* v_new,
+                void* k_ring, void* v_ring, const int32_t* head, const int32_t* fill,
+                const float* pos_bias, const float* scale_embed, const float* head_gain,
+                const int32_t* offsets, int J, int R,
+                void* out, int S, int H, int D, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSQG_B200_H */

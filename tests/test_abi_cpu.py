@@ -1,0 +1,113 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every declared symbol, and
+rejects bad arguments on the host with a status code (no kernel is launched, no GPU needed)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from dwarf_b200 import _lib
+from dwarf_b200.build import build_library
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build_library()
+    return _lib.load()
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "dsqg_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(dsqg_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(lib):
+    names = declared_functions()
+    assert {"dsqg_fwd", "dsqg_bwd", "dsqg_decode", "dsqg_bwd_scratch_bytes", "dsqg_status_str"} <= set(names)
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/dsqg_b200.h but not exported"
+    assert set(names) == set(_lib.EXPORTED_SYMBOLS)
+
+
+def test_status_strings(lib):
+    assert lib.dsqg_status_str(0) == b"ok"
+    for code in range(-8, 0):
+        assert len(lib.dsqg_status_str(code)) > 3
+    assert lib.dsqg_status_str(-99) == b"unknown status"
+    assert lib.dsqg_version() >= 100
+
+
+def _fake(n=1):
+    return 4096 * n      # a non-null, 16-byte aligned fake device address (never dereferenced)
+
+
+def _off(vals):
+    return (ctypes.c_int32 * len(vals))(*vals), len(vals)
+
+
+def call_fwd(lib, q=_fake(1), k=_fake(2), v=_fake(3), pb=_fake(4), se=None, hg=None,
+             offsets=(0, 1, 2, 8), out=_fake(5), lse=_fake(6), B=1, H=2, N=16, D=32, dtype=0):
+    off, J = _off(offsets) if offsets is not None else (None, 4)
+    return lib.dsqg_fwd(q, k, v, pb, se, hg, off, J, out, lse, B, H, N, D, dtype, None)
+
+
+def test_fwd_argument_errors_are_statuses(lib):
+    assert call_fwd(lib, q=None) == -1
+    assert call_fwd(lib, lse=None) == -1
+    assert call_fwd(lib, offsets=None) == -1
+    assert call_fwd(lib, D=33) == -2 and call_fwd(lib, D=0) == -2 and call_fwd(lib, D=136) == -2
+    assert call_fwd(lib, N=0) == -2 and call_fwd(lib, B=-1) == -2
+    assert call_fwd(lib, offsets=(0, 2, 2)) == -3 and call_fwd(lib, offsets=(-1, 0)) == -3
+    assert call_fwd(lib, offsets=(3, 1)) == -3
+    assert call_fwd(lib, offsets=tuple(range(129))) == -2
+    assert call_fwd(lib, dtype=7) == -4
+    assert call_fwd(lib, q=_fake(1) + 8) == -5 and call_fwd(lib, out=_fake(5) + 2) == -5
+
+
+def test_bwd_scratch_and_argument_errors(lib):
+    n = lib.dsqg_bwd_scratch_bytes(43, 32, 8, 2048, 32, 0)
+    assert n >= 32 * 8 * 2048 * 4
+    assert lib.dsqg_bwd_scratch_bytes(43, 32, 8, 2048, 32, 1) > n
+    assert lib.dsqg_bwd_scratch_bytes(0, 1, 1, 1, 32, 0) == 0
+    assert lib.dsqg_bwd_scratch_bytes(43, 1, 1, 16, 12, 0) == 0
+    off, J = _off((0, 1, 4))
+    args = dict(B=1, H=1, N=16, D=32)
+    need = lib.dsqg_bwd_scratch_bytes(J, 1, 1, 16, 32, 0)
+
+    def call(scratch=_fake(20), nbytes=need, dq=_fake(10), hg=None, dhg=None, dtype=0):
+        return lib.dsqg_bwd(_fake(1), _fake(2), _fake(3), _fake(4), None, hg, off, J,
+                            _fake(5), _fake(6), _fake(7), dq, _fake(11), _fake(12),
+                            _fake(13), None, dhg, scratch, nbytes, 1, 1, 16, 32, dtype, None)
+    assert call(nbytes=need - 1) == -6
+    assert call(scratch=None) == -1 and call(dq=None) == -1
+    assert call(hg=_fake(30), dhg=None) == -1          # gain given but no place for its gradient
+    assert call(scratch=_fake(20) + 4) == -5
+    assert call(dtype=2) == -4
+
+
+def test_decode_argument_errors(lib):
+    off, J = _off((0, 1, 2, 5))
+
+    def call(R=6, head=_fake(8), S=2, D=64, kr=_fake(4)):
+        return lib.dsqg_decode(_fake(1), _fake(2), _fake(3), kr, _fake(5), head, None,
+                               _fake(6), None, None, off, J, R, _fake(7), S, 2, D, 0, None)
+    assert call(R=5) == -3                  # max offset must be < R
+    assert call(head=None) == -1
+    assert call(D=12) == -2 and call(S=0) == -2
+    assert call(kr=_fake(4) + 8) == -5
+
+
+def test_python_wrappers_refuse_cpu_tensors():
+    import torch
+    from dwarf_b200 import dsqg_attention
+    q = torch.zeros(1, 1, 8, 32, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        dsqg_attention(q, q, q, torch.zeros(44, 1))
+
+
+def test_kernel_path_knob(lib):
+    assert lib.dsqg_set_kernel_path(1) == 0 and lib.dsqg_set_kernel_path(0) == 0
+    assert lib.dsqg_set_kernel_path(5) == -8

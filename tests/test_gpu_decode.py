@@ -1,0 +1,112 @@
+"""GPU tests of the ring-buffer decode kernel against the decode oracle (which is defined as
+the last row of the full-sequence reference on the time-ordered ring)."""
+import pytest
+import torch
+
+import dwarf_b200
+from dwarf_b200 import synth
+from oracle import dsqg_oracle as O
+from tests.gpu_util import assert_bf16_close, rel_inf
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run_cuda(q, kn, vn, kr, vr, head, pb, gain, offsets, fill=None, se=None, dtype=torch.bfloat16):
+    to = lambda t: t.to(DEV, dtype).contiguous()
+    krd, vrd = to(kr), to(vr)
+    out = dwarf_b200.dsqg_decode_step(to(q), to(kn), to(vn), krd, vrd, head.to(DEV), pb.to(DEV),
+                                      None if gain is None else gain.to(DEV),
+                                      None if se is None else se.to(DEV), offsets,
+                                      None if fill is None else fill.to(DEV))
+    return out.float().cpu(), krd.float().cpu(), vrd.float().cpu()
+
+
+def bf16v(*shape, gen=None):
+    return torch.randn(*shape, generator=gen).to(torch.bfloat16).float()
+
+
+def test_every_head_position_small_ring_matches_full_sequence_oracle():
+    g = torch.Generator().manual_seed(0)
+    offsets = (0, 1, 2, 3, 6, 9, 12)
+    R, S, H, D = 13, 13, 3, 32
+    kr, vr = bf16v(S, H, R, D, gen=g), bf16v(S, H, R, D, gen=g)
+    q, kn, vn = (bf16v(S, H, D, gen=g) for _ in range(3))
+    pb = torch.randn(len(offsets), H, generator=g); gain = torch.rand(H, generator=g) + 0.5
+    head = torch.arange(S, dtype=torch.int32)             # one sequence per head position 0..R-1
+    out, k2, v2 = run_cuda(q, kn, vn, kr, vr, head, pb, gain, offsets)
+    for s in range(S):     # full-sequence definition, one sequence at a time (fill may differ)
+        ref, kref, vref = O.decode_reference(q[s:s + 1], kn[s:s + 1], vn[s:s + 1], kr[s:s + 1], vr[s:s + 1],
+                                             head[s:s + 1], pb, gain, offsets)
+        assert_bf16_close(out[s:s + 1], ref, f"out[s={s}]")
+        assert torch.equal(k2[s:s + 1], kref) and torch.equal(v2[s:s + 1], vref)   # ring update is exact
+
+
+@pytest.mark.parametrize("D", [32, 64, 80, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_full_ring_1537_slots_43_taps(D, dtype):
+    g = torch.Generator().manual_seed(D)
+    S, H, R = 5, 4, 1537
+    kr, vr = bf16v(S, H, R, D, gen=g), bf16v(S, H, R, D, gen=g)
+    q, kn, vn = (bf16v(S, H, D, gen=g) for _ in range(3))
+    pb = synth.log_linear_pos_bias(O.OFFSETS_43, H); gain = torch.rand(H, generator=g) + 0.5
+    se = torch.randn(43, D, generator=g) * 0.05
+    head = torch.tensor([0, 1, 31, 1535, 1536], dtype=torch.int32)      # wrap-around cases
+    out, k2, v2 = run_cuda(q, kn, vn, kr, vr, head, pb, gain, O.OFFSETS_43, se=se, dtype=dtype)
+    ref, kref, vref = O.decode_reference_direct(q, kn, vn, kr, vr, head, pb, gain, O.OFFSETS_43, scale_embed=se)
+    if dtype == torch.float32:
+        assert rel_inf(out, ref) < 1e-5
+    else:
+        assert_bf16_close(out, ref, "out")
+    assert torch.equal(k2, kref) and torch.equal(v2, vref)
+
+
+def test_partially_filled_ring_masks_taps():
+    g = torch.Generator().manual_seed(4)
+    S, H, D, R = 6, 2, 64, 1537
+    kr, vr = bf16v(S, H, R, D, gen=g), bf16v(S, H, R, D, gen=g)
+    q, kn, vn = (bf16v(S, H, D, gen=g) for _ in range(3))
+    pb = synth.log_linear_pos_bias(O.OFFSETS_43, H)
+    head = torch.tensor([0, 4, 40, 100, 700, 1536], dtype=torch.int32)
+    fill = torch.tensor([1, 5, 41, 101, 701, 1537], dtype=torch.int32)
+    out, _, _ = run_cuda(q, kn, vn, kr, vr, head, pb, None, O.OFFSETS_43, fill=fill)
+    ref, _, _ = O.decode_reference_direct(q, kn, vn, kr, vr, head, pb, None, O.OFFSETS_43, fill=fill)
+    assert_bf16_close(out, ref, "out")
+    assert_bf16_close(out[0], vn[0], "first token attends to itself only")
+    # the full-sequence definition agrees for one of the partial fills
+    ref_full, _, _ = O.decode_reference(q[2:3], kn[2:3], vn[2:3], kr[2:3], vr[2:3], head[2:3], pb, None,
+                                        O.OFFSETS_43, fill=fill[2:3])
+    assert_bf16_close(out[2:3], ref_full, "out vs full-sequence oracle")
+
+
+def test_decode_reproduces_training_forward_token_by_token():
+    """Feeding a sequence through the ring cache one token at a time gives the rows of the
+    full-sequence forward kernel."""
+    g = torch.Generator().manual_seed(6)
+    S, H, D, N = 2, 4, 32, 70
+    offsets = tuple(range(8)) + (16, 32, 48)
+    q, k, v = (bf16v(S, H, N, D, gen=g).to(DEV, torch.bfloat16) for _ in range(3))
+    pb = torch.randn(len(offsets), H, generator=g).to(DEV)
+    gain = (torch.rand(H, generator=g) + 0.5).to(DEV)
+    full = dwarf_b200.dsqg_attention(q, k, v, pb, gain, None, offsets).float()
+    cache = dwarf_b200.DSQGRingCache(1, S, H, D, offsets)
+    assert cache.R == 49
+    for t in range(N):
+        cache.advance()
+        o = cache.step(0, q[:, :, t].contiguous(), k[:, :, t].contiguous(), v[:, :, t].contiguous(), pb, gain)
+        assert (o.float() - full[:, :, t]).abs().max().item() <= 2e-2, t
+
+
+def test_benchmark_shape_runs_and_matches_on_a_sample():
+    cfg = synth.DecodeConfig()
+    x = synth.make_decode_inputs(cfg, device="cpu", layers=1)
+    to = lambda t: t.to(DEV)
+    kr, vr = to(x["k_ring"][0]), to(x["v_ring"][0])
+    out = dwarf_b200.dsqg_decode_step(to(x["q"][0]), to(x["k_new"][0]), to(x["v_new"][0]), kr, vr, to(x["head"]),
+                                      to(x["pos_bias"]), to(x["head_gain"]), None, cfg.offsets)
+    sl = slice(0, 16)
+    f = lambda t: t[0][sl].float()
+    ref, kref, _ = O.decode_reference_direct(f(x["q"]), f(x["k_new"]), f(x["v_new"]), f(x["k_ring"]), f(x["v_ring"]),
+                                             x["head"][sl], x["pos_bias"], x["head_gain"], cfg.offsets)
+    assert_bf16_close(out[sl].float().cpu(), ref, "out")
+    assert torch.equal(kr[sl].float().cpu(), kref)

@@ -1,0 +1,302 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI, against the CPU oracles
+and the committed golden vectors of the reference.  Run with `pytest -m gpu` on a B200."""
+import ctypes
+
+import pytest
+import torch
+
+import dwarf_b200
+from dwarf_b200 import _lib, synth
+from oracle import dsqg_oracle as O
+from tests.gpu_util import (BF16_ABS_TOL, FP32_REL_TOL, assert_bf16_close, assert_param_grad_close,
+                            cuda_fwd_bwd, oracle_fwd_bwd, rel_inf)
+from tests.helpers import GOLDEN_FN_CASES, GOLDEN_MODULE_CASES, load_case
+
+pytestmark = pytest.mark.gpu
+
+
+def bf16_valued(*shape, scale=1.0, gen=None):
+    return (torch.randn(*shape, generator=gen) * scale).to(torch.bfloat16).float()
+
+
+# ------------------------------------------------------------------ golden vectors
+@pytest.mark.parametrize("name", GOLDEN_FN_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_golden_function_cases(golden, name, dtype):
+    c = load_case(golden, name)
+    if dtype == torch.bfloat16 and not c["bf16"]:
+        pytest.skip("fp32-valued inputs are not representable in bf16")
+    r = cuda_fwd_bwd(c["q"], c["k"], c["v"], c["pos_bias"], c["dout"], c.get("scale_embed"), None,
+                     c["offsets"], dtype)
+    names = ["out", "dq", "dk", "dv"]
+    if dtype == torch.float32:
+        for nm in names:
+            assert rel_inf(r[nm], c[nm]) < FP32_REL_TOL, (nm, rel_inf(r[nm], c[nm]))
+        assert_param_grad_close(r["dpb"], c["dpb"], "dpb", 5e-5)
+        if "dse" in c: assert_param_grad_close(r["dse"], c["dse"], "dse", 5e-5)
+    else:
+        for nm in names:
+            assert_bf16_close(r[nm], c[nm], nm)
+        assert_param_grad_close(r["dpb"], c["dpb"], "dpb", 1e-2)
+        if "dse" in c: assert_param_grad_close(r["dse"], c["dse"], "dse", 1e-2)
+
+
+@pytest.mark.parametrize("name", GOLDEN_MODULE_CASES)
+def test_golden_other_offset_sets_fp32(golden, name):
+    c = load_case(golden, name)
+    r = cuda_fwd_bwd(c["q"], c["k"], c["v"], c["pos_bias"], offsets=c["offsets"], dtype=torch.float32)
+    assert rel_inf(r["out"], c["out"]) < FP32_REL_TOL
+
+
+# ------------------------------------------------------------------ seeded shapes vs oracle
+# the reference's own self-test shapes (kernels/dsqg_attention_v2.py:508-513), trimmed in B
+REF_SHAPES = [(1, 8, 64, 32), (2, 8, 512, 32), (2, 8, 2047, 32), (1, 4, 2047, 80), (2, 3, 300, 64),
+              (1, 2, 1700, 128), (1, 1, 1, 32), (1, 2, 33, 16)]
+
+
+@pytest.mark.parametrize("shape", REF_SHAPES)
+@pytest.mark.parametrize("offsets", [O.OFFSETS_44, O.OFFSETS_43], ids=["J44", "J43"])
+def test_bf16_forward_backward_vs_oracle(shape, offsets):
+    B, H, N, D = shape
+    g = torch.Generator().manual_seed(42 + N + D)
+    q, k, v = (bf16_valued(B, H, N, D, scale=0.5, gen=g) for _ in range(3))
+    dout = bf16_valued(B, H, N, D, gen=g)
+    pb = synth.log_linear_pos_bias(offsets, H) + torch.randn(len(offsets), H, generator=g) * 0.05
+    gain = torch.rand(H, generator=g) * 0.4 + 0.8
+    ref = oracle_fwd_bwd(q, k, v, pb, dout, None, gain, offsets)
+    r = cuda_fwd_bwd(q, k, v, pb, dout, None, gain, offsets, torch.bfloat16)
+    for nm in ("out", "dq", "dk", "dv"):
+        assert_bf16_close(r[nm], ref[nm], nm)
+    assert_param_grad_close(r["dpb"], ref["dpb"], "dpb", 1e-2)
+    assert_param_grad_close(r["dgain"], ref["dgain"], "dgain", 1e-2)
+
+
+@pytest.mark.parametrize("shape", [(1, 4, 64, 32), (2, 2, 1600, 32), (1, 3, 200, 64), (1, 2, 100, 80)])
+def test_bf16_scale_embed_and_gain_vs_oracle(shape):
+    B, H, N, D = shape
+    g = torch.Generator().manual_seed(7 + N)
+    q, k, v = (bf16_valued(B, H, N, D, scale=0.5, gen=g) for _ in range(3))
+    dout = bf16_valued(B, H, N, D, gen=g)
+    pb = torch.randn(44, H, generator=g) * 0.5
+    se = torch.randn(44, D, generator=g) * 0.05
+    gain = torch.rand(H, generator=g) + 0.5
+    ref = oracle_fwd_bwd(q, k, v, pb, dout, se, gain, O.OFFSETS_44)
+    r = cuda_fwd_bwd(q, k, v, pb, dout, se, gain, O.OFFSETS_44, torch.bfloat16)
+    for nm in ("out", "dq", "dk", "dv"):
+        assert_bf16_close(r[nm], ref[nm], nm)
+    for nm in ("dpb", "dse", "dgain"):
+        assert_param_grad_close(r[nm], ref[nm], nm, 1e-2)
+
+
+@pytest.mark.parametrize("shape", [(1, 8, 64, 32), (2, 4, 777, 32), (1, 2, 1600, 64), (1, 1, 90, 80)])
+def test_fp32_forward_backward_vs_oracle_1e5(shape):
+    B, H, N, D = shape
+    g = torch.Generator().manual_seed(11 + N)
+    q, k, v, dout = (torch.randn(B, H, N, D, generator=g) for _ in range(4))
+    pb = synth.log_linear_pos_bias(O.OFFSETS_43, H)
+    se = torch.randn(43, D, generator=g) * 0.05
+    gain = torch.rand(H, generator=g) + 0.5
+    ref = oracle_fwd_bwd(q, k, v, pb, dout, se, gain, O.OFFSETS_43)
+    r = cuda_fwd_bwd(q, k, v, pb, dout, se, gain, O.OFFSETS_43, torch.float32)
+    for nm in ("out", "dq", "dk", "dv"):
+        assert rel_inf(r[nm], ref[nm]) < FP32_REL_TOL, (nm, rel_inf(r[nm], ref[nm]))
+    for nm in ("dpb", "dse", "dgain"):
+        assert_param_grad_close(r[nm], ref[nm], nm, 5e-5)
+
+
+def test_config0_fp32_forward_gate():
+    """Benchmark configuration 0 (B2 H8 N2048 D32 fp32, 43 offsets) against the PyTorch
+    restatement of the reference: <= 1e-5 relative."""
+    cfg = synth.OP_CONFIGS["cfg0"]
+    x = synth.make_op_inputs(cfg, with_dout=False)
+    ref = O.dsqg_reference_chunked(x["q"], x["k"], x["v"], x["pos_bias"], None, None, cfg.offsets, chunk=1)
+    r = cuda_fwd_bwd(x["q"], x["k"], x["v"], x["pos_bias"], offsets=cfg.offsets, dtype=torch.float32)
+    assert rel_inf(r["out"], ref) < FP32_REL_TOL
+
+
+# ------------------------------------------------------------------ identities and edge cases
+def test_v3_with_zero_scale_embed_equals_v2():
+    # kernels/dsqg_attention_v3.py:612-628
+    torch.manual_seed(7)
+    dev = "cuda:0"
+    q, k, v = (torch.randn(2, 8, 128, 32, device=dev, dtype=torch.bfloat16) * 0.1 for _ in range(3))
+    pb = torch.randn(44, 8, device=dev) * 0.5
+    a = dwarf_b200.dsqg_attention_v2(q, k, v, pb)
+    b = dwarf_b200.dsqg_attention_v3(q, k, v, pb, torch.zeros(44, 32, device=dev))
+    assert (a.float() - b.float()).abs().max().item() < 1e-3
+
+
+def test_softmax_weights_sum_to_one_and_gain_scales_output():
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(3)
+    B, H, N, D = 2, 8, 2048, 32
+    q, k = (bf16_valued(B, H, N, D, scale=0.5, gen=g).to(dev, torch.bfloat16) for _ in range(2))
+    v = torch.ones(B, H, N, D, device=dev, dtype=torch.bfloat16)
+    pb = synth.log_linear_pos_bias(O.OFFSETS_43, H).to(dev)
+    gain = torch.tensor([0.5, 1.0, 2.0, 4.0, 0.25, 1.0, 1.0, 8.0], device=dev)
+    out = dwarf_b200.dsqg_attention(q, k, v, pb, gain, None, O.OFFSETS_43).float()
+    assert (out - gain.view(1, H, 1, 1)).abs().max().item() <= 2e-2 * 8
+
+
+def test_offset_set_without_zero_gives_zero_rows_and_finite_grads():
+    dev = "cuda:0"
+    offsets = (1, 2, 3, 8)
+    g = torch.Generator().manual_seed(5)
+    B, H, N, D = 1, 2, 40, 32
+    q, k, v = (bf16_valued(B, H, N, D, gen=g) for _ in range(3))
+    dout = bf16_valued(B, H, N, D, gen=g)
+    pb = torch.randn(4, H, generator=g)
+    ref = oracle_fwd_bwd(q, k, v, pb, dout, None, None, offsets)
+    for dtype in (torch.bfloat16, torch.float32):
+        r = cuda_fwd_bwd(q, k, v, pb, dout, None, None, offsets, dtype)
+        assert torch.all(r["out"][:, :, 0] == 0)
+        for nm in ("out", "dq", "dk", "dv"):
+            assert torch.isfinite(r[nm]).all()
+            assert_bf16_close(r[nm], ref[nm], nm)
+    out, lse = dwarf_b200.dsqg_forward_lse(q.to(dev, torch.bfloat16), k.to(dev, torch.bfloat16),
+                                           v.to(dev, torch.bfloat16), pb.to(dev), offsets=offsets)
+    assert torch.all(lse[:, :, 0] == float("-inf")) and torch.isfinite(lse[:, :, 1:]).all()
+
+
+def test_lse_matches_oracle():
+    g = torch.Generator().manual_seed(8)
+    B, H, N, D = 1, 4, 1600, 32
+    q, k, v = (bf16_valued(B, H, N, D, scale=0.5, gen=g) for _ in range(3))
+    pb = torch.randn(44, H, generator=g) * 0.5
+    ref = oracle_fwd_bwd(q, k, v, pb, None, None, None, O.OFFSETS_44)
+    dev = "cuda:0"
+    for dtype, tol in ((torch.bfloat16, 2e-3), (torch.float32, 2e-5)):
+        _, lse = dwarf_b200.dsqg_forward_lse(q.to(dev, dtype), k.to(dev, dtype), v.to(dev, dtype),
+                                             pb.to(dev), offsets=O.OFFSETS_44)
+        assert (lse.cpu() - ref["lse"]).abs().max().item() < tol
+
+
+def test_causality_on_gpu():
+    # perturb position 10: rows < 10 must not change (train_2048_condM_layer_ablation.py:410-426)
+    dev = "cuda:0"
+    torch.manual_seed(1)
+    q, k, v = (torch.randn(1, 8, 64, 32, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    pb = torch.randn(44, 8, device=dev)
+    a = dwarf_b200.dsqg_attention_v2(q, k, v, pb)
+    k2, v2 = k.clone(), v.clone()
+    k2[:, :, 10] += 1; v2[:, :, 10] -= 1
+    b = dwarf_b200.dsqg_attention_v2(q, k2, v2, pb)
+    assert torch.equal(a[:, :, :10], b[:, :, :10]) and not torch.equal(a[:, :, 10:], b[:, :, 10:])
+
+
+def test_bitwise_determinism_and_no_unwritten_rows():
+    """No atomics anywhere: two runs are bit-identical.  Outputs are poison-filled before the
+    launch (direct C-ABI call) so that an unwritten row would show up as NaN."""
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(9)
+    B, H, N, D = 3, 8, 2047, 32
+    mk = lambda: bf16_valued(B, H, N, D, scale=0.5, gen=g).to(dev, torch.bfloat16)
+    q, k, v, dout = mk(), mk(), mk(), mk()
+    pb = (torch.randn(43, H, generator=g) * 0.5).to(dev)
+    se = (torch.randn(43, D, generator=g) * 0.05).to(dev)
+    gain = (torch.rand(H, generator=g) + 0.5).to(dev)
+    off, J = _lib.offsets_array(O.OFFSETS_43)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def run():
+        nan = float("nan")
+        out = torch.full_like(q, nan); lse = torch.full((B, H, N), nan, device=dev)
+        dq, dk, dv = (torch.full_like(q, nan) for _ in range(3))
+        dpb = torch.full((J, H), nan, device=dev); dse = torch.full((J, D), nan, device=dev)
+        dg = torch.full((H,), nan, device=dev)
+        nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, 1)
+        scratch = torch.full((nbytes // 4,), nan, device=dev)
+        _lib.check(lib.dsqg_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), se.data_ptr(),
+                                gain.data_ptr(), off, J, out.data_ptr(), lse.data_ptr(), B, H, N, D, 0, stream), "fwd")
+        _lib.check(lib.dsqg_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), se.data_ptr(),
+                                gain.data_ptr(), off, J, out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
+                                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dpb.data_ptr(), dse.data_ptr(),
+                                dg.data_ptr(), scratch.data_ptr(), nbytes, B, H, N, D, 0, stream), "bwd")
+        torch.cuda.synchronize()
+        return out, lse, dq, dk, dv, dpb, dse, dg
+
+    a, b = run(), run()
+    for x, y in zip(a, b):
+        assert torch.isfinite(x.float()).all()
+        assert torch.equal(x, y)
+
+
+def test_non_default_stream_and_checkpoint_and_autocast():
+    dev = torch.device("cuda", 0)
+    m = dwarf_b200.DSQGAttentionQW(256, 8, dropout=0.0).to(dev)
+    with torch.no_grad():
+        m.scale_embed.normal_(0, 0.05); m.if_gain.uniform_(0.8, 1.2)
+    x = torch.randn(2, 256, 256, device=dev, requires_grad=True)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        with torch.amp.autocast("cuda", dtype=torch.bfloat16):
+            y = torch.utils.checkpoint.checkpoint(m, x, use_reentrant=False)
+        y.float().sum().backward()
+    s.synchronize()
+    assert torch.isfinite(x.grad).all() and torch.isfinite(m.pos_bias.grad).all()
+    assert torch.isfinite(m.if_gain.grad).all() and m.scale_embed.grad.abs().sum() > 0
+    # fp16 autocast (the reference's default, train_2048_condU.py:582): computed in bf16, returned fp16
+    q = torch.randn(1, 8, 64, 32, device=dev, dtype=torch.float16)
+    out = dwarf_b200.dsqg_attention_v2(q, q, q, m.pos_bias.detach())
+    assert out.dtype == torch.float16
+
+
+def test_module_matches_reference_module_math():
+    """DSQGAttentionN_Fused on the GPU against the same module math evaluated with the oracle."""
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    m = dwarf_b200.DSQGAttentionN_Fused(64, 2, dropout=0.0, offsets=O.OFFSETS_43).eval()
+    x = torch.randn(1, 100, 64)
+    with torch.no_grad():
+        qkv = m.qkv_proj(x)
+        q, k, v = (t.view(1, 100, 2, 32).permute(0, 2, 1, 3).bfloat16().float() for t in qkv.split(64, -1))
+        o = O.dsqg_reference(q, k, v, m.pos_bias, None, None, O.OFFSETS_43)
+        ref = m.out_proj(o.permute(0, 2, 1, 3).reshape(1, 100, 64) * torch.sigmoid(m.gate_proj(x)))
+        got = m.to(dev)(x.to(dev)).cpu()
+    assert (got - ref).abs().max().item() < 2e-2
+
+
+def test_gpu_argument_errors_raise_with_status():
+    dev = torch.device("cuda", 0)
+    q = torch.zeros(1, 2, 16, 32, device=dev, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        dwarf_b200.dsqg_attention(q, q, q, torch.zeros(43, 2, device=dev))          # J mismatch
+    with pytest.raises(dwarf_b200.DSQGError) as e:
+        dwarf_b200.dsqg_attention(q, q, q, torch.zeros(3, 2, device=dev), offsets=(0, 2, 1))
+    assert e.value.status == -3
+    q12 = torch.zeros(1, 2, 16, 12, device=dev, dtype=torch.bfloat16)
+    with pytest.raises(dwarf_b200.DSQGError) as e:
+        dwarf_b200.dsqg_attention(q12, q12, q12, torch.zeros(44, 2, device=dev))
+    assert e.value.status == -2
+    # the context is still usable afterwards
+    out = dwarf_b200.dsqg_attention(q, q, q, torch.zeros(44, 2, device=dev))
+    assert torch.isfinite(out.float()).all()
+
+
+# ------------------------------------------------------------------ full benchmark sizes
+@pytest.mark.parametrize("cfg_name", ["cfg1", "cfg2", "cfg2_4k"])
+def test_full_size_configs_vs_c_oracle_on_batch_slices(cfg_name):
+    """Full benchmark shape on the GPU; the CPU oracle checks the first and last batch
+    entries (every (b,h) problem is independent, so a slice is a complete check of the rows
+    it covers), plus size-independent properties on everything."""
+    cfg = synth.OP_CONFIGS[cfg_name]
+    x = synth.make_op_inputs(cfg)
+    r = cuda_fwd_bwd(x["q"], x["k"], x["v"], x["pos_bias"], x["dout"], None, x["head_gain"],
+                     cfg.offsets, cfg.dtype)
+    for nm in ("out", "dq", "dk", "dv"):
+        assert torch.isfinite(r[nm]).all()
+    for b in (0, cfg.B - 1):
+        sl = slice(b, b + 1)
+        f = lambda t: t[sl].float()
+        ref = oracle_fwd_bwd(f(x["q"]), f(x["k"]), f(x["v"]), x["pos_bias"], f(x["dout"]), None,
+                             x["head_gain"], cfg.offsets)
+        for nm in ("out", "dq", "dk", "dv"):
+            assert_bf16_close(r[nm][sl], ref[nm], f"{nm}[b={b}]")
+    # row 0 of every (b,h) attends only to itself: out[0] = gain * v[0]
+    want = x["v"][:, :, 0].float() * x["head_gain"].view(1, cfg.H, 1)
+    assert (r["out"][:, :, 0] - want).abs().max().item() <= BF16_ABS_TOL
+    # sum_j dpos_bias[j,h] ~ 0: softmax gradients sum to zero over the taps of every row
+    # (up to the bf16 rounding of the saved output that enters delta = sum_d dout*out)
+    assert (r["dpb"].sum(0).abs() <= 5e-3 * r["dpb"].abs().sum(0) + 0.5).all()
