@@ -92,12 +92,10 @@ int dsqg_fwd(const void* q, const void* k, const void* v,
 
 size_t dsqg_bwd_scratch_bytes(int J, int B, int H, int N, int D, int has_scale_embed) {
     if (J < 1 || J > DSQG_MAX_TAPS || check_shape(B, H, N, D, DSQG_DTYPE_BF16)) return 0;
-    const BwdGeometry g = bwd_geometry(B, H, N, D);
-    size_t floats = (size_t)B * H * N                       // delta
-                  + (size_t)g.n_tiles * J                    // dpos_bias partials
-                  + (size_t)g.n_tiles                        // dhead_gain partials
-                  + (has_scale_embed ? (size_t)g.n_dse_blocks * J * D : 0);
-    return ((floats * sizeof(float) + 255) / 256) * 256 + 1024;   // room for 256-byte carving
+    // every kernel family tiles at kMinRowsPerBwdTile rows or coarser; scale_embed partials are
+    // only produced by the generic kernels (512-row tiles)
+    return bwd_scratch_need(kMinRowsPerBwdTile, J, B, H, N, D, false) +
+           (has_scale_embed ? bwd_scratch_need(512, J, B, H, N, D, true) : 0);
 }
 
 int dsqg_bwd(const void* q, const void* k, const void* v,
@@ -138,23 +136,13 @@ int dsqg_bwd_stages(const void* q, const void* k, const void* v,
     if (scratch_bytes < dsqg_bwd_scratch_bytes(J, B, H, N, D, scale_embed != nullptr))
         return DSQG_ERR_SCRATCH_TOO_SMALL;
 
-    const BwdGeometry g = bwd_geometry(B, H, N, D);
     BwdArgs a;
     a.q = q; a.k = k; a.v = v; a.pos_bias = pos_bias; a.scale_embed = scale_embed; a.head_gain = head_gain;
     a.out = out; a.lse = lse; a.dout = dout; a.dq = dq; a.dk = dk; a.dv = dv;
     a.dpos_bias = dpos_bias; a.dscale_embed = dscale_embed; a.dhead_gain = head_gain ? dhead_gain : nullptr;
-    auto carve = [](char*& p, size_t floats) {
-        float* r = reinterpret_cast<float*>(p);
-        p += ((floats * sizeof(float) + 255) / 256) * 256;
-        return r;
-    };
-    char* p = static_cast<char*>(scratch);
-    // carve() rounds every block up to 256 bytes; the size query reserves the slack.
-    a.delta = carve(p, (size_t)B * H * N);
-    a.dpb_part = carve(p, (size_t)g.n_tiles * J);
-    a.dg_part = carve(p, (size_t)g.n_tiles);
-    a.dse_part = scale_embed ? carve(p, (size_t)g.n_dse_blocks * J * D) : nullptr;
-    a.n_tiles = g.n_tiles; a.tiles_per_bh = g.tiles_per_bh; a.n_dse_blocks = g.n_dse_blocks;
+    a.scratch = scratch; a.scratch_bytes = scratch_bytes;
+    a.delta = a.dpb_part = a.dg_part = a.dse_part = nullptr;
+    a.n_tiles = a.tiles_per_bh = a.n_dse_blocks = 0;
     a.B = B; a.H = H; a.N = N; a.D = D;
     a.scale = 1.0f / sqrtf((float)D);
     cudaError_t e = launch_bwd(a, t, dtype, static_cast<cudaStream_t>(stream), stages);

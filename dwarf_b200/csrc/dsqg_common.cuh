@@ -38,11 +38,12 @@ struct BwdArgs {
     const void* out; const float* lse; const void* dout;
     void* dq; void* dk; void* dv;
     float* dpos_bias; float* dscale_embed; float* dhead_gain;
-    // scratch carve-up (all fp32)
+    void* scratch; size_t scratch_bytes;
+    // scratch carve-up (all fp32), filled in by carve_bwd_scratch() inside each launcher
     float* delta;      // [B*H*N]    sum_d dout*out per row
     float* dpb_part;   // [n_tiles, J]
     float* dg_part;    // [n_tiles]
-    float* dse_part;   // [n_dse_blocks, J, D]
+    float* dse_part;   // [n_tiles, J, D] (only with scale_embed)
     int n_tiles, tiles_per_bh, n_dse_blocks;
     int B, H, N, D;
     float scale;
@@ -66,9 +67,31 @@ cudaError_t launch_bwd_generic(const BwdArgs& a, const Taps& t, int dtype, cudaS
 cudaError_t launch_reduce_params(const BwdArgs& a, int J, cudaStream_t s);
 cudaError_t launch_decode(const DecodeArgs& a, const Taps& t, int dtype, cudaStream_t s);
 
-// Geometry of the generic backward's scratch, shared by the size query and the launcher.
-struct BwdGeometry { int rows_per_tile, tiles_per_bh, n_tiles, n_dse_blocks; };
-BwdGeometry bwd_geometry(int B, int H, int N, int D);
+cudaError_t launch_fwd_mma(const FwdArgs& a, const Taps& t, cudaStream_t s);
+cudaError_t launch_bwd_mma(const BwdArgs& a, const Taps& t, cudaStream_t s, int stages);
+bool mma_path_supported(int dtype, int D, const Taps& t, bool has_scale_embed);
+
+// Backward scratch layout: delta | dpos_bias partials | dhead_gain partials | dscale_embed
+// partials, each block rounded up to 256 bytes.  A "tile" is the set of rows whose partial
+// sums one thread block produces; kernels differ in rows_per_tile, so each launcher carves
+// for itself and the size query reserves room for the finest tiling in use.
+constexpr int kMinRowsPerBwdTile = 64;
+inline size_t round256(size_t bytes) { return (bytes + 255) / 256 * 256; }
+inline size_t bwd_scratch_need(int rows_per_tile, int J, int B, int H, int N, int D, bool has_se) {
+    const size_t tiles = (size_t)B * H * ((N + rows_per_tile - 1) / rows_per_tile);
+    return round256((size_t)B * H * N * 4) + round256(tiles * J * 4) + round256(tiles * 4) +
+           (has_se ? round256(tiles * J * D * 4) : 0);
+}
+inline void carve_bwd_scratch(BwdArgs& a, int rows_per_tile, int J, bool has_se) {
+    a.tiles_per_bh = (a.N + rows_per_tile - 1) / rows_per_tile;
+    a.n_tiles = a.B * a.H * a.tiles_per_bh;
+    a.n_dse_blocks = a.n_tiles;
+    char* p = static_cast<char*>(a.scratch);
+    a.delta = reinterpret_cast<float*>(p);    p += round256((size_t)a.B * a.H * a.N * 4);
+    a.dpb_part = reinterpret_cast<float*>(p); p += round256((size_t)a.n_tiles * J * 4);
+    a.dg_part = reinterpret_cast<float*>(p);  p += round256((size_t)a.n_tiles * 4);
+    a.dse_part = has_se ? reinterpret_cast<float*>(p) : nullptr;
+}
 
 // ---------------------------------------------------------------------------------
 // Device helpers: 8-element row slices in fp32 registers, from bf16 or fp32 storage.

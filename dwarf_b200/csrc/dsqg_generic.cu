@@ -280,52 +280,52 @@ bwd_dkdv_generic_kernel(const BwdArgs a, const Taps t) {
 
 }  // namespace
 
-// Fixed-order second stage of the parameter gradients (shared by every backward path):
-//   dpos_bias[j,h]  = sum_b sum_c dpb_part[((b*H+h)*tiles_per_bh + c), j]
-//   dhead_gain[h]   = sum_b sum_c dg_part[(b*H+h)*tiles_per_bh + c]
-//   dscale_embed    = sum_tiles dse_part[tile]
-__global__ void bwd_reduce_params_kernel(const BwdArgs a, const int J) {
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+// One block per output element; the partials are summed in a fixed order (per-thread strided
+// partial sums, then a fixed shared-memory tree), so the result is bitwise reproducible.
+constexpr int kReduceThreads = 128;
+__global__ void __launch_bounds__(kReduceThreads)
+bwd_reduce_params_kernel(const BwdArgs a, const int J) {
+    __shared__ float red[kReduceThreads];
+    const int idx = blockIdx.x;
     const int n_pb = J * a.H;
-    const int n_se = (a.dscale_embed && a.scale_embed) ? J * a.D : 0;
+    const int per_h = a.B * a.tiles_per_bh;          // partials per (.., h): b-major, then tile
+    float s = 0.f;
+    float* dst = nullptr;
     if (idx < n_pb) {
         const int j = idx / a.H, h = idx - j * a.H;
-        float s = 0.f;
-        for (int b = 0; b < a.B; ++b)
-            for (int c = 0; c < a.tiles_per_bh; ++c)
-                s += a.dpb_part[((size_t)(b * a.H + h) * a.tiles_per_bh + c) * J + j];
-        a.dpos_bias[idx] = s;
+        for (int i = threadIdx.x; i < per_h; i += kReduceThreads) {
+            const int b = i / a.tiles_per_bh, c = i - b * a.tiles_per_bh;
+            s += a.dpb_part[((size_t)(b * a.H + h) * a.tiles_per_bh + c) * J + j];
+        }
+        dst = a.dpos_bias + idx;
     } else if (idx < n_pb + a.H) {
         const int h = idx - n_pb;
         if (a.dhead_gain) {
-            float s = 0.f;
-            for (int b = 0; b < a.B; ++b)
-                for (int c = 0; c < a.tiles_per_bh; ++c)
-                    s += a.dg_part[(size_t)(b * a.H + h) * a.tiles_per_bh + c];
-            a.dhead_gain[h] = s;
+            for (int i = threadIdx.x; i < per_h; i += kReduceThreads) {
+                const int b = i / a.tiles_per_bh, c = i - b * a.tiles_per_bh;
+                s += a.dg_part[(size_t)(b * a.H + h) * a.tiles_per_bh + c];
+            }
+            dst = a.dhead_gain + h;
         }
-    } else if (idx < n_pb + a.H + n_se) {
+    } else if (a.dscale_embed && a.scale_embed) {
         const int e = idx - n_pb - a.H;
-        float s = 0.f;
-        for (int tl = 0; tl < a.n_dse_blocks; ++tl) s += a.dse_part[(size_t)tl * J * a.D + e];
-        a.dscale_embed[e] = s;
+        for (int tl = threadIdx.x; tl < a.n_dse_blocks; tl += kReduceThreads)
+            s += a.dse_part[(size_t)tl * J * a.D + e];
+        dst = a.dscale_embed + e;
     }
+    red[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = kReduceThreads / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && dst) *dst = red[0];
 }
 
 cudaError_t launch_reduce_params(const BwdArgs& a, int J, cudaStream_t s) {
-    const int total = J * a.H + a.H + J * a.D;
-    bwd_reduce_params_kernel<<<(total + 127) / 128, 128, 0, s>>>(a, J);
+    const int total = J * a.H + a.H + ((a.dscale_embed && a.scale_embed) ? J * a.D : 0);
+    bwd_reduce_params_kernel<<<total, kReduceThreads, 0, s>>>(a, J);
     return cudaGetLastError();
-}
-
-BwdGeometry bwd_geometry(int B, int H, int N, int D) {
-    (void)D;
-    BwdGeometry g;
-    g.rows_per_tile = kRowsPerBwdTile;
-    g.tiles_per_bh = (N + kRowsPerBwdTile - 1) / kRowsPerBwdTile;
-    g.n_tiles = B * H * g.tiles_per_bh;
-    g.n_dse_blocks = g.n_tiles;
-    return g;
 }
 
 namespace {
@@ -338,9 +338,10 @@ cudaError_t fwd_launch(const FwdArgs& a, const Taps& t, cudaStream_t s) {
 }
 
 template <typename T, int TPR>
-cudaError_t bwd_launch(const BwdArgs& a, const Taps& t, cudaStream_t s, int stages) {
+cudaError_t bwd_launch(BwdArgs a, const Taps& t, cudaStream_t s, int stages) {
     constexpr int RPB = kThreads / TPR;
     const bool has_se = a.scale_embed != nullptr;
+    carve_bwd_scratch(a, kRowsPerBwdTile, t.J, has_se);
     size_t smem = sizeof(float) * ((size_t)RPB * t.J + RPB + (has_se ? (size_t)RPB * a.D + (size_t)t.J * a.D : 0));
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(bwd_dq_generic_kernel<T, TPR>,

@@ -8,6 +8,9 @@ from oracle import dsqg_oracle as O
 
 BF16_ABS_TOL = 2e-2        # absolute tolerance for bf16 outputs and gradients (benchmark spec)
 BF16_ULP = 2.0 ** -8       # one bf16 rounding step relative to the value (output rounding)
+PARAM_REL_TOL_BF16 = 2e-2  # dpos_bias / dscale_embed / dhead_gain in the bf16 path: sums over all rows of
+                           # terms that carry delta = sum_d dout*out with the bf16-rounded saved output
+                           # (as in the reference kernels, kernels/dsqg_attention_v3.py:170-191)
 FP32_REL_TOL = 1e-5        # ||x-ref||_inf / ||ref||_inf for the fp32 instantiation
 
 
@@ -47,9 +50,12 @@ def assert_bf16_close(x, ref, name):
                                  f"(|ref|max {ref.abs().max().item():.4g}), {int(bad.sum())} elements out of tolerance")
 
 
-def assert_param_grad_close(x, ref, name, rel):
-    e = (x.double() - ref.double()).abs().max().item() / max(ref.double().abs().max().item(), 1e-30)
-    assert e < rel, f"{name}: rel-inf err {e:.3g} >= {rel}"
+def assert_param_grad_close(x, ref, name, rel, abs_floor=2e-3):
+    """max |x - ref| <= rel * max|ref| + abs_floor (the floor covers gradients that are exactly
+    zero in the reference, e.g. a single-tap softmax)."""
+    err = (x.double() - ref.double()).abs().max().item()
+    bound = rel * ref.double().abs().max().item() + abs_floor
+    assert err <= bound, f"{name}: max abs err {err:.3g} > {bound:.3g} (|ref|max {ref.abs().max().item():.3g})"
 
 
 def rel_inf(x, ref):

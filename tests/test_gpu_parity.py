@@ -8,7 +8,7 @@ import torch
 import dwarf_b200
 from dwarf_b200 import _lib, synth
 from oracle import dsqg_oracle as O
-from tests.gpu_util import (BF16_ABS_TOL, FP32_REL_TOL, assert_bf16_close, assert_param_grad_close,
+from tests.gpu_util import (BF16_ABS_TOL, FP32_REL_TOL, PARAM_REL_TOL_BF16, assert_bf16_close, assert_param_grad_close,
                             cuda_fwd_bwd, oracle_fwd_bwd, rel_inf)
 from tests.helpers import GOLDEN_FN_CASES, GOLDEN_MODULE_CASES, load_case
 
@@ -37,8 +37,8 @@ def test_golden_function_cases(golden, name, dtype):
     else:
         for nm in names:
             assert_bf16_close(r[nm], c[nm], nm)
-        assert_param_grad_close(r["dpb"], c["dpb"], "dpb", 1e-2)
-        if "dse" in c: assert_param_grad_close(r["dse"], c["dse"], "dse", 1e-2)
+        assert_param_grad_close(r["dpb"], c["dpb"], "dpb", PARAM_REL_TOL_BF16)
+        if "dse" in c: assert_param_grad_close(r["dse"], c["dse"], "dse", PARAM_REL_TOL_BF16)
 
 
 @pytest.mark.parametrize("name", GOLDEN_MODULE_CASES)
@@ -54,9 +54,21 @@ REF_SHAPES = [(1, 8, 64, 32), (2, 8, 512, 32), (2, 8, 2047, 32), (1, 4, 2047, 80
               (1, 2, 1700, 128), (1, 1, 1, 32), (1, 2, 33, 16)]
 
 
+@pytest.fixture(params=["auto", "generic"])
+def kernel_path(request):
+    """Runs a test once with the automatic kernel choice (tensor-core kernels where they apply)
+    and once with the generic CUDA-core kernels forced."""
+    lib = _lib.load()
+    lib.dsqg_set_kernel_path(1 if request.param == "generic" else 0)
+    yield request.param
+    lib.dsqg_set_kernel_path(0)
+
+
 @pytest.mark.parametrize("shape", REF_SHAPES)
-@pytest.mark.parametrize("offsets", [O.OFFSETS_44, O.OFFSETS_43], ids=["J44", "J43"])
-def test_bf16_forward_backward_vs_oracle(shape, offsets):
+@pytest.mark.parametrize("offsets", [O.OFFSETS_44, O.OFFSETS_43, O.OFFSETS_45,
+                                     tuple(range(41)) + (128, 384, 1536), tuple(range(2, 60)) + (64, 1000)],
+                         ids=["J44", "J43", "J45", "d41", "odd"])
+def test_bf16_forward_backward_vs_oracle(shape, offsets, kernel_path):
     B, H, N, D = shape
     g = torch.Generator().manual_seed(42 + N + D)
     q, k, v = (bf16_valued(B, H, N, D, scale=0.5, gen=g) for _ in range(3))
@@ -67,8 +79,8 @@ def test_bf16_forward_backward_vs_oracle(shape, offsets):
     r = cuda_fwd_bwd(q, k, v, pb, dout, None, gain, offsets, torch.bfloat16)
     for nm in ("out", "dq", "dk", "dv"):
         assert_bf16_close(r[nm], ref[nm], nm)
-    assert_param_grad_close(r["dpb"], ref["dpb"], "dpb", 1e-2)
-    assert_param_grad_close(r["dgain"], ref["dgain"], "dgain", 1e-2)
+    assert_param_grad_close(r["dpb"], ref["dpb"], "dpb", PARAM_REL_TOL_BF16)
+    assert_param_grad_close(r["dgain"], ref["dgain"], "dgain", PARAM_REL_TOL_BF16)
 
 
 @pytest.mark.parametrize("shape", [(1, 4, 64, 32), (2, 2, 1600, 32), (1, 3, 200, 64), (1, 2, 100, 80)])
@@ -85,7 +97,7 @@ def test_bf16_scale_embed_and_gain_vs_oracle(shape):
     for nm in ("out", "dq", "dk", "dv"):
         assert_bf16_close(r[nm], ref[nm], nm)
     for nm in ("dpb", "dse", "dgain"):
-        assert_param_grad_close(r[nm], ref[nm], nm, 1e-2)
+        assert_param_grad_close(r[nm], ref[nm], nm, PARAM_REL_TOL_BF16)
 
 
 @pytest.mark.parametrize("shape", [(1, 8, 64, 32), (2, 4, 777, 32), (1, 2, 1600, 64), (1, 1, 90, 80)])
