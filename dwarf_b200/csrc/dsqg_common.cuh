@@ -70,6 +70,9 @@ cudaError_t launch_decode(const DecodeArgs& a, const Taps& t, int dtype, cudaStr
 cudaError_t launch_fwd_mma(const FwdArgs& a, const Taps& t, cudaStream_t s);
 cudaError_t launch_bwd_mma(const BwdArgs& a, const Taps& t, cudaStream_t s, int stages);
 bool mma_path_supported(int dtype, int D, const Taps& t, bool has_scale_embed);
+cudaError_t launch_fwd_tma(const FwdArgs& a, const Taps& t, cudaStream_t s);
+bool tma_fwd_supported(int dtype, int D, int N, const Taps& t, bool has_scale_embed);
+cudaError_t read_device_error_fwd_tma(int* value, bool reset);
 
 // Backward scratch layout: delta | dpos_bias partials | dhead_gain partials | dscale_embed
 // partials, each block rounded up to 256 bytes.  A "tile" is the set of rows whose partial

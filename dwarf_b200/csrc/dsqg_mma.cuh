@@ -25,6 +25,7 @@ namespace dsqg {
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kNeg = -1.0e30f;   // finite "minus infinity": masked scores
+constexpr float kMinM = -1.0e29f;  // floor of the running row maximum: exp2(kNeg - kMinM) == 0
 
 template <int D> struct RowFrag { uint32_t r[D / 8]; };   // D/32 chunks x 4 registers
 
@@ -50,6 +51,24 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// d = A.B with a zero accumulator input (no register initialisation needed)
+__device__ __forceinline__ void mma16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// c = A.B (overwrites c), contraction over d as in mma_rows
+template <int D>
+__device__ __forceinline__ void mma_rows_z(float (&c)[4], const RowFrag<D>& a_lo, const RowFrag<D>& a_hi,
+                                           const RowFrag<D>& b) {
+    mma16816_z(c, a_lo.r[0], a_hi.r[0], a_lo.r[1], a_hi.r[1], b.r[0], b.r[1]);
+#pragma unroll
+    for (int kk = 1; kk < D / 16; ++kk)
+        mma16816(c, a_lo.r[2 * kk], a_hi.r[2 * kk], a_lo.r[2 * kk + 1], a_hi.r[2 * kk + 1], b.r[2 * kk], b.r[2 * kk + 1]);
 }
 
 // C[16 x 8] += A(rows g / g+8 = a_lo / a_hi)[16 x D] . B(row g = b)[8 x D]^T   (contracts over d)

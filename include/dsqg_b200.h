@@ -58,8 +58,16 @@ const char* dsqg_last_cuda_error(void);
 int dsqg_version(void);
 
 /* Testing knob with no counterpart in the reference: 0 = choose kernels automatically
- * (default), 1 = always use the generic CUDA-core kernels.  Process-wide. */
+ * (default), 1 = always use the generic CUDA-core kernels, 2 = tensor-core kernels but not
+ * their persistent TMA variants.  Process-wide. */
 int dsqg_set_kernel_path(int path);
+
+/* Device-side error word of the current device (no counterpart in the reference).  The
+ * persistent kernels bound every wait on a shared-memory barrier; a wait that runs out
+ * records (kernel id << 8 | wait site) here and the kernel returns with unspecified output
+ * instead of hanging.  0 = no error, -1 = the word could not be read.  Synchronises the
+ * device.  reset != 0 clears the word after reading. */
+int dsqg_device_error(int reset);
 
 /* Forward.
  * Replaces: _DSQGFn.forward / _DSQGFnV3.forward + the _fwd/_fwd_v3 kernels
