@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libdsqg_b200.so")
 DSQG_DTYPE_BF16 = 0
 DSQG_DTYPE_F32 = 1
 DSQG_MAX_TAPS = 128
+DSQG_STATIC_SCRATCH_BYTES = 8 << 20
 
 # Every symbol include/dsqg_b200.h declares, with its ctypes signature.
 _SIGNATURES = {
@@ -31,6 +32,8 @@ _SIGNATURES = {
     "dsqg_bwd_stages": (c_int, [c_void_p] * 3 + [c_void_p] * 3 + [POINTER(c_int32), c_int] + [c_void_p] * 3
                         + [c_void_p] * 3 + [c_void_p] * 3 + [c_void_p, c_size_t] + [c_int] * 5
                         + [c_void_p, c_int]),
+    "dsqg_bwd_static": (c_int, [c_void_p] * 3 + [c_void_p] * 3 + [POINTER(c_int32), c_int] + [c_void_p] * 3
+                        + [c_void_p] * 3 + [c_void_p] * 3 + [c_int] * 5 + [c_void_p]),
     "dsqg_decode": (c_int, [c_void_p] * 3 + [c_void_p] * 2 + [c_void_p] * 2 + [c_void_p] * 3
                     + [POINTER(c_int32), c_int, c_int] + [c_void_p] + [c_int] * 4 + [c_void_p]),
 }

@@ -60,6 +60,9 @@ const char* dsqg_status_str(int status) {
         case DSQG_ERR_SCRATCH_TOO_SMALL: return "scratch buffer smaller than dsqg_bwd_scratch_bytes()";
         case DSQG_ERR_CUDA: return "CUDA error (see dsqg_last_cuda_error)";
         case DSQG_ERR_UNSUPPORTED: return "no kernel for this configuration";
+        case DSQG_ERR_STATIC_SCRATCH_EXCEEDED:
+            return "dsqg_bwd_static: this problem needs more scratch than the built-in DSQG_STATIC_SCRATCH_BYTES; "
+                   "use dsqg_bwd with a caller-allocated buffer";
         default: return "unknown status";
     }
 }

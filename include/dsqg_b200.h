@@ -43,7 +43,8 @@ typedef enum {
     DSQG_ERR_MISALIGNED = -5,     /* a tensor pointer is not 16-byte aligned */
     DSQG_ERR_SCRATCH_TOO_SMALL = -6,
     DSQG_ERR_CUDA = -7,           /* a CUDA runtime/driver call failed (see dsqg_last_cuda_error) */
-    DSQG_ERR_UNSUPPORTED = -8     /* valid request that this build has no kernel for */
+    DSQG_ERR_UNSUPPORTED = -8,    /* valid request that this build has no kernel for */
+    DSQG_ERR_STATIC_SCRATCH_EXCEEDED = -9  /* dsqg_bwd_static: problem needs more than DSQG_STATIC_SCRATCH_BYTES */
 } dsqg_status;
 
 enum { DSQG_DTYPE_BF16 = 0, DSQG_DTYPE_F32 = 1 };
@@ -104,6 +105,29 @@ int dsqg_bwd(const void* q, const void* k, const void* v,
              float* dpos_bias, float* dscale_embed, float* dhead_gain,
              void* scratch, size_t scratch_bytes,
              int B, int H, int N, int D, int dtype, void* stream);
+
+/* Backward without a caller-supplied scratch buffer.  No counterpart in the reference (its
+ * extensions allocate through PyTorch); it exists for callers that cannot allocate device
+ * memory at all -- e.g. a server that hands all of its device memory to a fixed arena at
+ * start-up, or a plugin host that lends the plugin nothing but the tensors of the call.
+ * Same arguments and results as dsqg_bwd minus scratch/scratch_bytes; the scratch is a
+ * DSQG_STATIC_SCRATCH_BYTES array built into the library (each GPU that loads the library
+ * holds those bytes until the process exits).  The call allocates and frees nothing.
+ *   - Problems with dsqg_bwd_scratch_bytes(...) > DSQG_STATIC_SCRATCH_BYTES are refused with
+ *     DSQG_ERR_STATIC_SCRATCH_EXCEEDED before anything is launched.
+ *   - The first call on each device looks up that device's copy of the array (the device must
+ *     be current, as for every entry point); make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps whatever the last call left; the
+ *     kernels overwrite every word they later read, so nothing has to be cleared.  Two calls
+ *     that may run on the GPU at the same time (different streams) race on it: serialise them. */
+#define DSQG_STATIC_SCRATCH_BYTES (8u << 20)
+int dsqg_bwd_static(const void* q, const void* k, const void* v,
+                    const float* pos_bias, const float* scale_embed, const float* head_gain,
+                    const int32_t* offsets, int J,
+                    const void* out, const float* lse, const void* dout,
+                    void* dq, void* dk, void* dv,
+                    float* dpos_bias, float* dscale_embed, float* dhead_gain,
+                    int B, int H, int N, int D, int dtype, void* stream);
 
 /* dsqg_bwd restricted to some of its kernels: a profiling aid with no counterpart in the
  * reference.  `stages` is a bit mask: DSQG_BWD_STAGE_DQ (dQ, delta and the parameter-gradient

@@ -34,7 +34,7 @@ def test_header_symbols_are_exported(lib):
 
 def test_status_strings(lib):
     assert lib.dsqg_status_str(0) == b"ok"
-    for code in range(-8, 0):
+    for code in range(-9, 0):
         assert len(lib.dsqg_status_str(code)) > 3
     assert lib.dsqg_status_str(-99) == b"unknown status"
     assert lib.dsqg_version() >= 100
