@@ -97,8 +97,10 @@ size_t dsqg_bwd_scratch_bytes(int J, int B, int H, int N, int D, int has_scale_e
     if (J < 1 || J > DSQG_MAX_TAPS || check_shape(B, H, N, D, DSQG_DTYPE_BF16)) return 0;
     // every kernel family tiles at kMinRowsPerBwdTile rows or coarser; scale_embed partials are
     // only produced by the generic kernels (512-row tiles)
-    return bwd_scratch_need(kMinRowsPerBwdTile, J, B, H, N, D, false) +
-           (has_scale_embed ? bwd_scratch_need(512, J, B, H, N, D, true) : 0);
+    size_t need = bwd_scratch_need(kMinRowsPerBwdTile, J, B, H, N, D, false);
+    const size_t tma = bwd_scratch_need_tma(J, B, H, N);      // persistent kernels: partials per (CTA, sequence, warp)
+    if (tma > need) need = tma;
+    return need + (has_scale_embed ? bwd_scratch_need(512, J, B, H, N, D, true) : 0);
 }
 
 int dsqg_bwd(const void* q, const void* k, const void* v,

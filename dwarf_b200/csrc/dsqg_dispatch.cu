@@ -7,18 +7,22 @@
 namespace dsqg {
 
 // 0 = automatic, 1 = always the generic kernels, 2 = tensor-core kernels without the
-// persistent TMA variants
+// persistent TMA variants, 3 = persistent TMA variants wherever they exist (the backward ones
+// are not chosen automatically: on B200 they measure slower than the plain tensor-core
+// backward, which keeps more warps resident per SM)
 static std::atomic<int> g_path{0};
 
 cudaError_t launch_fwd(const FwdArgs& a, const Taps& t, int dtype, cudaStream_t s) {
     const int path = g_path.load();
-    if (path == 0 && tma_fwd_supported(dtype, a.D, a.N, t, a.scale_embed != nullptr)) return launch_fwd_tma(a, t, s);
+    if ((path == 0 || path == 3) && tma_fwd_supported(dtype, a.D, a.N, t, a.scale_embed != nullptr)) return launch_fwd_tma(a, t, s);
     if (path != 1 && mma_path_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_mma(a, t, s);
     return launch_fwd_generic(a, t, dtype, s);
 }
 
 cudaError_t launch_bwd(const BwdArgs& a, const Taps& t, int dtype, cudaStream_t s, int stages) {
-    if (g_path.load() != 1 && mma_path_supported(dtype, a.D, t, a.scale_embed != nullptr))
+    const int path = g_path.load();
+    if (path == 3 && tma_bwd_supported(dtype, a.D, a.N, t, a.scale_embed != nullptr)) return launch_bwd_tma(a, t, s, stages);
+    if (path != 1 && mma_path_supported(dtype, a.D, t, a.scale_embed != nullptr))
         return launch_bwd_mma(a, t, s, stages);
     return launch_bwd_generic(a, t, dtype, s, stages);
 }
@@ -26,13 +30,15 @@ cudaError_t launch_bwd(const BwdArgs& a, const Taps& t, int dtype, cudaStream_t 
 }  // namespace dsqg
 
 extern "C" int dsqg_set_kernel_path(int path) {
-    if (path < 0 || path > 2) return DSQG_ERR_UNSUPPORTED;
+    if (path < 0 || path > 3) return DSQG_ERR_UNSUPPORTED;
     dsqg::g_path.store(path);
     return DSQG_OK;
 }
 
 extern "C" int dsqg_device_error(int reset) {
     int v = 0;
+    int w = 0;
     if (dsqg::read_device_error_fwd_tma(&v, reset != 0) != cudaSuccess) return -1;
-    return v;
+    if (dsqg::read_device_error_bwd_tma(&w, reset != 0) != cudaSuccess) return -1;
+    return v ? v : w;
 }

@@ -512,7 +512,7 @@ cudaError_t fwd_launch_tma(const FwdArgs& a, const Taps& t, cudaStream_t stream)
 template <int D, int WB>
 cudaError_t fwd_launch_tma_w(const FwdArgs& a, const Taps& t, cudaStream_t stream) {
     const char* w = getenv("DSQG_FWD_WARPS");
-    const int W = w ? atoi(w) : 15;
+    const int W = w ? atoi(w) : (D == 32 ? 15 : 8);     // measured best on B200
     // at least 8 consumer warps: the 8 tiles of a block must sit on 8 different warps, or a warp
     // would wait for a stage that only its own later tile can release
     if (W == 8) return fwd_launch_tma<D, WB, 8>(a, t, stream);

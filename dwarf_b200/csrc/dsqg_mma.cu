@@ -64,8 +64,7 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
         const int kr = kb0 + 8 * nt + g;
         RowFrag<D> kf;
         load_row(kf, kp + (size_t)kr * D, tig, kr >= 0 && kr < N);
-        S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
-        mma_rows(S[nt], qa, qb, kf);
+        mma_rows_z(S[nt], qa, qb, kf);
     }
     float m_lo = kNeg, m_hi = kNeg;
 #pragma unroll
@@ -94,9 +93,9 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
                 RowFrag<D> kf0, kf1;
                 load_row(kf0, kp + (size_t)kr0 * D, tig, v0);
                 load_row(kf1, kp + (size_t)kr1 * D, tig, v1);
-                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_rows(s0, qa, qb, kf0);
-                mma_rows(s1, qa, qb, kf1);
+                float s0[4], s1[4];
+                mma_rows_z(s0, qa, qb, kf0);
+                mma_rows_z(s1, qa, qb, kf1);
                 const float pbv = pb2_s[nd + si];
                 const float d0 = (g & 1) ? s0[1] : s0[0], d1 = (g & 1) ? s1[3] : s1[2];
                 sp_lo[si] = v0 ? fmaf(d0, c2, pbv) : kNeg;
@@ -164,8 +163,12 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
 // Also writes delta[n] = sum_d dout*out for the dK/dV kernel and the per-CTA partial sums of
 // dpos_bias (through a [J][rows] staging tile in shared memory, summed in a fixed order) and
 // of dhead_gain.
+// Resident CTAs per SM the backward kernels are compiled for (measured best on B200: the
+// register budget that follows trades spills against warps in flight).
+template <int D> struct BwdOccupancy { static constexpr int dq = D == 32 ? 6 : 4, dkdv = D == 32 ? 5 : 3; };
+
 template <int D, int WB>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, BwdOccupancy<D>::dq)
 bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
     constexpr int NT = (WB + 16) / 8;
     extern __shared__ float stage[];                   // [J][kStagePitch] ds values, then [128] dgain terms
@@ -230,9 +233,9 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
                 RowFrag<D> vf;
                 load_row(kf[hf], kp + (size_t)kr * D, tig, kv);
                 load_row(vf, vp + (size_t)kr * D, tig, kv);
-                float s[4] = {0.f, 0.f, 0.f, 0.f}, dp[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_rows(s, qa, qb, kf[hf]);
-                mma_rows(dp, da, db, vf);
+                float s[4], dp[4];
+                mma_rows_z(s, qa, qb, kf[hf]);
+                mma_rows_z(dp, da, db, vf);
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const int i = g + 8 * (r >> 1), cc = 8 * nt + 2 * tig + (r & 1);
@@ -262,10 +265,9 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
             load_row(kf1, kp + (size_t)kr1 * D, tig, v1);
             load_row(vf0, vp + (size_t)kr0 * D, tig, v0);
             load_row(vf1, vp + (size_t)kr1 * D, tig, v1);
-            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-            float e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_rows(s0, qa, qb, kf0); mma_rows(s1, qa, qb, kf1);
-            mma_rows(e0, da, db, vf0); mma_rows(e1, da, db, vf1);
+            float s0[4], s1[4], e0[4], e1[4];
+            mma_rows_z(s0, qa, qb, kf0); mma_rows_z(s1, qa, qb, kf1);
+            mma_rows_z(e0, da, db, vf0); mma_rows_z(e1, da, db, vf1);
             const float pbv = pb2_s[nd + si];
             const float sd0 = (g & 1) ? s0[1] : s0[0], sd1 = (g & 1) ? s1[3] : s1[2];
             const float dp0 = (g & 1) ? e0[1] : e0[0], dp1 = (g & 1) ? e1[3] : e1[2];
@@ -306,7 +308,7 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
 // query rows [m0, m0+16+WB) for the dense window and the diagonal of the tile at m0+delta for
 // every sparse tap.  Key rows are owned by exactly one warp: no atomics.
 template <int D, int WB>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, BwdOccupancy<D>::dkdv)
 bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t) {
     constexpr int NT = (WB + 16) / 8;
     __shared__ float pb2_s[DSQG_MAX_TAPS];
@@ -353,9 +355,9 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t) {
             const int qr = m0 + 8 * nt + g;
             load_row(qf[hf], qp + (size_t)qr * D, tig, qr < N);
             load_row(df[hf], dop + (size_t)qr * D, tig, qr < N);
-            float s[4] = {0.f, 0.f, 0.f, 0.f}, dp[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_rows(s, ka, kb, qf[hf]);
-            mma_rows(dp, va, vb, df[hf]);
+            float s[4], dp[4];
+            mma_rows_z(s, ka, kb, qf[hf]);
+            mma_rows_z(dp, va, vb, df[hf]);
             // this thread's two query columns of the n-tile
             const int qc = m0 + 8 * nt + 2 * tig;
             float l2c[2], dlc[2];
@@ -395,10 +397,9 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t) {
         load_row(qf1, qp + (size_t)qr1 * D, tig, v1);
         load_row(df0, dop + (size_t)qr0 * D, tig, v0);
         load_row(df1, dop + (size_t)qr1 * D, tig, v1);
-        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-        float e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f};
-        mma_rows(s0, ka, kb, qf0); mma_rows(s1, ka, kb, qf1);
-        mma_rows(e0, va, vb, df0); mma_rows(e1, va, vb, df1);
+        float s0[4], s1[4], e0[4], e1[4];
+        mma_rows_z(s0, ka, kb, qf0); mma_rows_z(s1, ka, kb, qf1);
+        mma_rows_z(e0, va, vb, df0); mma_rows_z(e1, va, vb, df1);
         const float pbv = pb2_s[nd + si];
         const float sd0 = (g & 1) ? s0[1] : s0[0], sd1 = (g & 1) ? s1[3] : s1[2];
         const float dp0 = (g & 1) ? e0[1] : e0[0], dp1 = (g & 1) ? e1[3] : e1[2];

@@ -60,7 +60,8 @@ int dsqg_version(void);
 
 /* Testing knob with no counterpart in the reference: 0 = choose kernels automatically
  * (default), 1 = always use the generic CUDA-core kernels, 2 = tensor-core kernels but not
- * their persistent TMA variants.  Process-wide. */
+ * their persistent TMA variants, 3 = persistent TMA variants wherever one exists (including
+ * the backward ones, which the automatic choice does not use).  Process-wide. */
 int dsqg_set_kernel_path(int path);
 
 /* Device-side error word of the current device (no counterpart in the reference).  The

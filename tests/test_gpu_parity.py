@@ -54,13 +54,13 @@ REF_SHAPES = [(1, 8, 64, 32), (2, 8, 512, 32), (2, 8, 2047, 32), (1, 4, 2047, 80
               (1, 2, 1700, 128), (1, 1, 1, 32), (1, 2, 33, 16)]
 
 
-@pytest.fixture(params=["auto", "generic", "mma"])
+@pytest.fixture(params=["auto", "generic", "mma", "tma"])
 def kernel_path(request):
     """Runs a test with the automatic kernel choice (persistent TMA / tensor-core kernels where
-    they apply), with the generic CUDA-core kernels forced, and with the plain tensor-core
-    kernels (no TMA variants)."""
+    they apply), with the generic CUDA-core kernels forced, with the plain tensor-core
+    kernels (no TMA variants), and with every persistent TMA variant (forward and backward)."""
     lib = _lib.load()
-    lib.dsqg_set_kernel_path({"auto": 0, "generic": 1, "mma": 2}[request.param])
+    lib.dsqg_set_kernel_path({"auto": 0, "generic": 1, "mma": 2, "tma": 3}[request.param])
     yield request.param
     lib.dsqg_set_kernel_path(0)
     assert lib.dsqg_device_error(1) == 0, "a bounded device-side wait gave up"
