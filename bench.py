@@ -364,6 +364,9 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="cfg1", choices=["cfg1", "cfg2", "cfg2_4k", "cfg3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-path", type=int, default=0,
+                    help="dsqg_set_kernel_path value for A/B runs: 0 automatic (default), 1 generic, 2 tensor-core "
+                         "without TMA variants, 3 TMA variants everywhere")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -379,6 +382,9 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the DSQG kernels have no CPU fallback")
     ddist.init_process_group("nccl")
+    if args.kernel_path:
+        from dwarf_b200 import _lib
+        _lib.check(_lib.load().dsqg_set_kernel_path(args.kernel_path), "dsqg_set_kernel_path")
     if args.workload == "cfg3":
         line = run_decode_workload(args, rank, local_rank, world)
     else:

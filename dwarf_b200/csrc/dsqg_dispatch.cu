@@ -6,15 +6,15 @@
 
 namespace dsqg {
 
-// 0 = automatic, 1 = always the generic kernels, 2 = tensor-core kernels without the
-// persistent TMA variants, 3 = persistent TMA variants wherever they exist (the backward ones
-// are not chosen automatically: on B200 they measure slower than the plain tensor-core
-// backward, which keeps more warps resident per SM)
+// 0 = automatic, 1 = always the generic kernels, 2 = tensor-core kernels (same as automatic
+// where they apply), 3 = persistent TMA variants wherever they exist.  The TMA variants are not
+// chosen automatically: on B200 they measure 10-50 % slower than the plain tensor-core kernels,
+// which need fewer registers and keep 20-24 warps resident per SM instead of 9-16.
 static std::atomic<int> g_path{0};
 
 cudaError_t launch_fwd(const FwdArgs& a, const Taps& t, int dtype, cudaStream_t s) {
     const int path = g_path.load();
-    if ((path == 0 || path == 3) && tma_fwd_supported(dtype, a.D, a.N, t, a.scale_embed != nullptr)) return launch_fwd_tma(a, t, s);
+    if (path == 3 && tma_fwd_supported(dtype, a.D, a.N, t, a.scale_embed != nullptr)) return launch_fwd_tma(a, t, s);
     if (path != 1 && mma_path_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_mma(a, t, s);
     return launch_fwd_generic(a, t, dtype, s);
 }

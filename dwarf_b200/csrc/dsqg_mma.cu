@@ -15,7 +15,7 @@
 namespace dsqg {
 namespace {
 
-constexpr int kMaxSparse = 16;     // sparse taps the register-resident score array can hold
+constexpr int kMaxSparse = DSQG_MAX_TAPS;   // any number of sparse taps (they are processed in a loop)
 constexpr int kWarps = 4;
 constexpr int kRows = 16 * kWarps; // rows per CTA
 constexpr int kStagePitch = kRows + 1;
@@ -32,8 +32,13 @@ struct Lane {
 };
 
 // ------------------------------------------------------------------------------ forward
+// Online softmax: the dense window initialises the running maximum and denominator of each
+// row, the sparse taps are then folded in one at a time (rescaling only when a maximum moves,
+// which the distance prior makes rare).  Few live registers, so several CTAs stay resident.
+template <int D> struct FwdOccupancy { static constexpr int ctas = D == 32 ? 5 : 3; };
+
 template <int D, int WB>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, FwdOccupancy<D>::ctas)
 fwd_mma_kernel(const FwdArgs a, const Taps t) {
     constexpr int NT = (WB + 16) / 8;
     __shared__ float pb2_s[DSQG_MAX_TAPS];
@@ -46,9 +51,10 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
     const int g = L.g, tig = L.tig;
     const int row_lo = g0 + g, row_hi = row_lo + 8;
     const bool ok_lo = row_lo < N, ok_hi = row_hi < N;
-    const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(a.q) + (size_t)bh * N * D;
-    const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(a.k) + (size_t)bh * N * D;
-    const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(a.v) + (size_t)bh * N * D;
+    const size_t base = (size_t)bh * N * D;
+    const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(a.q) + base;
+    const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(a.k) + base;
+    const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(a.v) + base;
     const float c2 = a.scale * kLog2e;
     const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1, nd = t.n_dense, ns = t.n_sparse;
     const int kb0 = g0 - WB;
@@ -57,7 +63,7 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
     load_row(qa, qp + (size_t)row_lo * D, tig, ok_lo);
     load_row(qb, qp + (size_t)row_hi * D, tig, ok_hi);
 
-    // ---- phase A: all scores, in log2 units, masked entries = kNeg
+    // ---- dense window
     float S[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -66,7 +72,7 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
         load_row(kf, kp + (size_t)kr * D, tig, kr >= 0 && kr < N);
         mma_rows_z(S[nt], qa, qb, kf);
     }
-    float m_lo = kNeg, m_hi = kNeg;
+    float m_lo = kMinM, m_hi = kMinM;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -79,42 +85,11 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
             if (r < 2) m_lo = fmaxf(m_lo, s); else m_hi = fmaxf(m_hi, s);
         }
     m_lo = quad_max(m_lo); m_hi = quad_max(m_hi);
-
-    float sp_lo[kMaxSparse], sp_hi[kMaxSparse];
-    float sm_lo = kNeg, sm_hi = kNeg;
-#pragma unroll
-    for (int si = 0; si < kMaxSparse; ++si) {
-        sp_lo[si] = kNeg; sp_hi[si] = kNeg;
-        if (si < ns) {
-            const int delta = t.sparse[si];
-            if (g0 + 15 >= delta) {                       // warp-uniform: some row of the tile reaches back
-                const int kr0 = row_lo - delta, kr1 = row_hi - delta;
-                const bool v0 = kr0 >= 0 && ok_lo, v1 = kr1 >= 0 && ok_hi;
-                RowFrag<D> kf0, kf1;
-                load_row(kf0, kp + (size_t)kr0 * D, tig, v0);
-                load_row(kf1, kp + (size_t)kr1 * D, tig, v1);
-                float s0[4], s1[4];
-                mma_rows_z(s0, qa, qb, kf0);
-                mma_rows_z(s1, qa, qb, kf1);
-                const float pbv = pb2_s[nd + si];
-                const float d0 = (g & 1) ? s0[1] : s0[0], d1 = (g & 1) ? s1[3] : s1[2];
-                sp_lo[si] = v0 ? fmaf(d0, c2, pbv) : kNeg;
-                sp_hi[si] = v1 ? fmaf(d1, c2, pbv) : kNeg;
-                sm_lo = fmaxf(sm_lo, sp_lo[si]); sm_hi = fmaxf(sm_hi, sp_hi[si]);
-            }
-        }
-    }
-    m_lo = fmaxf(m_lo, __shfl_sync(0xffffffffu, sm_lo, L.owner_lane));
-    m_hi = fmaxf(m_hi, __shfl_sync(0xffffffffu, sm_hi, L.owner_lane));
-    const float mu_lo = m_lo < -1.0e29f ? 0.f : m_lo;     // row without a valid tap: every p becomes 0
-    const float mu_hi = m_hi < -1.0e29f ? 0.f : m_hi;
-
-    // ---- phase B: probabilities and the value products
     float l_lo = 0.f, l_hi = 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        S[nt][0] = ex2(S[nt][0] - mu_lo); S[nt][1] = ex2(S[nt][1] - mu_lo);
-        S[nt][2] = ex2(S[nt][2] - mu_hi); S[nt][3] = ex2(S[nt][3] - mu_hi);
+        S[nt][0] = ex2(S[nt][0] - m_lo); S[nt][1] = ex2(S[nt][1] - m_lo);
+        S[nt][2] = ex2(S[nt][2] - m_hi); S[nt][3] = ex2(S[nt][3] - m_hi);
         l_lo += S[nt][0] + S[nt][1]; l_hi += S[nt][2] + S[nt][3];
     }
     float O[D / 8][4];
@@ -130,32 +105,49 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
         mma_cols<D>(O, pack_bf16x2(S[2 * c][0], S[2 * c][1]), pack_bf16x2(S[2 * c][2], S[2 * c][3]),
                     pack_bf16x2(S[2 * c + 1][0], S[2 * c + 1][1]), pack_bf16x2(S[2 * c + 1][2], S[2 * c + 1][3]), vt0, vt1);
     }
+    // ---- sparse taps, one at a time
+#pragma unroll 1
+    for (int si = 0; si < ns; ++si) {
+        const int delta = t.sparse[si];
+        if (g0 + 15 < delta) break;                       // taps ascend: no row of the tile reaches back that far
+        const int kr0 = row_lo - delta, kr1 = row_hi - delta;
+        const bool v0 = kr0 >= 0 && ok_lo, v1 = kr1 >= 0 && ok_hi;
+        RowFrag<D> kf0, kf1, vf0, vf1;
+        load_row(kf0, kp + (size_t)kr0 * D, tig, v0);
+        load_row(kf1, kp + (size_t)kr1 * D, tig, v1);
+        load_row(vf0, vp + (size_t)kr0 * D, tig, v0);
+        load_row(vf1, vp + (size_t)kr1 * D, tig, v1);
+        float s0[4], s1[4];
+        mma_rows_z(s0, qa, qb, kf0);
+        mma_rows_z(s1, qa, qb, kf1);
+        const float pbv = pb2_s[nd + si];
+        const float x0 = v0 ? fmaf((g & 1) ? s0[1] : s0[0], c2, pbv) : kNeg;
+        const float x1 = v1 ? fmaf((g & 1) ? s1[3] : s1[2], c2, pbv) : kNeg;
+        const float mn_lo = fmaxf(m_lo, __shfl_sync(0xffffffffu, x0, L.owner_lane));
+        const float mn_hi = fmaxf(m_hi, __shfl_sync(0xffffffffu, x1, L.owner_lane));
+        if (__any_sync(0xffffffffu, mn_lo > m_lo || mn_hi > m_hi)) {
+            const float al_lo = ex2(m_lo - mn_lo), al_hi = ex2(m_hi - mn_hi);
+            m_lo = mn_lo; m_hi = mn_hi;
+            l_lo *= al_lo; l_hi *= al_hi;
 #pragma unroll
-    for (int si = 0; si < kMaxSparse; ++si) {
-        if (si < ns) {
-            const int delta = t.sparse[si];
-            if (g0 + 15 >= delta) {
-                const int kr0 = row_lo - delta, kr1 = row_hi - delta;
-                const float p0 = ex2(sp_lo[si] - mu_lo), p1 = ex2(sp_hi[si] - mu_hi);
-                if (L.owner) { l_lo += p0; l_hi += p1; }
-                RowFrag<D> vf0, vf1, vt0, vt1;
-                load_row(vf0, vp + (size_t)kr0 * D, tig, kr0 >= 0 && ok_lo);
-                load_row(vf1, vp + (size_t)kr1 * D, tig, kr1 >= 0 && ok_hi);
-                transpose_frag(vt0, vf0); transpose_frag(vt1, vf1);
-                uint32_t a0, a3;
-                diag_frag(p0, p1, L.owner, g, a0, a3);
-                mma_cols<D>(O, a0, 0u, 0u, a3, vt0, vt1);
-            }
+            for (int j = 0; j < D / 8; ++j) { O[j][0] *= al_lo; O[j][1] *= al_lo; O[j][2] *= al_hi; O[j][3] *= al_hi; }
         }
+        const float p0 = ex2(x0 - m_lo), p1 = ex2(x1 - m_hi);
+        if (L.owner) { l_lo += p0; l_hi += p1; }
+        RowFrag<D> vt0, vt1;
+        transpose_frag(vt0, vf0); transpose_frag(vt1, vf1);
+        uint32_t a0, a3;
+        diag_frag(p0, p1, L.owner, g, a0, a3);
+        mma_cols<D>(O, a0, 0u, 0u, a3, vt0, vt1);
     }
     l_lo = quad_sum(l_lo); l_hi = quad_sum(l_hi);
     const float gain = a.head_gain ? a.head_gain[h] : 1.f;
-    __nv_bfloat16* op = static_cast<__nv_bfloat16*>(a.out) + (size_t)bh * N * D;
+    __nv_bfloat16* op = static_cast<__nv_bfloat16*>(a.out) + base;
     store_acc_rows<D>(O, op + (size_t)row_lo * D, op + (size_t)row_hi * D, ok_lo, ok_hi,
-                      l_lo > 0.f ? gain / l_lo : 0.f, l_hi > 0.f ? gain / l_hi : 0.f, tig);
+                      l_lo > 0.f ? __fdividef(gain, l_lo) : 0.f, l_hi > 0.f ? __fdividef(gain, l_hi) : 0.f, tig);
     if (tig == 0) {
-        if (ok_lo) a.lse[(size_t)bh * N + row_lo] = l_lo > 0.f ? (m_lo + log2f(l_lo)) * kLn2 : -INFINITY;
-        if (ok_hi) a.lse[(size_t)bh * N + row_hi] = l_hi > 0.f ? (m_hi + log2f(l_hi)) * kLn2 : -INFINITY;
+        if (ok_lo) a.lse[(size_t)bh * N + row_lo] = l_lo > 0.f ? (m_lo + __log2f(l_lo)) * kLn2 : -INFINITY;
+        if (ok_hi) a.lse[(size_t)bh * N + row_hi] = l_hi > 0.f ? (m_hi + __log2f(l_hi)) * kLn2 : -INFINITY;
     }
 }
 

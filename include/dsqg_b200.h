@@ -59,9 +59,9 @@ const char* dsqg_last_cuda_error(void);
 int dsqg_version(void);
 
 /* Testing knob with no counterpart in the reference: 0 = choose kernels automatically
- * (default), 1 = always use the generic CUDA-core kernels, 2 = tensor-core kernels but not
- * their persistent TMA variants, 3 = persistent TMA variants wherever one exists (including
- * the backward ones, which the automatic choice does not use).  Process-wide. */
+ * (default), 1 = always use the generic CUDA-core kernels, 2 = the tensor-core kernels (what the
+ * automatic choice uses where they apply), 3 = the persistent TMA-fed variants wherever one
+ * exists (not chosen automatically: they measure slower on B200).  Process-wide. */
 int dsqg_set_kernel_path(int path);
 
 /* Device-side error word of the current device (no counterpart in the reference).  The
