@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the DSQG attention hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1|cfg2|cfg2_4k|cfg3]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1|cfg2|cfg2_4k|cfg3|cfg4]
     python bench.py --impl reference ...      # the reference's PyTorch path on the host cores
 
 A "step" is one forward+backward pass of the DSQG op over one batch of synthetic input
@@ -229,6 +229,9 @@ def run_decode_workload(args, rank, local_rank, world):
     from dwarf_b200 import dist as ddist, synth
 
     cfg = synth.DecodeConfig()
+    if args.decode_layers > 0:
+        cfg.layers = args.decode_layers
+        cfg.name = cfg.name.replace("L10", f"L{cfg.layers}")
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     x = synth.make_decode_inputs(cfg, device="cpu")
@@ -255,6 +258,26 @@ def run_decode_workload(args, rank, local_rank, world):
     e0.record(stream)
     for _ in range(args.steps):
         step()
+    e1.record(stream)
+    torch.cuda.synchronize(); ddist.barrier()
+    eager_ms = ddist.max_over_ranks(e0.elapsed_time(e1), dev if world > 1 else "cpu") / args.steps
+    # The 10 launches of a step are latency-bound: replay them as one CUDA graph (the library
+    # neither allocates nor synchronises, so its calls can be captured as they are).
+    graph = torch.cuda.CUDAGraph()
+    gs = torch.cuda.Stream()
+    gs.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(gs):
+        step()
+        gs.synchronize()
+        with torch.cuda.graph(graph, stream=gs):
+            step()
+    torch.cuda.current_stream().wait_stream(gs)
+    for _ in range(args.warmup):
+        graph.replay()
+    ddist.barrier(); torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(args.steps):
+        graph.replay()
     e1.record(stream)
     torch.cuda.synchronize(); ddist.barrier()
     ms = ddist.max_over_ranks(e0.elapsed_time(e1), dev if world > 1 else "cpu") / args.steps
@@ -290,13 +313,78 @@ def run_decode_workload(args, rank, local_rank, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": cfg.name, "l2": f"ring footprint {2 * L * cfg.S * cfg.H * cfg.R * cfg.D * esz / 1e9:.1f} GB >> L2",
+                   "launch": "one CUDA graph of the 10 per-layer launches per step",
                    "parallelism": f"sequences replicated x{world}, no collective"},
+        "ms_per_step_eager": eager_ms,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": small,
                 "d2h_bytes_per_step": small // 3, "ms_per_step": e2e_ms, "steps": e2e_steps},
         "gpu_launches": L * args.steps,
         "roofline": {"bound": "hbm", "kernel": "dsqg_decode", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": layer_bytes, "ms_per_launch": ms / L},
+        "clocks": clocks,
+    }
+
+
+def run_train_workload(args, rank, local_rank, world):
+    """cfg4: end-to-end training step of the condM-shaped LM (fwd + bwd + AdamW), bf16 autocast,
+    DDP gradient all-reduce over NCCL when world > 1.  Token ids come from pinned host memory
+    every step and the loss is read back: the whole step is the end-to-end path."""
+    import torch.nn.functional as F
+    from dwarf_b200 import dist as ddist
+    from dwarf_b200.model import CondMLM
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    B, N, V = 32, 2048, 32000
+    torch.manual_seed(1234)
+    model = CondMLM(vocab=V, seq_len=N).to(dev)
+    if world > 1:
+        model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True)
+    g = torch.Generator().manual_seed(4321 + rank)
+    host_ids = torch.randint(0, V, (B, N + 1), generator=g).pin_memory()
+    loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
+    stream = torch.cuda.current_stream()
+
+    def step():
+        ids = host_ids.to(dev, non_blocking=True)
+        with torch.amp.autocast("cuda", dtype=torch.bfloat16):
+            logits = model(ids[:, :-1])
+        loss = F.cross_entropy(logits.float().view(-1, V), ids[:, 1:].reshape(-1))
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        loss_host.copy_(loss.detach(), non_blocking=True)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ddist.barrier(); torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize(); ddist.barrier()
+    ms = ddist.max_over_ranks(e0.elapsed_time(e1), dev if world > 1 else "cpu") / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    tokens = B * N * world
+    val = tokens / (ms * 1e-3)
+    n_params = sum(p.numel() for p in model.parameters())
+    return {
+        "metric": "condM-shaped LM training tokens/s", "value": val, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "cfg4 condM-shaped LM train step: 6 layers d256 8x32 heads FFN1024 vocab32000, "
+                               "DSQG layers 0-4 + full attention layer 5, B32/GPU N2048, AdamW",
+                   "parameters": n_params, "final_loss": float(loss_host),
+                   "parallelism": f"dp{world} (DDP, NCCL gradient all-reduce)" if world > 1 else "single GPU"},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": B * (N + 1) * 8, "d2h_bytes_per_step": 4,
+                "note": "the timed step already starts from pinned host token ids and ends with the loss on the host"},
+        "gpu_launches": 3 * 5 * args.steps,      # DSQG forward + dQ + dK/dV kernels of the 5 DSQG layers (others are library GEMMs)
         "clocks": clocks,
     }
 
@@ -362,8 +450,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=["cfg1", "cfg2", "cfg2_4k", "cfg3"])
+    ap.add_argument("--workload", default="cfg1", choices=["cfg1", "cfg2", "cfg2_4k", "cfg3", "cfg4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--decode-layers", type=int, default=0, help="cfg3: number of layers (default: the 10 of the configuration)")
     ap.add_argument("--kernel-path", type=int, default=0,
                     help="dsqg_set_kernel_path value for A/B runs: 0 automatic (default), 1 generic, 2 tensor-core "
                          "without TMA variants, 3 TMA variants everywhere")
@@ -375,7 +464,7 @@ def main():
 
     if args.impl == "reference":
         if rank == 0:
-            cfg = synth.OP_CONFIGS["cfg1" if args.workload == "cfg3" else args.workload]
+            cfg = synth.OP_CONFIGS["cfg1" if args.workload in ("cfg3", "cfg4") else args.workload]
             print(json.dumps(run_reference_arm(args, cfg)), flush=True)
         return 0
 
@@ -387,6 +476,8 @@ def main():
         _lib.check(_lib.load().dsqg_set_kernel_path(args.kernel_path), "dsqg_set_kernel_path")
     if args.workload == "cfg3":
         line = run_decode_workload(args, rank, local_rank, world)
+    elif args.workload == "cfg4":
+        line = run_train_workload(args, rank, local_rank, world)
     else:
         cfg = synth.OP_CONFIGS[args.workload]
         line = run_op_workload(args, cfg, rank, local_rank, world)

@@ -13,7 +13,31 @@ namespace {
 
 constexpr int kWarpsPerBlock = 4;
 
-template <typename T, int TPR>
+// Raw 8-element slices as loaded from memory; conversion happens after every load of the step
+// has been issued, so one (sequence, head) pair costs a single memory round trip.
+template <typename T> struct Raw8;
+template <> struct Raw8<__nv_bfloat16> {
+    uint4 u;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void zero() { u = make_uint4(0u, 0u, 0u, 0u); }
+    __device__ __forceinline__ void get(float (&x)[8]) const {
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { x[2 * i] = __uint_as_float(w[i] << 16); x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+    }
+};
+template <> struct Raw8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) { a = *reinterpret_cast<const float4*>(p); b = *reinterpret_cast<const float4*>(p + 4); }
+    __device__ __forceinline__ void zero() { a = make_float4(0.f, 0.f, 0.f, 0.f); b = a; }
+    __device__ __forceinline__ void get(float (&x)[8]) const {
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    }
+};
+
+// All K and V rows of up to ROUNDS taps per lane group are requested before any is used
+// (2*ROUNDS independent 16/32-byte loads per lane): one memory round trip per pass.
+template <typename T, int TPR, int ROUNDS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 decode_kernel(const DecodeArgs a, const Taps t) {
     constexpr int GROUPS = 32 / TPR;
@@ -36,52 +60,61 @@ decode_kernel(const DecodeArgs a, const Taps t) {
 
     float qx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (active) load8(q + d0, qx);
-    // Store the new token; taps with delta == 0 read k_new / v_new directly, so no lane
-    // depends on this store becoming visible inside the kernel.
-    if (g == 0 && active) {
+    if (g == 0 && active) {          // store the new token in the ring (bf16->fp32->bf16 is exact)
         float t8[8];
-        load8(kn + d0, t8); store8(kr + (size_t)head * D + d0, t8);   // bf16->fp32->bf16 is exact
+        load8(kn + d0, t8); store8(kr + (size_t)head * D + d0, t8);
         load8(vn + d0, t8); store8(vr + (size_t)head * D + d0, t8);
     }
-
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     float m = -INFINITY, l = 0.f;
     const int rounds = (t.J + GROUPS - 1) / GROUPS;
-#pragma unroll 4
-    for (int r = 0; r < rounds; ++r) {
-        const int j = r * GROUPS + g;
-        const int delta = j < t.J ? t.delta(j) : 0;
-        const bool valid = j < t.J && delta < fill;
-        int slot = head - delta;
-        if (slot < 0) slot += a.R;
-        float kx[8] = {0, 0, 0, 0, 0, 0, 0, 0}, vx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (valid && active) {
-            const T* kp = delta == 0 ? kn : kr + (size_t)slot * D;
-            const T* vp = delta == 0 ? vn : vr + (size_t)slot * D;
-            load8(kp + d0, kx);
-            load8(vp + d0, vx);
-            if (has_se) {
+#pragma unroll 1
+    for (int r0 = 0; r0 < rounds; r0 += ROUNDS) {         // one pass for the usual tap counts
+        // ---- request the rows of up to ROUNDS taps per lane group
+        Raw8<T> kraw[ROUNDS], vraw[ROUNDS];
+#pragma unroll
+        for (int r = 0; r < ROUNDS; ++r) {
+            const int j = (r0 + r) * GROUPS + g;
+            const int delta = j < t.J ? t.delta(j) : 0;
+            int slot = head - delta;
+            if (slot < 0) slot += a.R;
+            kraw[r].zero(); vraw[r].zero();
+            if (j < t.J && delta < fill && active) {
+                // taps with delta == 0 read k_new / v_new directly, so nothing depends on the ring
+                // store above becoming visible inside the kernel
+                kraw[r].load(delta == 0 ? kn + d0 : kr + (size_t)slot * D + d0);
+                vraw[r].load(delta == 0 ? vn + d0 : vr + (size_t)slot * D + d0);
+            }
+        }
+        // ---- scores and online softmax over this lane group's taps
+#pragma unroll
+        for (int r = 0; r < ROUNDS; ++r) {
+            const int j = (r0 + r) * GROUPS + g;
+            const bool valid = j < t.J && t.delta(j < t.J ? j : 0) < fill;
+            float kx[8], vx[8];
+            kraw[r].get(kx); vraw[r].get(vx);
+            if (has_se && valid && active) {
                 float se[8];
                 load8(a.scale_embed + (size_t)j * D + d0, se);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) kx[i] += se[i];
             }
-        }
-        float dot = 0.f;
+            float dot = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dot = fmaf(qx[i], kx[i], dot);
-        dot = group_sum<TPR>(dot);
-        if (valid) {
-            const float sc = dot * a.scale + a.pos_bias[j * a.H + h];
-            const float mn = fmaxf(m, sc);
-            const float cor = __expf(m - mn), p = __expf(sc - mn);
-            l = l * cor + p;
+            for (int i = 0; i < 8; ++i) dot = fmaf(qx[i], kx[i], dot);
+            dot = group_sum<TPR>(dot);
+            if (valid) {
+                const float sc = dot * a.scale + a.pos_bias[j * a.H + h];
+                const float mn = fmaxf(m, sc);
+                const float cor = __expf(m - mn), p = __expf(sc - mn);
+                l = l * cor + p;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = acc[i] * cor + p * vx[i];
-            m = mn;
+                for (int i = 0; i < 8; ++i) acc[i] = acc[i] * cor + p * vx[i];
+                m = mn;
+            }
         }
     }
-    // Merge the GROUPS partial softmax states.
+    // ---- merge the GROUPS partial softmax states
 #pragma unroll
     for (int o = TPR; o < 32; o <<= 1) {
         const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
@@ -107,11 +140,20 @@ decode_kernel(const DecodeArgs a, const Taps t) {
     }
 }
 
+template <typename T, int TPR, int ROUNDS>
+cudaError_t decode_launch_r(const DecodeArgs& a, const Taps& t, cudaStream_t s) {
+    const int pairs = a.S * a.H;
+    decode_kernel<T, TPR, ROUNDS><<<(pairs + kWarpsPerBlock - 1) / kWarpsPerBlock, kWarpsPerBlock * 32, 0, s>>>(a, t);
+    return cudaGetLastError();
+}
+
 template <typename T, int TPR>
 cudaError_t decode_launch(const DecodeArgs& a, const Taps& t, cudaStream_t s) {
-    const int pairs = a.S * a.H;
-    decode_kernel<T, TPR><<<(pairs + kWarpsPerBlock - 1) / kWarpsPerBlock, kWarpsPerBlock * 32, 0, s>>>(a, t);
-    return cudaGetLastError();
+    const int rounds = (t.J + 32 / TPR - 1) / (32 / TPR);
+    // Passes of 6 rounds keep the kernel at 96 registers (all warps of the benchmark shape resident
+    // at once); measured slightly faster on B200 than one pass of 12 rounds at 166 registers.
+    (void)rounds;
+    return decode_launch_r<T, TPR, 6>(a, t, s);
 }
 }  // namespace
 
