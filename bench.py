@@ -194,6 +194,9 @@ def run_op_workload(args, cfg, rank, local_rank, world):
 
     T = op_bytes(cfg)
     peak, peak_src = measured_peaks()
+    # DRAM bytes (read + write) per launch from the ncu capture summarised in
+    # profiles/dsqg_mma_kernels_cfg1.md; only known for the workload that was captured.
+    ncu_traffic = {"cfg1": [119.96e6, 195.40e6, 183.60e6, None]}.get(args.workload, [None] * 4)
     names = ["dsqg_fwd", "dsqg_bwd_dq", "dsqg_bwd_dkdv", "dsqg_bwd_reduce_params"]
     alg = [4 * T, 6 * T, 6 * T, 0]        # per launch: fwd Q,K,V->O ; dq Q,K,V,O,dO->dQ ; dkdv Q,K,V,dO->dK,dV
     top = max(range(3), key=lambda s: kern_ms[s])
@@ -212,11 +215,11 @@ def run_op_workload(args, cfg, rank, local_rank, world):
                 "steps": e2e_steps},
         "gpu_launches": 4 * args.steps,
         "roofline": {"bound": "hbm", "kernel": names[top], "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "frac": achieved / peak, "traffic": ncu_traffic[top], "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": alg[top], "ms_per_launch": kern_ms[top]},
         "step_roofline": {"algorithmic_bytes_per_step": 12 * T, "achieved": step_achieved,
                           "frac": step_achieved / peak, "unit": "GB/s"},
-        "kernels": [{"name": names[s], "ms": kern_ms[s], "algorithmic_bytes": alg[s],
+        "kernels": [{"name": names[s], "ms": kern_ms[s], "algorithmic_bytes": alg[s], "traffic": ncu_traffic[s],
                      "gbs": (alg[s] / (kern_ms[s] * 1e-3) / 1e9) if alg[s] else None} for s in range(4)],
         "wall_ms_timed_region": wall_ms,
         "clocks": clocks,
@@ -470,6 +473,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the DSQG kernels have no CPU fallback")
+    # keep stdout to the one JSON line: NCCL's version banner goes there at NCCL_DEBUG=VERSION
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
     ddist.init_process_group("nccl")
     if args.kernel_path:
         from dwarf_b200 import _lib
@@ -482,7 +488,7 @@ def main():
         cfg = synth.OP_CONFIGS[args.workload]
         line = run_op_workload(args, cfg, rank, local_rank, world)
         if rank == 0 and world == 1 and not args.no_cpu_baseline:
-            sample_B = 8
+            sample_B = min(cfg.B, 32)
             val, secs = cpu_reference_time(cfg, sample_B, repeats=4)
             line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": torch.get_num_threads(),
                                     "kind": "port",
