@@ -179,4 +179,15 @@ int dsqg_decode(const void* q, const void* k_new, const void* v_new,
     return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
 }
 
+int dsqg_ring_prefill(const void* k, const void* v, void* k_ring, void* v_ring,
+                      int32_t* head, int32_t* fill, int S, int H, int N, int D, int R, int dtype, void* stream) {
+    if (!k || !v || !k_ring || !v_ring || !head || !fill) return DSQG_ERR_NULL_POINTER;
+    int rc = check_shape(S, H, N, D, dtype);
+    if (rc) return rc;
+    if (R < 1 || (long long)S * H * R > 0x7fffffffLL) return DSQG_ERR_BAD_SHAPE;
+    if (misaligned16(k) || misaligned16(v) || misaligned16(k_ring) || misaligned16(v_ring)) return DSQG_ERR_MISALIGNED;
+    cudaError_t e = launch_ring_prefill(k, v, k_ring, v_ring, head, fill, S, H, N, D, R, dtype, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
+}
+
 }  // extern "C"

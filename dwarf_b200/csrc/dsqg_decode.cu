@@ -167,6 +167,42 @@ cudaError_t decode_launch(const DecodeArgs& a, const Taps& t, cudaStream_t s) {
         return decode_launch<T, 16>(a, t, s);                           \
     } while (0)
 
+// Ring prefill: copies the last min(N, R) positions of K and V from the training layout
+// [S,H,N,D] into the rings [S,H,R,D] so that position p lands in slot p mod R, and sets
+// head[s] = (N-1) mod R, fill[s] = min(N, R).  One 16-byte chunk per thread.
+__global__ void ring_prefill_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, uint4* k_ring, uint4* v_ring,
+                                    int32_t* head, int32_t* fill, int SH, int H, int N, int R, int chunks_per_row) {
+    const int keep = N < R ? N : R;
+    const long long total = (long long)SH * keep * chunks_per_row;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % chunks_per_row);
+        const long long rowi = i / chunks_per_row;
+        const int j = (int)(rowi % keep);
+        const int sh = (int)(rowi / keep);
+        const int p = N - keep + j;                       // position in the sequence
+        const int slot = p % R;
+        const long long src = ((long long)sh * N + p) * chunks_per_row + c;
+        const long long dst = ((long long)sh * R + slot) * chunks_per_row + c;
+        k_ring[dst] = k[src];
+        v_ring[dst] = v[src];
+    }
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid < SH / H) { head[tid] = (N - 1) % R; fill[tid] = keep; }
+}
+
+cudaError_t launch_ring_prefill(const void* k, const void* v, void* k_ring, void* v_ring, int32_t* head, int32_t* fill,
+                                int S, int H, int N, int D, int R, int dtype, cudaStream_t s) {
+    const int chunks = D * (dtype == DSQG_DTYPE_BF16 ? 2 : 4) / 16;
+    const long long total = (long long)S * H * (N < R ? N : R) * chunks;
+    long long blocks = (total + 255) / 256;
+    if (blocks < (S + 255) / 256) blocks = (S + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    ring_prefill_kernel<<<(int)blocks, 256, 0, s>>>(static_cast<const uint4*>(k), static_cast<const uint4*>(v),
+                                                  static_cast<uint4*>(k_ring), static_cast<uint4*>(v_ring), head, fill,
+                                                  S * H, H, N, R, chunks);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_decode(const DecodeArgs& a, const Taps& t, int dtype, cudaStream_t s) {
     if (dtype == DSQG_DTYPE_BF16) DSQG_DECODE_TPR(__nv_bfloat16);
     DSQG_DECODE_TPR(float);

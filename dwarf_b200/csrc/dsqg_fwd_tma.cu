@@ -48,7 +48,6 @@ struct FwdTmaPlan {
     int total_blocks;    // B*H*blocks_per_seq
     int blocks_per_cta;
     int consumers;       // W
-    int debug;           // experiment switches (0 in production): 1 skip window taps, 2 skip far taps, 4 skip dense
 };
 
 template <int D>
@@ -333,7 +332,7 @@ __device__ __forceinline__ void consumer_loop(const FwdArgs& a, const FwdTmaPlan
             const int seq = j * plan.n_far + f;
             const int fs = seq % plan.n_far_stages;
             mbar_wait(bars.far_full(fs), (seq / plan.n_far_stages) & 1, abort_flag, 0x203);
-            if (active && n_win + f < nv && !(plan.debug & 2)) {
+            if (active && n_win + f < nv) {
                 const uint32_t base = smem_base + lay.far + fs * 2 * kTile + tib * 16 * kPitch;
                 const uint32_t srcK[1] = {base}, srcV[1] = {base + kTile};
                 const bool ok[1] = {true};
@@ -345,9 +344,8 @@ __device__ __forceinline__ void consumer_loop(const FwdArgs& a, const FwdTmaPlan
             if (lane == 0) mbar_arrive(bars.far_empty(fs));
         }
         if (active) {
-            if (!(plan.debug & 4))
-                dense_window<D, WB>(st, qa, qb, biasd, k_ring, v_ring, g0, gs, ring_mask, c2, lo, co, merged);
-            const int nvw = (plan.debug & 1) ? 0 : (nv < n_win ? nv : n_win);
+            dense_window<D, WB>(st, qa, qb, biasd, k_ring, v_ring, g0, gs, ring_mask, c2, lo, co, merged);
+            const int nvw = nv < n_win ? nv : n_win;
             const uint32_t gsp = (uint32_t)gs * kPitch;
 #pragma unroll 1
             for (int t0 = 0; t0 < nvw; t0 += kGroup) {
@@ -472,7 +470,6 @@ cudaError_t fwd_launch_tma(const FwdArgs& a, const Taps& t, cudaStream_t stream)
     if (e != cudaSuccess) return e;
     if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
     FwdTmaPlan plan;
-    { const char* dbg = getenv("DSQG_FWD_DEBUG"); plan.debug = dbg ? atoi(dbg) : 0; }
     plan.consumers = W;
     plan.nrb = 8;                               // 8 x 128 rows of K and of V: 128 KB at D = 32
     if (D == 64) plan.nrb = 4;

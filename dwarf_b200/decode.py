@@ -61,6 +61,20 @@ class DSQGRingCache:
         self.head = torch.full((sequences,), -1, dtype=torch.int32, device=device)
         self.fill = torch.zeros(sequences, dtype=torch.int32, device=device)
 
+    def prefill(self, layer, k, v):
+        """Load the rings of `layer` from a prefix in training layout: k, v [S,H,N,D].  Sets head
+        and fill for the whole cache (call it with the same N for every layer)."""
+        lib = _lib.load()
+        S, H, N, D = k.shape
+        if tuple(self.k[layer].shape) != (S, H, self.R, D) or k.dtype != self.k.dtype or v.shape != k.shape:
+            raise ValueError("dsqg ring prefill: k, v must be [S,H,N,D] matching the cache")
+        k, v = k.contiguous(), v.contiguous()
+        with torch.cuda.device(k.device):
+            stream = torch.cuda.current_stream(k.device).cuda_stream
+            _lib.check(lib.dsqg_ring_prefill(k.data_ptr(), v.data_ptr(), self.k[layer].data_ptr(),
+                                             self.v[layer].data_ptr(), self.head.data_ptr(), self.fill.data_ptr(),
+                                             S, H, N, D, self.R, _dtype_code(k), stream), "dsqg_ring_prefill")
+
     def advance(self):
         """Move every write head to the next slot; call once per token before the layers run."""
         self.head = torch.remainder(self.head + 1, self.R).to(torch.int32)

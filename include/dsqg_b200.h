@@ -164,6 +164,16 @@ int dsqg_decode(const void* q, const void* k_new, const void* v_new,
                 const int32_t* offsets, int J, int R,
                 void* out, int S, int H, int D, int dtype, void* stream);
 
+/* Fills the decode rings from a training-layout prefix.
+ * Replaces: nothing executable (the reference has no cache; its generate() re-runs the whole
+ *   prefix, DWARF train/train_2048_condU.py:463-487).
+ * k, v: [S,H,N,D]; k_ring, v_ring: [S,H,R,D].  Position p of every sequence is copied to slot
+ * p mod R for the last min(N,R) positions; head[s] = (N-1) mod R and fill[s] = min(N,R) are
+ * written (DEVICE int32 [S]).  The next token then goes to slot (head+1) mod R with fill+1
+ * (capped at R), which is what dsqg_decode expects. */
+int dsqg_ring_prefill(const void* k, const void* v, void* k_ring, void* v_ring,
+                      int32_t* head, int32_t* fill, int S, int H, int N, int D, int R, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

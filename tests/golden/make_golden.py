@@ -39,7 +39,7 @@ def bf16_bits(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a DWARF checkout")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "kernels"))
     sys.path.insert(0, os.path.join(args.reference, "train"))

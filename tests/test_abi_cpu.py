@@ -100,6 +100,14 @@ def test_decode_argument_errors(lib):
     assert call(kr=_fake(4) + 8) == -5
 
 
+def test_ring_prefill_argument_errors(lib):
+    call = lambda **kw: lib.dsqg_ring_prefill(kw.get("k", _fake(1)), _fake(2), _fake(3), _fake(4), _fake(5),
+                                              kw.get("fill", _fake(6)), 2, 2, kw.get("N", 8), kw.get("D", 64), kw.get("R", 16), 0, None)
+    assert call(k=None) == -1 and call(fill=None) == -1
+    assert call(N=0) == -2 and call(D=12) == -2 and call(R=0) == -2
+    assert call(k=_fake(1) + 4) == -5
+
+
 def test_python_wrappers_refuse_cpu_tensors():
     import torch
     from dwarf_b200 import dsqg_attention

@@ -97,6 +97,24 @@ def test_decode_reproduces_training_forward_token_by_token():
         assert (o.float() - full[:, :, t]).abs().max().item() <= 2e-2, t
 
 
+@pytest.mark.parametrize("N", [5, 49, 50, 120])
+def test_prefill_then_decode_continues_the_sequence(N):
+    """Rings filled from a training-layout prefix of N tokens, then token N decoded: must equal
+    row N of the full-sequence forward over N+1 tokens (prefix shorter, equal and longer than R)."""
+    g = torch.Generator().manual_seed(N)
+    S, H, D = 3, 2, 64
+    offsets = tuple(range(8)) + (16, 32, 48)
+    q, k, v = (bf16v(S, H, N + 1, D, gen=g).to(DEV, torch.bfloat16) for _ in range(3))
+    pb = torch.randn(len(offsets), H, generator=g).to(DEV)
+    full = dwarf_b200.dsqg_attention(q, k, v, pb, None, None, offsets).float()
+    cache = dwarf_b200.DSQGRingCache(1, S, H, D, offsets)
+    cache.prefill(0, k[:, :, :N].contiguous(), v[:, :, :N].contiguous())
+    assert int(cache.head[0]) == (N - 1) % cache.R and int(cache.fill[0]) == min(N, cache.R)
+    cache.advance()
+    o = cache.step(0, q[:, :, N].contiguous(), k[:, :, N].contiguous(), v[:, :, N].contiguous(), pb)
+    assert (o.float() - full[:, :, N]).abs().max().item() <= 2e-2
+
+
 def test_benchmark_shape_runs_and_matches_on_a_sample():
     cfg = synth.DecodeConfig()
     x = synth.make_decode_inputs(cfg, device="cpu", layers=1)
