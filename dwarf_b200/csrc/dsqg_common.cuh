@@ -40,7 +40,7 @@ struct BwdArgs {
     float* dpos_bias; float* dscale_embed; float* dhead_gain;
     void* scratch; size_t scratch_bytes;
     // scratch carve-up (all fp32), filled in by carve_bwd_scratch() inside each launcher
-    float* delta;      // [B*H*N]    sum_d dout*out per row
+    float* delta;      // [B*H*N] sum_d dout*out per row; the tensor-core kernels keep {lse*log2e, delta} pairs here ([B*H*N] float2)
     float* dpb_part;   // [n_tiles, J]
     float* dg_part;    // [n_tiles]
     float* dse_part;   // [n_tiles, J, D] (only with scale_embed)
@@ -80,7 +80,7 @@ bool tma_bwd_supported(int dtype, int D, int N, const Taps& t, bool has_scale_em
 size_t bwd_scratch_need_tma(int J, int B, int H, int N);
 cudaError_t read_device_error_bwd_tma(int* value, bool reset);
 
-// Backward scratch layout: delta | dpos_bias partials | dhead_gain partials | dscale_embed
+// Backward scratch layout: row statistics (8 bytes per row) | dpos_bias partials | dhead_gain partials | dscale_embed
 // partials, each block rounded up to 256 bytes.  A "tile" is the set of rows whose partial
 // sums one thread block produces; kernels differ in rows_per_tile, so each launcher carves
 // for itself and the size query reserves room for the finest tiling in use.
@@ -88,7 +88,7 @@ constexpr int kMinRowsPerBwdTile = 64;
 inline size_t round256(size_t bytes) { return (bytes + 255) / 256 * 256; }
 inline size_t bwd_scratch_need(int rows_per_tile, int J, int B, int H, int N, int D, bool has_se) {
     const size_t tiles = (size_t)B * H * ((N + rows_per_tile - 1) / rows_per_tile);
-    return round256((size_t)B * H * N * 4) + round256(tiles * J * 4) + round256(tiles * 4) +
+    return round256((size_t)B * H * N * 8) + round256(tiles * J * 4) + round256(tiles * 4) +
            (has_se ? round256(tiles * J * D * 4) : 0);
 }
 inline void carve_bwd_scratch(BwdArgs& a, int rows_per_tile, int J, bool has_se) {
@@ -96,7 +96,7 @@ inline void carve_bwd_scratch(BwdArgs& a, int rows_per_tile, int J, bool has_se)
     a.n_tiles = a.B * a.H * a.tiles_per_bh;
     a.n_dse_blocks = a.n_tiles;
     char* p = static_cast<char*>(a.scratch);
-    a.delta = reinterpret_cast<float*>(p);    p += round256((size_t)a.B * a.H * a.N * 4);
+    a.delta = reinterpret_cast<float*>(p);    p += round256((size_t)a.B * a.H * a.N * 8);
     a.dpb_part = reinterpret_cast<float*>(p); p += round256((size_t)a.n_tiles * J * 4);
     a.dg_part = reinterpret_cast<float*>(p);  p += round256((size_t)a.n_tiles * 4);
     a.dse_part = has_se ? reinterpret_cast<float*>(p) : nullptr;

@@ -11,6 +11,7 @@
 // output gain of train/train_2048_condU.py:187 fused in.  See dsqg_mma.cuh for the
 // fragment conventions.
 #include "dsqg_mma.cuh"
+#include <type_traits>
 
 namespace dsqg {
 namespace {
@@ -18,7 +19,6 @@ namespace {
 constexpr int kMaxSparse = DSQG_MAX_TAPS;   // any number of sparse taps (they are processed in a loop)
 constexpr int kWarps = 4;
 constexpr int kRows = 16 * kWarps; // rows per CTA
-constexpr int kStagePitch = kRows + 1;
 
 struct Lane {
     int warp, lane, g, tig;
@@ -32,113 +32,186 @@ struct Lane {
 };
 
 // ------------------------------------------------------------------------------ forward
-// Online softmax: the dense window initialises the running maximum and denominator of each
-// row, the sparse taps are then folded in one at a time (rescaling only when a maximum moves,
-// which the distance prior makes rare).  Few live registers, so several CTAs stay resident.
-template <int D> struct FwdOccupancy { static constexpr int ctas = D == 32 ? 5 : 3; };
+// Online softmax over the dense window, then over the sparse taps, with the per-element
+// bookkeeping moved out of the tile loop:
+//   * the band mask and the position bias of the dense window are the INITIAL VALUE of the score
+//     accumulators (a per-lane table in shared memory, one 16-byte load per n-tile), so the
+//     scores leave the MMAs already biased and masked (in units of 1/scale);
+//   * interior tiles (all band rows inside the sequence) load with no predicates and constant
+//     offsets from one pointer; a sparse tap whose 16 key rows all exist does the same;
+//   * the running maximum only moves when a sparse score exceeds it by more than kSlack
+//     (log2 units): p stays below 2^kSlack, which fp32 sums and bf16 probabilities absorb;
+//   * lanes that do not own a diagonal entry subtract +1e30 instead of the maximum, so their
+//     probability is exactly zero without a select.
+constexpr float kSlack = 16.f;
 
-template <int D, int WB>
-__global__ void __launch_bounds__(kWarps * 32, FwdOccupancy<D>::ctas)
-fwd_mma_kernel(const FwdArgs a, const Taps t) {
+template <int D>
+__device__ __forceinline__ void load_row_at(RowFrag<D>& f, const __nv_bfloat16* p) {
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(p + 32 * c));
+        f.r[4 * c + 0] = u.x; f.r[4 * c + 1] = u.y; f.r[4 * c + 2] = u.z; f.r[4 * c + 3] = u.w;
+    }
+}
+
+template <int D, int WB, bool INTERIOR, int kTapGroup>
+__device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s, const int2* tap_s, int ns,
+                                         int bh, int h, int g0, const Lane& L) {
     constexpr int NT = (WB + 16) / 8;
-    __shared__ float pb2_s[DSQG_MAX_TAPS];
-    const Lane L;
-    const int bh = blockIdx.y, h = bh % a.H, N = a.N;
-    for (int j = threadIdx.x; j < t.J; j += kWarps * 32) pb2_s[j] = a.pos_bias[j * a.H + h] * kLog2e;
-    __syncthreads();
-    const int g0 = blockIdx.x * kRows + L.warp * 16;
-    if (g0 >= N) return;
-    const int g = L.g, tig = L.tig;
+    const int N = a.N, g = L.g, tig = L.tig;
     const int row_lo = g0 + g, row_hi = row_lo + 8;
-    const bool ok_lo = row_lo < N, ok_hi = row_hi < N;
+    const bool ok_lo = INTERIOR || row_lo < N, ok_hi = INTERIOR || row_hi < N;
     const size_t base = (size_t)bh * N * D;
     const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(a.q) + base;
-    const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(a.k) + base;
-    const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(a.v) + base;
+    // per-thread pointers to this thread's chunk of row row_lo of K and V
+    const __nv_bfloat16* kl = static_cast<const __nv_bfloat16*>(a.k) + base + (ptrdiff_t)row_lo * D + 8 * tig;
+    const __nv_bfloat16* vl = static_cast<const __nv_bfloat16*>(a.v) + base + (ptrdiff_t)row_lo * D + 8 * tig;
     const float c2 = a.scale * kLog2e;
-    const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1, nd = t.n_dense, ns = t.n_sparse;
     const int kb0 = g0 - WB;
 
     RowFrag<D> qa, qb;
     load_row(qa, qp + (size_t)row_lo * D, tig, ok_lo);
     load_row(qb, qp + (size_t)row_hi * D, tig, ok_hi);
 
-    // ---- dense window
+    // ---- dense window: key row of n-tile nt for this thread is kb0 + 8 nt + g = row_lo - WB + 8 nt
     float S[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        const int kr = kb0 + 8 * nt + g;
+        const float4 ini = init_s[nt * 32 + L.lane];
+        S[nt][0] = ini.x; S[nt][1] = ini.y; S[nt][2] = ini.z; S[nt][3] = ini.w;
         RowFrag<D> kf;
-        load_row(kf, kp + (size_t)kr * D, tig, kr >= 0 && kr < N);
-        mma_rows_z(S[nt], qa, qb, kf);
+        if (INTERIOR) {
+            load_row_at(kf, kl + (8 * nt - WB) * D);
+        } else {
+            const int kr = kb0 + 8 * nt + g;
+            load_row(kf, kl + (ptrdiff_t)(8 * nt - WB) * D - 8 * tig, tig, kr >= 0 && kr < N);
+        }
+        mma_rows(S[nt], qa, qb, kf);
+    }
+    if (!INTERIOR && kb0 < 0) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                if (kb0 + 8 * nt + 2 * tig + (r & 1) < 0) S[nt][r] = kNeg;
     }
     float m_lo = kMinM, m_hi = kMinM;
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int i = g + 8 * (r >> 1), c = 8 * nt + 2 * tig + (r & 1);
-            const int delta = WB + i - c;
-            const bool inband = delta >= d_lo && delta <= d_hi && kb0 + c >= 0;
-            const float s = inband ? fmaf(S[nt][r], c2, pb2_s[inband ? delta - d_lo : 0]) : kNeg;
-            S[nt][r] = s;
-            if (r < 2) m_lo = fmaxf(m_lo, s); else m_hi = fmaxf(m_hi, s);
-        }
-    m_lo = quad_max(m_lo); m_hi = quad_max(m_hi);
+    for (int nt = 0; nt < NT; ++nt) {
+        m_lo = fmaxf(m_lo, fmaxf(S[nt][0], S[nt][1]));
+        m_hi = fmaxf(m_hi, fmaxf(S[nt][2], S[nt][3]));
+    }
+    m_lo = quad_max(m_lo) * c2; m_hi = quad_max(m_hi) * c2;          // log2 units from here on
     float l_lo = 0.f, l_hi = 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        S[nt][0] = ex2(S[nt][0] - m_lo); S[nt][1] = ex2(S[nt][1] - m_lo);
-        S[nt][2] = ex2(S[nt][2] - m_hi); S[nt][3] = ex2(S[nt][3] - m_hi);
+        S[nt][0] = ex2(fmaf(S[nt][0], c2, -m_lo)); S[nt][1] = ex2(fmaf(S[nt][1], c2, -m_lo));
+        S[nt][2] = ex2(fmaf(S[nt][2], c2, -m_hi)); S[nt][3] = ex2(fmaf(S[nt][3], c2, -m_hi));
         l_lo += S[nt][0] + S[nt][1]; l_hi += S[nt][2] + S[nt][3];
     }
     float O[D / 8][4];
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) O[j][0] = O[j][1] = O[j][2] = O[j][3] = 0.f;
-#pragma unroll
     for (int c = 0; c < NT / 2; ++c) {
-        const int kr = kb0 + 16 * c + g;
         RowFrag<D> vf0, vf1, vt0, vt1;
-        load_row(vf0, vp + (size_t)kr * D, tig, kr >= 0 && kr < N);
-        load_row(vf1, vp + (size_t)(kr + 8) * D, tig, kr + 8 >= 0 && kr + 8 < N);
+        if (INTERIOR) {
+            load_row_at(vf0, vl + (16 * c - WB) * D);
+            load_row_at(vf1, vl + (16 * c + 8 - WB) * D);
+        } else {
+            const int kr = kb0 + 16 * c + g;
+            load_row(vf0, vl + (ptrdiff_t)(16 * c - WB) * D - 8 * tig, tig, kr >= 0 && kr < N);
+            load_row(vf1, vl + (ptrdiff_t)(16 * c + 8 - WB) * D - 8 * tig, tig, kr + 8 >= 0 && kr + 8 < N);
+        }
         transpose_frag(vt0, vf0); transpose_frag(vt1, vf1);
-        mma_cols<D>(O, pack_bf16x2(S[2 * c][0], S[2 * c][1]), pack_bf16x2(S[2 * c][2], S[2 * c][3]),
-                    pack_bf16x2(S[2 * c + 1][0], S[2 * c + 1][1]), pack_bf16x2(S[2 * c + 1][2], S[2 * c + 1][3]), vt0, vt1);
+        const uint32_t a0 = pack_bf16x2(S[2 * c][0], S[2 * c][1]), a1 = pack_bf16x2(S[2 * c][2], S[2 * c][3]);
+        const uint32_t a2 = pack_bf16x2(S[2 * c + 1][0], S[2 * c + 1][1]), a3 = pack_bf16x2(S[2 * c + 1][2], S[2 * c + 1][3]);
+        if (c == 0) {
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) mma16816_z(O[j], a0, a1, a2, a3, vt0.r[j], vt1.r[j]);
+        } else {
+            mma_cols<D>(O, a0, a1, a2, a3, vt0, vt1);
+        }
     }
-    // ---- sparse taps, one at a time
-#pragma unroll 1
-    for (int si = 0; si < ns; ++si) {
-        const int delta = t.sparse[si];
-        if (g0 + 15 < delta) break;                       // taps ascend: no row of the tile reaches back that far
-        const int kr0 = row_lo - delta, kr1 = row_hi - delta;
-        const bool v0 = kr0 >= 0 && ok_lo, v1 = kr1 >= 0 && ok_hi;
-        RowFrag<D> kf0, kf1, vf0, vf1;
-        load_row(kf0, kp + (size_t)kr0 * D, tig, v0);
-        load_row(kf1, kp + (size_t)kr1 * D, tig, v1);
-        load_row(vf0, vp + (size_t)kr0 * D, tig, v0);
-        load_row(vf1, vp + (size_t)kr1 * D, tig, v1);
-        float s0[4], s1[4];
-        mma_rows_z(s0, qa, qb, kf0);
-        mma_rows_z(s1, qa, qb, kf1);
-        const float pbv = pb2_s[nd + si];
-        const float x0 = v0 ? fmaf((g & 1) ? s0[1] : s0[0], c2, pbv) : kNeg;
-        const float x1 = v1 ? fmaf((g & 1) ? s1[3] : s1[2], c2, pbv) : kNeg;
-        const float mn_lo = fmaxf(m_lo, __shfl_sync(0xffffffffu, x0, L.owner_lane));
-        const float mn_hi = fmaxf(m_hi, __shfl_sync(0xffffffffu, x1, L.owner_lane));
-        if (__any_sync(0xffffffffu, mn_lo > m_lo || mn_hi > m_hi)) {
+    // ---- sparse taps
+    const uint32_t dmask = (g & 1) ? 0xffff0000u : 0x0000ffffu;
+    float ms_lo = L.owner ? m_lo : 1.0e30f, ms_hi = L.owner ? m_hi : 1.0e30f;   // what this lane subtracts
+    // Folds G taps whose scores x0[i] (row g) and x1[i] (row g+8) are known into the running softmax.
+    auto fold = [&](auto GC, const float (&x0)[decltype(GC)::value], const float (&x1)[decltype(GC)::value],
+                    const RowFrag<D> (&vf0)[decltype(GC)::value], const RowFrag<D> (&vf1)[decltype(GC)::value]) {
+        constexpr int G = decltype(GC)::value;
+        float xm0 = x0[0], xm1 = x1[0];
+#pragma unroll
+        for (int i = 1; i < G; ++i) { xm0 = fmaxf(xm0, x0[i]); xm1 = fmaxf(xm1, x1[i]); }
+        if (__any_sync(0xffffffffu, xm0 > ms_lo + kSlack || xm1 > ms_hi + kSlack)) {
+            const float mn_lo = fmaxf(m_lo, __shfl_sync(0xffffffffu, xm0, L.owner_lane));
+            const float mn_hi = fmaxf(m_hi, __shfl_sync(0xffffffffu, xm1, L.owner_lane));
             const float al_lo = ex2(m_lo - mn_lo), al_hi = ex2(m_hi - mn_hi);
             m_lo = mn_lo; m_hi = mn_hi;
+            ms_lo = L.owner ? m_lo : 1.0e30f; ms_hi = L.owner ? m_hi : 1.0e30f;
             l_lo *= al_lo; l_hi *= al_hi;
 #pragma unroll
             for (int j = 0; j < D / 8; ++j) { O[j][0] *= al_lo; O[j][1] *= al_lo; O[j][2] *= al_hi; O[j][3] *= al_hi; }
         }
-        const float p0 = ex2(x0 - m_lo), p1 = ex2(x1 - m_hi);
-        if (L.owner) { l_lo += p0; l_hi += p1; }
-        RowFrag<D> vt0, vt1;
-        transpose_frag(vt0, vf0); transpose_frag(vt1, vf1);
-        uint32_t a0, a3;
-        diag_frag(p0, p1, L.owner, g, a0, a3);
-        mma_cols<D>(O, a0, 0u, 0u, a3, vt0, vt1);
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            const float p0 = ex2(x0[i] - ms_lo), p1 = ex2(x1[i] - ms_hi);   // exactly 0 on lanes that own no diagonal entry
+            l_lo += p0; l_hi += p1;
+            RowFrag<D> vt0, vt1;
+            transpose_frag(vt0, vf0[i]); transpose_frag(vt1, vf1[i]);
+            mma_cols<D>(O, pack_bf16x2(p0, p0) & dmask, 0u, 0u, pack_bf16x2(p1, p1) & dmask, vt0, vt1);
+        }
+    };
+    // G consecutive taps whose 16 key rows all exist: no predicates, loads of all G taps in flight together
+    auto full_taps = [&](auto GC, int si) {
+        constexpr int G = decltype(GC)::value;
+        RowFrag<D> kf0[G], kf1[G], vf0[G], vf1[G];
+        float pbv[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            const int2 tp = tap_s[si + i];
+            const ptrdiff_t off = (ptrdiff_t)tp.x * D;
+            pbv[i] = __int_as_float(tp.y);
+            load_row_at(kf0[i], kl - off);
+            load_row_at(kf1[i], kl - off + 8 * D);
+            load_row_at(vf0[i], vl - off);
+            load_row_at(vf1[i], vl - off + 8 * D);
+        }
+        float x0[G], x1[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            float s0[4], s1[4];
+            mma_rows_z(s0, qa, qb, kf0[i]);
+            mma_rows_z(s1, qa, qb, kf1[i]);
+            x0[i] = fmaf((g & 1) ? s0[1] : s0[0], c2, pbv[i]);
+            x1[i] = fmaf((g & 1) ? s1[3] : s1[2], c2, pbv[i]);
+        }
+        fold(GC, x0, x1, vf0, vf1);
+    };
+    int si = 0;
+    for (; si + kTapGroup <= ns && g0 >= tap_s[si + kTapGroup - 1].x; si += kTapGroup)
+        full_taps(std::integral_constant<int, kTapGroup>(), si);
+#pragma unroll 1
+    for (; si < ns; ++si) {
+        const int delta = tap_s[si].x;
+        if (g0 + 15 < delta) break;                       // taps ascend: no row of the tile reaches back that far
+        if (g0 >= delta) {
+            full_taps(std::integral_constant<int, 1>(), si);
+        } else {                                          // some key rows lie before the sequence start
+            const float pbv = __int_as_float(tap_s[si].y);
+            const int kr0 = row_lo - delta, kr1 = row_hi - delta;
+            const bool v0 = kr0 >= 0, v1 = kr1 >= 0;
+            const ptrdiff_t off = (ptrdiff_t)delta * D + 8 * tig;
+            RowFrag<D> kf0, kf1, vf0[1], vf1[1];
+            load_row(kf0, kl - off, tig, v0);
+            load_row(kf1, kl - off + 8 * D, tig, v1);
+            load_row(vf0[0], vl - off, tig, v0);
+            load_row(vf1[0], vl - off + 8 * D, tig, v1);
+            float s0[4], s1[4];
+            mma_rows_z(s0, qa, qb, kf0);
+            mma_rows_z(s1, qa, qb, kf1);
+            const float x0[1] = {v0 ? fmaf((g & 1) ? s0[1] : s0[0], c2, pbv) : kNeg};
+            const float x1[1] = {v1 ? fmaf((g & 1) ? s1[3] : s1[2], c2, pbv) : kNeg};
+            fold(std::integral_constant<int, 1>(), x0, x1, vf0, vf1);
+        }
     }
     l_lo = quad_sum(l_lo); l_hi = quad_sum(l_hi);
     const float gain = a.head_gain ? a.head_gain[h] : 1.f;
@@ -151,134 +224,258 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
     }
 }
 
-// ------------------------------------------------------------------------------ backward: dQ
-// Also writes delta[n] = sum_d dout*out for the dK/dV kernel and the per-CTA partial sums of
-// dpos_bias (through a [J][rows] staging tile in shared memory, summed in a fixed order) and
-// of dhead_gain.
-// Resident CTAs per SM the backward kernels are compiled for (measured best on B200: the
-// register budget that follows trades spills against warps in flight).
-template <int D> struct BwdOccupancy { static constexpr int dq = D == 32 ? 6 : 4, dkdv = D == 32 ? 5 : 3; };
+// Tuning per head dimension (measured on B200): warps per CTA, sparse taps folded together,
+// resident CTAs per SM the register budget is set for.
+template <int D> struct FwdTune { static constexpr int warps = 4, group = D == 32 ? 2 : 3, ctas = D == 32 ? 5 : 4; };
 
 template <int D, int WB>
-__global__ void __launch_bounds__(kWarps * 32, BwdOccupancy<D>::dq)
-bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
+__global__ void __launch_bounds__(FwdTune<D>::warps * 32, FwdTune<D>::ctas)
+fwd_mma_kernel(const FwdArgs a, const Taps t) {
+    constexpr int W = FwdTune<D>::warps, G = FwdTune<D>::group;
     constexpr int NT = (WB + 16) / 8;
-    extern __shared__ float stage[];                   // [J][kStagePitch] ds values, then [128] dgain terms
-    __shared__ float pb2_s[DSQG_MAX_TAPS];
+    __shared__ float4 init_s[NT * 32];
+    __shared__ int2 tap_s[DSQG_MAX_TAPS];
     const Lane L;
-    const int bh = blockIdx.y, h = bh % a.H, N = a.N, J = t.J;
-    float* dg_s = stage + J * kStagePitch;
-    for (int j = threadIdx.x; j < J; j += kWarps * 32) pb2_s[j] = a.pos_bias[j * a.H + h] * kLog2e;
-    for (int i = threadIdx.x; i < J * kStagePitch; i += kWarps * 32) stage[i] = 0.f;
+    const int bh = blockIdx.y, h = bh % a.H, N = a.N;
+    {
+        const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1;
+        const float inv_scale = 1.f / a.scale;
+        for (int e = threadIdx.x; e < NT * 32; e += W * 32) {
+            const int nt = e >> 5, gg = (e & 31) >> 2, tt = e & 3;
+            float v[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int delta = WB + gg + 8 * (r >> 1) - (8 * nt + 2 * tt + (r & 1));
+                v[r] = (delta >= d_lo && delta <= d_hi) ? a.pos_bias[(delta - d_lo) * a.H + h] * inv_scale : kNeg;
+            }
+            init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
+        }
+        for (int si = threadIdx.x; si < t.n_sparse; si += W * 32)
+            tap_s[si] = make_int2(t.sparse[si], __float_as_int(a.pos_bias[(t.n_dense + si) * a.H + h] * kLog2e));
+    }
     __syncthreads();
-    const int g0 = blockIdx.x * kRows + L.warp * 16;
-    const int g = L.g, tig = L.tig;
+    const int g0 = blockIdx.x * (16 * W) + L.warp * 16;
+    if (g0 >= N) return;
+    if (g0 >= WB && g0 + 16 <= N) fwd_tile<D, WB, true, G>(a, init_s, tap_s, t.n_sparse, bh, h, g0, L);
+    else fwd_tile<D, WB, false, G>(a, init_s, tap_s, t.n_sparse, bh, h, g0, L);
+}
+
+// ------------------------------------------------------------------------------ backward: dQ
+// Also writes rowstat[n] = {lse[n]*log2(e) (0 for fully masked rows), sum_d dout*out} for the
+// dK/dV kernel and the per-CTA partial sums of dpos_bias (through a [J+1][kStagePitch] staging
+// tile in shared memory, summed in a fixed order; row J is a dump for out-of-band entries) and
+// of dhead_gain.  Every staging entry of a tile is written exactly once, so the tile is not
+// cleared.  As in the forward, mask and bias of the dense window are the initial value of the
+// score accumulators, and the staging offsets of the dense entries come from a per-lane table.
+// Tuning per head dimension (measured on B200): sparse taps whose loads are issued together and
+// resident CTAs per SM the register budget is set for (spills against warps in flight).
+template <int D> struct BwdTune {
+    static constexpr int dq_group = 1, dq_ctas = D == 32 ? 6 : 4;
+    static constexpr int dkdv_group = D == 32 ? 2 : 1, dkdv_ctas = D == 32 ? 4 : 3;
+};
+constexpr int kStagePitch = kRows + 3;      // 67: 2-way bank conflicts on the scattered writes, none on the column sums
+
+template <int D, int WB, bool INTERIOR, int G>
+__device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s, const int4* soff_s, const int2* tap_s,
+                                         float* stage_w, int nd, int ns, int bh, int h, int g0, const Lane& L) {
+    constexpr int NT = (WB + 16) / 8;
+    const int N = a.N, g = L.g, tig = L.tig;
+    const int row_lo = g0 + g, row_hi = row_lo + 8;
+    const bool ok_lo = INTERIOR || row_lo < N, ok_hi = INTERIOR || row_hi < N;
+    const size_t base = (size_t)bh * N * D;
+    const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(a.q) + base;
+    const __nv_bfloat16* op = static_cast<const __nv_bfloat16*>(a.out) + base;
+    const __nv_bfloat16* dop = static_cast<const __nv_bfloat16*>(a.dout) + base;
+    const __nv_bfloat16* kl = static_cast<const __nv_bfloat16*>(a.k) + base + (ptrdiff_t)row_lo * D + 8 * tig;
+    const __nv_bfloat16* vl = static_cast<const __nv_bfloat16*>(a.v) + base + (ptrdiff_t)row_lo * D + 8 * tig;
+    const float c2 = a.scale * kLog2e;
+    const float gain = a.head_gain ? a.head_gain[h] : 1.f;
+    const int kb0 = g0 - WB;
     float dgrow = 0.f;
-    if (g0 < N) {
-        const int row_lo = g0 + g, row_hi = row_lo + 8;
-        const int rs_lo = L.warp * 16 + g, rs_hi = rs_lo + 8;        // row inside the CTA tile
-        const bool ok_lo = row_lo < N, ok_hi = row_hi < N;
-        const size_t base = (size_t)bh * N * D;
-        const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(a.q) + base;
-        const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(a.k) + base;
-        const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(a.v) + base;
-        const __nv_bfloat16* op = static_cast<const __nv_bfloat16*>(a.out) + base;
-        const __nv_bfloat16* dop = static_cast<const __nv_bfloat16*>(a.dout) + base;
-        const float c2 = a.scale * kLog2e;
-        const float gain = a.head_gain ? a.head_gain[h] : 1.f;
-        const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1, nd = t.n_dense, ns = t.n_sparse;
-        const int kb0 = g0 - WB;
 
-        RowFrag<D> qa, qb, da, db;
-        load_row(qa, qp + (size_t)row_lo * D, tig, ok_lo);
-        load_row(qb, qp + (size_t)row_hi * D, tig, ok_hi);
-        load_row(da, dop + (size_t)row_lo * D, tig, ok_lo);
-        load_row(db, dop + (size_t)row_hi * D, tig, ok_hi);
-        float delta_lo, delta_hi;
-        {
-            RowFrag<D> oa, ob;
-            load_row(oa, op + (size_t)row_lo * D, tig, ok_lo);
-            load_row(ob, op + (size_t)row_hi * D, tig, ok_hi);
-            delta_lo = quad_sum(frag_dot(da, oa));
-            delta_hi = quad_sum(frag_dot(db, ob));
-        }
-        float l2_lo = 0.f, l2_hi = 0.f;
-        if (ok_lo) { const float x = a.lse[(size_t)bh * N + row_lo]; l2_lo = x == -INFINITY ? 0.f : x * kLog2e; }
-        if (ok_hi) { const float x = a.lse[(size_t)bh * N + row_hi]; l2_hi = x == -INFINITY ? 0.f : x * kLog2e; }
-        if (tig == 0) {
-            if (ok_lo) a.delta[(size_t)bh * N + row_lo] = delta_lo;
-            if (ok_hi) a.delta[(size_t)bh * N + row_hi] = delta_hi;
-        }
-        float dQ[D / 8][4];
-#pragma unroll
-        for (int j = 0; j < D / 8; ++j) dQ[j][0] = dQ[j][1] = dQ[j][2] = dQ[j][3] = 0.f;
+    RowFrag<D> qa, qb, da, db;
+    load_row(qa, qp + (size_t)row_lo * D, tig, ok_lo);
+    load_row(qb, qp + (size_t)row_hi * D, tig, ok_hi);
+    load_row(da, dop + (size_t)row_lo * D, tig, ok_lo);
+    load_row(db, dop + (size_t)row_hi * D, tig, ok_hi);
+    float delta_lo, delta_hi;
+    {
+        RowFrag<D> oa, ob;
+        load_row(oa, op + (size_t)row_lo * D, tig, ok_lo);
+        load_row(ob, op + (size_t)row_hi * D, tig, ok_hi);
+        delta_lo = quad_sum(frag_dot(da, oa));
+        delta_hi = quad_sum(frag_dot(db, ob));
+    }
+    float l2_lo = 0.f, l2_hi = 0.f;
+    if (ok_lo) { const float x = a.lse[(size_t)bh * N + row_lo]; l2_lo = x == -INFINITY ? 0.f : x * kLog2e; }
+    if (ok_hi) { const float x = a.lse[(size_t)bh * N + row_hi]; l2_hi = x == -INFINITY ? 0.f : x * kLog2e; }
+    if (tig == 0) {
+        float2* rs = reinterpret_cast<float2*>(a.delta) + (size_t)bh * N;
+        if (ok_lo) rs[row_lo] = make_float2(l2_lo, delta_lo);
+        if (ok_hi) rs[row_hi] = make_float2(l2_hi, delta_hi);
+    }
+    float dQ[D / 8][4];
 
+    // ---- dense window
 #pragma unroll
-        for (int c = 0; c < NT / 2; ++c) {
-            RowFrag<D> kf[2];
-            float ds[2][4];
+    for (int c = 0; c < NT / 2; ++c) {
+        RowFrag<D> kf[2];
+        float ds[2][4];
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                const int nt = 2 * c + hf;
+        for (int hf = 0; hf < 2; ++hf) {
+            const int nt = 2 * c + hf;
+            const float4 ini = init_s[nt * 32 + L.lane];
+            const int4 so = soff_s[nt * 32 + L.lane];
+            float s[4] = {ini.x, ini.y, ini.z, ini.w}, dp[4];
+            RowFrag<D> vf;
+            if (INTERIOR) {
+                load_row_at(kf[hf], kl + (8 * nt - WB) * D);
+                load_row_at(vf, vl + (8 * nt - WB) * D);
+            } else {
                 const int kr = kb0 + 8 * nt + g;
                 const bool kv = kr >= 0 && kr < N;
-                RowFrag<D> vf;
-                load_row(kf[hf], kp + (size_t)kr * D, tig, kv);
-                load_row(vf, vp + (size_t)kr * D, tig, kv);
-                float s[4], dp[4];
-                mma_rows_z(s, qa, qb, kf[hf]);
-                mma_rows_z(dp, da, db, vf);
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const int i = g + 8 * (r >> 1), cc = 8 * nt + 2 * tig + (r & 1);
-                    const int delta = WB + i - cc;
-                    const bool geom = delta >= d_lo && delta <= d_hi;
-                    const bool inband = geom && kb0 + cc >= 0 && (r < 2 ? ok_lo : ok_hi);
-                    const float p = inband ? ex2(fmaf(s[r], c2, pb2_s[inband ? delta - d_lo : 0]) - (r < 2 ? l2_lo : l2_hi)) : 0.f;
-                    dgrow = fmaf(p, dp[r], dgrow);
-                    const float x = p * (gain * dp[r] - (r < 2 ? delta_lo : delta_hi));
-                    ds[hf][r] = x;
-                    if (geom) stage[(delta - d_lo) * kStagePitch + (r < 2 ? rs_lo : rs_hi)] = x;
-                }
+                load_row(kf[hf], kl + (ptrdiff_t)(8 * nt - WB) * D - 8 * tig, tig, kv);
+                load_row(vf, vl + (ptrdiff_t)(8 * nt - WB) * D - 8 * tig, tig, kv);
             }
-            RowFrag<D> kt0, kt1;
-            transpose_frag(kt0, kf[0]); transpose_frag(kt1, kf[1]);
-            mma_cols<D>(dQ, pack_bf16x2(ds[0][0], ds[0][1]), pack_bf16x2(ds[0][2], ds[0][3]),
-                        pack_bf16x2(ds[1][0], ds[1][1]), pack_bf16x2(ds[1][2], ds[1][3]), kt0, kt1);
+            mma_rows(s, qa, qb, kf[hf]);
+            mma_rows_z(dp, da, db, vf);
+            if (!INTERIOR && kb0 < 0) {
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    if (kb0 + 8 * nt + 2 * tig + (r & 1) < 0) s[r] = kNeg;
+            }
+            const int so_r[4] = {so.x, so.y, so.z, so.w};
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float p = ex2(fmaf(s[r], c2, r < 2 ? -l2_lo : -l2_hi));
+                dgrow = fmaf(p, dp[r], dgrow);
+                const float x = p * fmaf(gain, dp[r], r < 2 ? -delta_lo : -delta_hi);
+                ds[hf][r] = x;
+                stage_w[so_r[r]] = x;
+            }
         }
+        RowFrag<D> kt0, kt1;
+        transpose_frag(kt0, kf[0]); transpose_frag(kt1, kf[1]);
+        const uint32_t a0 = pack_bf16x2(ds[0][0], ds[0][1]), a1 = pack_bf16x2(ds[0][2], ds[0][3]);
+        const uint32_t a2 = pack_bf16x2(ds[1][0], ds[1][1]), a3 = pack_bf16x2(ds[1][2], ds[1][3]);
+        if (c == 0) {
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) mma16816_z(dQ[j], a0, a1, a2, a3, kt0.r[j], kt1.r[j]);
+        } else {
+            mma_cols<D>(dQ, a0, a1, a2, a3, kt0, kt1);
+        }
+    }
+    // ---- sparse taps
+    const uint32_t dmask = L.owner ? ((g & 1) ? 0xffff0000u : 0x0000ffffu) : 0u;
+    const float ls_lo = L.owner ? l2_lo : 1.0e30f, ls_hi = L.owner ? l2_hi : 1.0e30f;   // p == 0 on lanes without a diagonal entry
+    float* stage_sp = stage_w + nd * kStagePitch + g;
+    auto finish = [&](int si, float sd0, float sd1, float dp0, float dp1, float pbv, bool v0, bool v1,
+                      const RowFrag<D>& kf0, const RowFrag<D>& kf1) {
+        const float p0 = v0 ? ex2(fmaf(sd0, c2, pbv) - ls_lo) : 0.f;
+        const float p1 = v1 ? ex2(fmaf(sd1, c2, pbv) - ls_hi) : 0.f;
+        dgrow = fmaf(p0, dp0, dgrow); dgrow = fmaf(p1, dp1, dgrow);
+        const float x0 = p0 * fmaf(gain, dp0, -delta_lo), x1 = p1 * fmaf(gain, dp1, -delta_hi);
+        if (L.owner) { stage_sp[si * kStagePitch] = x0; stage_sp[si * kStagePitch + 8] = x1; }
+        RowFrag<D> kt0, kt1;
+        transpose_frag(kt0, kf0); transpose_frag(kt1, kf1);
+        mma_cols<D>(dQ, pack_bf16x2(x0, x0) & dmask, 0u, 0u, pack_bf16x2(x1, x1) & dmask, kt0, kt1);
+    };
+    auto full_taps = [&](auto GC, int si) {
+        constexpr int GG = decltype(GC)::value;
+        RowFrag<D> kf0[GG], kf1[GG], vf0[GG], vf1[GG];
+        float pbv[GG];
+#pragma unroll
+        for (int i = 0; i < GG; ++i) {
+            const int2 tp = tap_s[si + i];
+            const ptrdiff_t off = (ptrdiff_t)tp.x * D;
+            pbv[i] = __int_as_float(tp.y);
+            load_row_at(kf0[i], kl - off);
+            load_row_at(kf1[i], kl - off + 8 * D);
+            load_row_at(vf0[i], vl - off);
+            load_row_at(vf1[i], vl - off + 8 * D);
+        }
+#pragma unroll
+        for (int i = 0; i < GG; ++i) {
+            float s0[4], s1[4], e0[4], e1[4];
+            mma_rows_z(s0, qa, qb, kf0[i]); mma_rows_z(s1, qa, qb, kf1[i]);
+            mma_rows_z(e0, da, db, vf0[i]); mma_rows_z(e1, da, db, vf1[i]);
+            finish(si + i, (g & 1) ? s0[1] : s0[0], (g & 1) ? s1[3] : s1[2], (g & 1) ? e0[1] : e0[0],
+                   (g & 1) ? e1[3] : e1[2], pbv[i], true, true, kf0[i], kf1[i]);
+        }
+    };
+    int si = 0;
+    for (; si + G <= ns && g0 >= tap_s[si + G - 1].x; si += G) full_taps(std::integral_constant<int, G>(), si);
 #pragma unroll 1
-        for (int si = 0; si < ns; ++si) {
-            const int delta = t.sparse[si];
-            if (g0 + 15 < delta) break;
-            const int kr0 = row_lo - delta, kr1 = row_hi - delta;
-            const bool v0 = kr0 >= 0 && ok_lo, v1 = kr1 >= 0 && ok_hi;
+    for (; si < ns; ++si) {
+        const int delta = tap_s[si].x;
+        if (g0 + 15 < delta) break;
+        if (g0 >= delta) {
+            full_taps(std::integral_constant<int, 1>(), si);
+        } else {
+            const float pbv = __int_as_float(tap_s[si].y);
+            const bool v0 = row_lo >= delta, v1 = row_hi >= delta;
+            const ptrdiff_t off = (ptrdiff_t)delta * D + 8 * tig;
             RowFrag<D> kf0, kf1, vf0, vf1;
-            load_row(kf0, kp + (size_t)kr0 * D, tig, v0);
-            load_row(kf1, kp + (size_t)kr1 * D, tig, v1);
-            load_row(vf0, vp + (size_t)kr0 * D, tig, v0);
-            load_row(vf1, vp + (size_t)kr1 * D, tig, v1);
+            load_row(kf0, kl - off, tig, v0);
+            load_row(kf1, kl - off + 8 * D, tig, v1);
+            load_row(vf0, vl - off, tig, v0);
+            load_row(vf1, vl - off + 8 * D, tig, v1);
             float s0[4], s1[4], e0[4], e1[4];
             mma_rows_z(s0, qa, qb, kf0); mma_rows_z(s1, qa, qb, kf1);
             mma_rows_z(e0, da, db, vf0); mma_rows_z(e1, da, db, vf1);
-            const float pbv = pb2_s[nd + si];
-            const float sd0 = (g & 1) ? s0[1] : s0[0], sd1 = (g & 1) ? s1[3] : s1[2];
-            const float dp0 = (g & 1) ? e0[1] : e0[0], dp1 = (g & 1) ? e1[3] : e1[2];
-            const float p0 = v0 ? ex2(fmaf(sd0, c2, pbv) - l2_lo) : 0.f;
-            const float p1 = v1 ? ex2(fmaf(sd1, c2, pbv) - l2_hi) : 0.f;
-            const float x0 = p0 * (gain * dp0 - delta_lo), x1 = p1 * (gain * dp1 - delta_hi);
-            if (L.owner) {
-                dgrow = fmaf(p0, dp0, dgrow); dgrow = fmaf(p1, dp1, dgrow);
-                stage[(nd + si) * kStagePitch + rs_lo] = x0;
-                stage[(nd + si) * kStagePitch + rs_hi] = x1;
-            }
-            uint32_t a0, a3;
-            diag_frag(x0, x1, L.owner, g, a0, a3);
-            RowFrag<D> kt0, kt1;
-            transpose_frag(kt0, kf0); transpose_frag(kt1, kf1);
-            mma_cols<D>(dQ, a0, 0u, 0u, a3, kt0, kt1);
+            finish(si, (g & 1) ? s0[1] : s0[0], (g & 1) ? s1[3] : s1[2], (g & 1) ? e0[1] : e0[0],
+                   (g & 1) ? e1[3] : e1[2], pbv, v0, v1, kf0, kf1);
         }
-        __nv_bfloat16* dqp = static_cast<__nv_bfloat16*>(a.dq) + base;
-        store_acc_rows<D>(dQ, dqp + (size_t)row_lo * D, dqp + (size_t)row_hi * D, ok_lo, ok_hi, a.scale, a.scale, tig);
+    }
+    if (L.owner)                                          // taps no row of the tile reaches: zero entries
+        for (; si < ns; ++si) { stage_sp[si * kStagePitch] = 0.f; stage_sp[si * kStagePitch + 8] = 0.f; }
+    __nv_bfloat16* dqp = static_cast<__nv_bfloat16*>(a.dq) + base;
+    store_acc_rows<D>(dQ, dqp + (size_t)row_lo * D, dqp + (size_t)row_hi * D, ok_lo, ok_hi, a.scale, a.scale, tig);
+    return dgrow;
+}
+
+template <int D, int WB, int G, int CT>
+__global__ void __launch_bounds__(kWarps * 32, CT)
+bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
+    constexpr int NT = (WB + 16) / 8;
+    extern __shared__ float stage[];                   // [J + 1][kStagePitch] ds values, then [128] dgain terms
+    __shared__ float4 init_s[NT * 32];
+    __shared__ int4 soff_s[NT * 32];
+    __shared__ int2 tap_s[DSQG_MAX_TAPS];
+    const Lane L;
+    const int bh = blockIdx.y, h = bh % a.H, N = a.N, J = t.J;
+    float* dg_s = stage + (J + 1) * kStagePitch;
+    {
+        const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1;
+        const float inv_scale = 1.f / a.scale;
+        for (int e = threadIdx.x; e < NT * 32; e += kWarps * 32) {
+            const int nt = e >> 5, gg = (e & 31) >> 2, tt = e & 3;
+            float v[4];
+            int o[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int i = gg + 8 * (r >> 1);
+                const int delta = WB + i - (8 * nt + 2 * tt + (r & 1));
+                const bool inband = delta >= d_lo && delta <= d_hi;
+                v[r] = inband ? a.pos_bias[(delta - d_lo) * a.H + h] * inv_scale : kNeg;
+                o[r] = (inband ? delta - d_lo : J) * kStagePitch + i;
+            }
+            init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
+            soff_s[e] = make_int4(o[0], o[1], o[2], o[3]);
+        }
+        for (int si = threadIdx.x; si < t.n_sparse; si += kWarps * 32)
+            tap_s[si] = make_int2(t.sparse[si], __float_as_int(a.pos_bias[(t.n_dense + si) * a.H + h] * kLog2e));
+    }
+    __syncthreads();
+    const int g0 = blockIdx.x * kRows + L.warp * 16;
+    float* stage_w = stage + L.warp * 16;
+    float dgrow = 0.f;
+    if (g0 >= N) {                                      // no rows: this warp's staging columns are zero
+        for (int e = L.lane; e < J * 16; e += 32) stage_w[(e >> 4) * kStagePitch + (e & 15)] = 0.f;
+    } else if (g0 >= WB && g0 + 16 <= N) {
+        dgrow = dq_tile<D, WB, true, G>(a, init_s, soff_s, tap_s, stage_w, t.n_dense, t.n_sparse, bh, h, g0, L);
+    } else {
+        dgrow = dq_tile<D, WB, false, G>(a, init_s, soff_s, tap_s, stage_w, t.n_dense, t.n_sparse, bh, h, g0, L);
     }
     dg_s[threadIdx.x] = dgrow;
     __syncthreads();
@@ -286,6 +483,7 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
     if (threadIdx.x < J) {
         float s = 0.f;
         const float* row = stage + threadIdx.x * kStagePitch;
+#pragma unroll 8
         for (int r = 0; r < kRows; ++r) s += row[r];
         a.dpb_part[(size_t)tile * J + threadIdx.x] = s;
     } else if (threadIdx.x == kWarps * 32 - 1) {
@@ -298,31 +496,23 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
 // ------------------------------------------------------------------------------ backward: dK, dV
 // The warp owns 16 key rows; the roles of rows and columns are swapped: S^T = K.Q^T over the
 // query rows [m0, m0+16+WB) for the dense window and the diagonal of the tile at m0+delta for
-// every sparse tap.  Key rows are owned by exactly one warp: no atomics.
-template <int D, int WB>
-__global__ void __launch_bounds__(kWarps * 32, BwdOccupancy<D>::dkdv)
-bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t) {
+// every sparse tap.  Key rows are owned by exactly one warp: no atomics.  The per-query
+// statistics {lse*log2(e), delta} of the CTA's dense query range sit in shared memory.
+template <int D, int WB, bool INTERIOR, int G>
+__device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s, const int2* tap_s, const float2* stat_w,
+                                          int ns, int bh, int h, int m0, const Lane& L) {
     constexpr int NT = (WB + 16) / 8;
-    __shared__ float pb2_s[DSQG_MAX_TAPS];
-    const Lane L;
-    const int bh = blockIdx.y, h = bh % a.H, N = a.N;
-    for (int j = threadIdx.x; j < t.J; j += kWarps * 32) pb2_s[j] = a.pos_bias[j * a.H + h] * kLog2e;
-    __syncthreads();
-    const int m0 = blockIdx.x * kRows + L.warp * 16;
-    if (m0 >= N) return;
-    const int g = L.g, tig = L.tig;
+    const int N = a.N, g = L.g, tig = L.tig;
     const int row_lo = m0 + g, row_hi = row_lo + 8;
-    const bool ok_lo = row_lo < N, ok_hi = row_hi < N;
+    const bool ok_lo = INTERIOR || row_lo < N, ok_hi = INTERIOR || row_hi < N;
     const size_t base = (size_t)bh * N * D;
-    const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(a.q) + base;
     const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(a.k) + base;
     const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(a.v) + base;
-    const __nv_bfloat16* dop = static_cast<const __nv_bfloat16*>(a.dout) + base;
-    const float* lse = a.lse + (size_t)bh * N;
-    const float* dl = a.delta + (size_t)bh * N;
+    const __nv_bfloat16* ql = static_cast<const __nv_bfloat16*>(a.q) + base + (ptrdiff_t)row_lo * D + 8 * tig;
+    const __nv_bfloat16* dl = static_cast<const __nv_bfloat16*>(a.dout) + base + (ptrdiff_t)row_lo * D + 8 * tig;
+    const float2* rs = reinterpret_cast<const float2*>(a.delta) + (size_t)bh * N + row_lo;
     const float c2 = a.scale * kLog2e;
     const float gain = a.head_gain ? a.head_gain[h] : 1.f;
-    const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1, nd = t.n_dense, ns = t.n_sparse;
 
     RowFrag<D> ka, kb, va, vb;
     load_row(ka, kp + (size_t)row_lo * D, tig, ok_lo);
@@ -330,84 +520,121 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t) {
     load_row(va, vp + (size_t)row_lo * D, tig, ok_lo);
     load_row(vb, vp + (size_t)row_hi * D, tig, ok_hi);
     float dK[D / 8][4], dV[D / 8][4];
-#pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
-        dK[j][0] = dK[j][1] = dK[j][2] = dK[j][3] = 0.f;
-        dV[j][0] = dV[j][1] = dV[j][2] = dV[j][3] = 0.f;
-    }
 
+    // ---- dense window: query row of n-tile nt for this thread is m0 + 8 nt + g
 #pragma unroll
     for (int c = 0; c < NT / 2; ++c) {
-        if (m0 + 16 * c >= N) break;                    // warp-uniform: no query rows left
+        if (!INTERIOR && c > 0 && m0 + 16 * c >= N) break;   // warp-uniform: no query rows left
         RowFrag<D> qf[2], df[2];
         float ds[2][4], pv[2][4];
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
             const int nt = 2 * c + hf;
-            const int qr = m0 + 8 * nt + g;
-            load_row(qf[hf], qp + (size_t)qr * D, tig, qr < N);
-            load_row(df[hf], dop + (size_t)qr * D, tig, qr < N);
-            float s[4], dp[4];
-            mma_rows_z(s, ka, kb, qf[hf]);
-            mma_rows_z(dp, va, vb, df[hf]);
-            // this thread's two query columns of the n-tile
-            const int qc = m0 + 8 * nt + 2 * tig;
-            float l2c[2], dlc[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const bool qv = qc + e < N;
-                const float x = qv ? lse[qc + e] : 0.f;
-                l2c[e] = x == -INFINITY ? 0.f : x * kLog2e;
-                dlc[e] = qv ? dl[qc + e] : 0.f;
+            const float4 ini = init_s[nt * 32 + L.lane];
+            float s[4] = {ini.x, ini.y, ini.z, ini.w}, dp[4];
+            if (INTERIOR) {
+                load_row_at(qf[hf], ql + 8 * nt * D);
+                load_row_at(df[hf], dl + 8 * nt * D);
+            } else {
+                const bool qv = m0 + 8 * nt + g < N;
+                load_row(qf[hf], ql + (ptrdiff_t)8 * nt * D - 8 * tig, tig, qv);
+                load_row(df[hf], dl + (ptrdiff_t)8 * nt * D - 8 * tig, tig, qv);
             }
+            mma_rows(s, ka, kb, qf[hf]);
+            mma_rows_z(dp, va, vb, df[hf]);
+            // statistics of this thread's two query columns: {l2, delta} x 2
+            const float4 st = *reinterpret_cast<const float4*>(stat_w + 8 * nt + 2 * tig);
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
-                const int i = g + 8 * (r >> 1), cc = 8 * nt + 2 * tig + (r & 1);
-                const int delta = cc - i;
-                const bool inband = delta >= d_lo && delta <= d_hi && m0 + cc < N;
-                const float p = inband ? ex2(fmaf(s[r], c2, pb2_s[inband ? delta - d_lo : 0]) - l2c[r & 1]) : 0.f;
-                ds[hf][r] = p * (gain * dp[r] - dlc[r & 1]);
+                const float p = ex2(fmaf(s[r], c2, (r & 1) ? -st.z : -st.x));
+                ds[hf][r] = p * fmaf(gain, dp[r], (r & 1) ? -st.w : -st.y);
                 pv[hf][r] = p * gain;
             }
         }
         RowFrag<D> t0, t1;
         transpose_frag(t0, df[0]); transpose_frag(t1, df[1]);
-        mma_cols<D>(dV, pack_bf16x2(pv[0][0], pv[0][1]), pack_bf16x2(pv[0][2], pv[0][3]),
-                    pack_bf16x2(pv[1][0], pv[1][1]), pack_bf16x2(pv[1][2], pv[1][3]), t0, t1);
+        const uint32_t b0 = pack_bf16x2(pv[0][0], pv[0][1]), b1 = pack_bf16x2(pv[0][2], pv[0][3]);
+        const uint32_t b2 = pack_bf16x2(pv[1][0], pv[1][1]), b3 = pack_bf16x2(pv[1][2], pv[1][3]);
+        const uint32_t a0 = pack_bf16x2(ds[0][0], ds[0][1]), a1 = pack_bf16x2(ds[0][2], ds[0][3]);
+        const uint32_t a2 = pack_bf16x2(ds[1][0], ds[1][1]), a3 = pack_bf16x2(ds[1][2], ds[1][3]);
+        if (c == 0) {
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) mma16816_z(dV[j], b0, b1, b2, b3, t0.r[j], t1.r[j]);
+        } else {
+            mma_cols<D>(dV, b0, b1, b2, b3, t0, t1);
+        }
         transpose_frag(t0, qf[0]); transpose_frag(t1, qf[1]);
-        mma_cols<D>(dK, pack_bf16x2(ds[0][0], ds[0][1]), pack_bf16x2(ds[0][2], ds[0][3]),
-                    pack_bf16x2(ds[1][0], ds[1][1]), pack_bf16x2(ds[1][2], ds[1][3]), t0, t1);
+        if (c == 0) {
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) mma16816_z(dK[j], a0, a1, a2, a3, t0.r[j], t1.r[j]);
+        } else {
+            mma_cols<D>(dK, a0, a1, a2, a3, t0, t1);
+        }
     }
-#pragma unroll 1
-    for (int si = 0; si < ns; ++si) {
-        const int delta = t.sparse[si];
-        if (m0 + delta >= N) break;                     // taps ascend: no query row reads these keys any more
-        const int qr0 = row_lo + delta, qr1 = row_hi + delta;
-        const bool v0 = qr0 < N, v1 = qr1 < N;
-        RowFrag<D> qf0, qf1, df0, df1;
-        load_row(qf0, qp + (size_t)qr0 * D, tig, v0);
-        load_row(qf1, qp + (size_t)qr1 * D, tig, v1);
-        load_row(df0, dop + (size_t)qr0 * D, tig, v0);
-        load_row(df1, dop + (size_t)qr1 * D, tig, v1);
-        float s0[4], s1[4], e0[4], e1[4];
-        mma_rows_z(s0, ka, kb, qf0); mma_rows_z(s1, ka, kb, qf1);
-        mma_rows_z(e0, va, vb, df0); mma_rows_z(e1, va, vb, df1);
-        const float pbv = pb2_s[nd + si];
-        const float sd0 = (g & 1) ? s0[1] : s0[0], sd1 = (g & 1) ? s1[3] : s1[2];
-        const float dp0 = (g & 1) ? e0[1] : e0[0], dp1 = (g & 1) ? e1[3] : e1[2];
-        float l0 = 0.f, l1 = 0.f, dl0 = 0.f, dl1 = 0.f;
-        if (v0) { const float x = lse[qr0]; l0 = x == -INFINITY ? 0.f : x * kLog2e; dl0 = dl[qr0]; }
-        if (v1) { const float x = lse[qr1]; l1 = x == -INFINITY ? 0.f : x * kLog2e; dl1 = dl[qr1]; }
-        const float p0 = v0 ? ex2(fmaf(sd0, c2, pbv) - l0) : 0.f;
-        const float p1 = v1 ? ex2(fmaf(sd1, c2, pbv) - l1) : 0.f;
-        uint32_t a0, a3;
+    // ---- sparse taps
+    const uint32_t dmask = L.owner ? ((g & 1) ? 0xffff0000u : 0x0000ffffu) : 0u;
+    auto finish = [&](float sd0, float sd1, float dp0, float dp1, float pbv, float2 st0, float2 st1,
+                      const RowFrag<D>& qf0, const RowFrag<D>& qf1, const RowFrag<D>& df0, const RowFrag<D>& df1) {
+        const float p0 = ex2(fmaf(sd0, c2, pbv) - st0.x), p1 = ex2(fmaf(sd1, c2, pbv) - st1.x);
+        const float w0 = p0 * gain, w1 = p1 * gain;
+        const float x0 = p0 * fmaf(gain, dp0, -st0.y), x1 = p1 * fmaf(gain, dp1, -st1.y);
         RowFrag<D> t0, t1;
-        diag_frag(p0 * gain, p1 * gain, L.owner, g, a0, a3);
         transpose_frag(t0, df0); transpose_frag(t1, df1);
-        mma_cols<D>(dV, a0, 0u, 0u, a3, t0, t1);
-        diag_frag(p0 * (gain * dp0 - dl0), p1 * (gain * dp1 - dl1), L.owner, g, a0, a3);
+        mma_cols<D>(dV, pack_bf16x2(w0, w0) & dmask, 0u, 0u, pack_bf16x2(w1, w1) & dmask, t0, t1);
         transpose_frag(t0, qf0); transpose_frag(t1, qf1);
-        mma_cols<D>(dK, a0, 0u, 0u, a3, t0, t1);
+        mma_cols<D>(dK, pack_bf16x2(x0, x0) & dmask, 0u, 0u, pack_bf16x2(x1, x1) & dmask, t0, t1);
+    };
+    auto full_taps = [&](auto GC, int si) {
+        constexpr int GG = decltype(GC)::value;
+        RowFrag<D> qf0[GG], qf1[GG], df0[GG], df1[GG];
+        float2 st0[GG], st1[GG];
+        float pbv[GG];
+#pragma unroll
+        for (int i = 0; i < GG; ++i) {
+            const int2 tp = tap_s[si + i];
+            const ptrdiff_t off = (ptrdiff_t)tp.x * D;
+            pbv[i] = __int_as_float(tp.y);
+            load_row_at(qf0[i], ql + off);
+            load_row_at(qf1[i], ql + off + 8 * D);
+            load_row_at(df0[i], dl + off);
+            load_row_at(df1[i], dl + off + 8 * D);
+            st0[i] = __ldg(rs + tp.x);
+            st1[i] = __ldg(rs + tp.x + 8);
+        }
+#pragma unroll
+        for (int i = 0; i < GG; ++i) {
+            float s0[4], s1[4], e0[4], e1[4];
+            mma_rows_z(s0, ka, kb, qf0[i]); mma_rows_z(s1, ka, kb, qf1[i]);
+            mma_rows_z(e0, va, vb, df0[i]); mma_rows_z(e1, va, vb, df1[i]);
+            finish((g & 1) ? s0[1] : s0[0], (g & 1) ? s1[3] : s1[2], (g & 1) ? e0[1] : e0[0], (g & 1) ? e1[3] : e1[2],
+                   pbv[i], st0[i], st1[i], qf0[i], qf1[i], df0[i], df1[i]);
+        }
+    };
+    int si = 0;
+    for (; si + G <= ns && m0 + 16 + tap_s[si + G - 1].x <= N; si += G) full_taps(std::integral_constant<int, G>(), si);
+#pragma unroll 1
+    for (; si < ns; ++si) {
+        const int delta = tap_s[si].x;
+        if (m0 + delta >= N) break;                     // taps ascend: no query row reads these keys any more
+        if (m0 + 16 + delta <= N) {
+            full_taps(std::integral_constant<int, 1>(), si);
+        } else {
+            const float pbv = __int_as_float(tap_s[si].y);
+            const bool v0 = row_lo + delta < N, v1 = row_hi + delta < N;
+            const ptrdiff_t off = (ptrdiff_t)delta * D - 8 * tig;
+            RowFrag<D> qf0, qf1, df0, df1;
+            load_row(qf0, ql + off, tig, v0);
+            load_row(qf1, ql + off + 8 * D, tig, v1);
+            load_row(df0, dl + off, tig, v0);
+            load_row(df1, dl + off + 8 * D, tig, v1);
+            const float2 st0 = v0 ? __ldg(rs + delta) : make_float2(0.f, 0.f);
+            const float2 st1 = v1 ? __ldg(rs + delta + 8) : make_float2(0.f, 0.f);
+            float s0[4], s1[4], e0[4], e1[4];
+            mma_rows_z(s0, ka, kb, qf0); mma_rows_z(s1, ka, kb, qf1);
+            mma_rows_z(e0, va, vb, df0); mma_rows_z(e1, va, vb, df1);
+            finish((g & 1) ? s0[1] : s0[0], (g & 1) ? s1[3] : s1[2], (g & 1) ? e0[1] : e0[0], (g & 1) ? e1[3] : e1[2],
+                   pbv, st0, st1, qf0, qf1, df0, df1);
+        }
     }
     __nv_bfloat16* dkp = static_cast<__nv_bfloat16*>(a.dk) + base;
     __nv_bfloat16* dvp = static_cast<__nv_bfloat16*>(a.dv) + base;
@@ -415,29 +642,69 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t) {
     store_acc_rows<D>(dV, dvp + (size_t)row_lo * D, dvp + (size_t)row_hi * D, ok_lo, ok_hi, 1.f, 1.f, tig);
 }
 
+template <int D, int WB, int G, int CT>
+__global__ void __launch_bounds__(kWarps * 32, CT)
+bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t) {
+    constexpr int NT = (WB + 16) / 8;
+    constexpr int kStat = kRows + WB;                  // query rows the CTA's dense windows touch
+    __shared__ float4 init_s[NT * 32];
+    __shared__ int2 tap_s[DSQG_MAX_TAPS];
+    __shared__ __align__(16) float2 stat_s[kStat];
+    const Lane L;
+    const int bh = blockIdx.y, h = bh % a.H, N = a.N;
+    const int m_cta = blockIdx.x * kRows;
+    {
+        const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1;
+        const float inv_scale = 1.f / a.scale;
+        for (int e = threadIdx.x; e < NT * 32; e += kWarps * 32) {
+            const int nt = e >> 5, gg = (e & 31) >> 2, tt = e & 3;
+            float v[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int delta = 8 * nt + 2 * tt + (r & 1) - (gg + 8 * (r >> 1));
+                v[r] = (delta >= d_lo && delta <= d_hi) ? a.pos_bias[(delta - d_lo) * a.H + h] * inv_scale : kNeg;
+            }
+            init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
+        }
+        for (int si = threadIdx.x; si < t.n_sparse; si += kWarps * 32)
+            tap_s[si] = make_int2(t.sparse[si], __float_as_int(a.pos_bias[(t.n_dense + si) * a.H + h] * kLog2e));
+        const float2* rs = reinterpret_cast<const float2*>(a.delta) + (size_t)bh * N;
+        for (int i = threadIdx.x; i < kStat; i += kWarps * 32)
+            stat_s[i] = m_cta + i < N ? rs[m_cta + i] : make_float2(0.f, 0.f);
+    }
+    __syncthreads();
+    const int m0 = m_cta + L.warp * 16;
+    if (m0 >= N) return;
+    if (m0 + 16 + WB <= N) dkdv_tile<D, WB, true, G>(a, init_s, tap_s, stat_s + L.warp * 16, t.n_sparse, bh, h, m0, L);
+    else dkdv_tile<D, WB, false, G>(a, init_s, tap_s, stat_s + L.warp * 16, t.n_sparse, bh, h, m0, L);
+}
+
 template <int D, int WB>
 cudaError_t fwd_launch_mma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
-    dim3 grid((a.N + kRows - 1) / kRows, a.B * a.H);
-    fwd_mma_kernel<D, WB><<<grid, kWarps * 32, 0, s>>>(a, t);
+    constexpr int rows = 16 * FwdTune<D>::warps;
+    dim3 grid((a.N + rows - 1) / rows, a.B * a.H);
+    fwd_mma_kernel<D, WB><<<grid, FwdTune<D>::warps * 32, 0, s>>>(a, t);
     return cudaGetLastError();
 }
 
 template <int D, int WB>
 cudaError_t bwd_launch_mma(BwdArgs a, const Taps& t, cudaStream_t s, int stages) {
+    using T = BwdTune<D>;
     carve_bwd_scratch(a, kRows, t.J, false);
     dim3 grid((a.N + kRows - 1) / kRows, a.B * a.H);
     cudaError_t e = cudaSuccess;
     if (stages & DSQG_BWD_STAGE_DQ) {
-        const size_t smem = sizeof(float) * ((size_t)t.J * kStagePitch + kWarps * 32);
+        const size_t smem = sizeof(float) * ((size_t)(t.J + 1) * kStagePitch + kWarps * 32);
         if (smem > 48 * 1024) {
-            e = cudaFuncSetAttribute(bwd_dq_mma_kernel<D, WB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            e = cudaFuncSetAttribute(bwd_dq_mma_kernel<D, WB, T::dq_group, T::dq_ctas>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
         }
-        bwd_dq_mma_kernel<D, WB><<<grid, kWarps * 32, smem, s>>>(a, t);
+        bwd_dq_mma_kernel<D, WB, T::dq_group, T::dq_ctas><<<grid, kWarps * 32, smem, s>>>(a, t);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
     if (stages & DSQG_BWD_STAGE_DKDV) {
-        bwd_dkdv_mma_kernel<D, WB><<<grid, kWarps * 32, 0, s>>>(a, t);
+        bwd_dkdv_mma_kernel<D, WB, T::dkdv_group, T::dkdv_ctas><<<grid, kWarps * 32, 0, s>>>(a, t);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
     if (stages & DSQG_BWD_STAGE_REDUCE) e = launch_reduce_params(a, t.J, s);
