@@ -6,8 +6,9 @@ from .ops import (ALL_OFFSETS, OFFSETS_43, OFFSETS_45, SPARSE_TAPS, DSQGFunction
 from .modules import (DSQGAttentionN_Fused, DSQGAttentionQW, DSQGAttentionV3, dsqg_attention_v2,
                       dsqg_attention_v3)
 from .decode import DSQGRingCache, dsqg_decode_step
+from .host import DSQGHostPipeline
 from ._lib import DSQGError
 
 __all__ = ["ALL_OFFSETS", "OFFSETS_43", "OFFSETS_45", "SPARSE_TAPS", "DSQGFunction", "dsqg_attention",
            "dsqg_forward_lse", "DSQGAttentionN_Fused", "DSQGAttentionQW", "DSQGAttentionV3",
-           "dsqg_attention_v2", "dsqg_attention_v3", "DSQGRingCache", "dsqg_decode_step", "DSQGError"]
+           "dsqg_attention_v2", "dsqg_attention_v3", "DSQGRingCache", "dsqg_decode_step", "DSQGHostPipeline", "DSQGError"]

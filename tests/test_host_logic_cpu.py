@@ -50,6 +50,13 @@ def test_compat_shims_export_reference_names():
     assert callable(s3.dsqg_attention_v3) and s3.DSQGAttentionV3
 
 
+def test_host_pipeline_needs_a_cuda_device():
+    with pytest.raises(RuntimeError):
+        dwarf_b200.DSQGHostPipeline((1, 2, 64, 32), torch.bfloat16, (0, 1, 2), "cpu")
+    with pytest.raises(ValueError):
+        dwarf_b200.DSQGHostPipeline((1, 2, 64, 32), torch.bfloat16, (0, 1, 2), "cuda:0", depth=0)
+
+
 def test_synthetic_inputs_are_seeded_and_prefix_stable():
     cfg = synth.OP_CONFIGS["cfg1"]
     a = synth.make_op_inputs(cfg, B=2)
