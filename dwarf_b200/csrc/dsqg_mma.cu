@@ -4,8 +4,10 @@
 // banded GEMM: the 16 query rows against the WB+16 key rows [g0-WB, g0+16) with
 // mma.sync.m16n8k16; out-of-band entries are masked.  Every sparse tap pairs row n with row
 // n-delta, i.e. it is the diagonal of a 16x16 tile: its scores come from two m16n8 MMAs per
-// k-step, of which the thread with tig == g>>1 keeps the diagonal entries, and its value
-// products use a diagonal A fragment.  The math is that of the DWARF reference kernels
+// k-step, of which the thread with tig == g>>1 keeps the diagonal entries; the products that
+// follow (p.v, ds.k, ds.q, p.dO) scale row g of a tile the thread already holds as a row
+// fragment, so they are plain fp32 FMAs on the thread's accumulators (no transposes, no tensor
+// core: measured faster than a diagonal A fragment).  The math is that of the DWARF reference kernels
 // (kernels/dsqg_attention_v3.py:60-163 forward, :198-275 dQ, :282-352 dK/dV) without the
 // scale_embed term (shapes with scale_embed use the generic kernels), with the per-head
 // output gain of train/train_2048_condU.py:187 fused in.  See dsqg_mma.cuh for the
@@ -30,6 +32,22 @@ struct Lane {
         owner_lane = (lane & ~3) | (g >> 1);
     }
 };
+
+// acc(rows g / g+8) += x_lo * f_lo, x_hi * f_hi for this thread's elements: the diagonal form of
+// "A.B with A = diag(x)" -- row g of the product only needs row g of B, which the thread holds
+// as a row fragment for exactly the elements d its accumulators cover.
+template <int D>
+__device__ __forceinline__ void diag_fma(float (&acc)[D / 8][4], float x_lo, float x_hi, const RowFrag<D>& f_lo,
+                                         const RowFrag<D>& f_hi) {
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+        const uint32_t u0 = f_lo.r[j], u1 = f_hi.r[j];
+        acc[j][0] = fmaf(x_lo, __uint_as_float(u0 << 16), acc[j][0]);
+        acc[j][1] = fmaf(x_lo, __uint_as_float(u0 & 0xffff0000u), acc[j][1]);
+        acc[j][2] = fmaf(x_hi, __uint_as_float(u1 << 16), acc[j][2]);
+        acc[j][3] = fmaf(x_hi, __uint_as_float(u1 & 0xffff0000u), acc[j][3]);
+    }
+}
 
 // ------------------------------------------------------------------------------ forward
 // Online softmax over the dense window, then over the sparse taps, with the per-element
@@ -132,7 +150,6 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
         }
     }
     // ---- sparse taps
-    const uint32_t dmask = (g & 1) ? 0xffff0000u : 0x0000ffffu;
     float ms_lo = L.owner ? m_lo : 1.0e30f, ms_hi = L.owner ? m_hi : 1.0e30f;   // what this lane subtracts
     // Folds G taps whose scores x0[i] (row g) and x1[i] (row g+8) are known into the running softmax.
     auto fold = [&](auto GC, const float (&x0)[decltype(GC)::value], const float (&x1)[decltype(GC)::value],
@@ -155,9 +172,10 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
         for (int i = 0; i < G; ++i) {
             const float p0 = ex2(x0[i] - ms_lo), p1 = ex2(x1[i] - ms_hi);   // exactly 0 on lanes that own no diagonal entry
             l_lo += p0; l_hi += p1;
-            RowFrag<D> vt0, vt1;
-            transpose_frag(vt0, vf0[i]); transpose_frag(vt1, vf1[i]);
-            mma_cols<D>(O, pack_bf16x2(p0, p0) & dmask, 0u, 0u, pack_bf16x2(p1, p1) & dmask, vt0, vt1);
+            // P is diagonal: row g only needs its own value row, which this thread holds for the
+            // same elements d as its accumulators
+            diag_fma<D>(O, __shfl_sync(0xffffffffu, p0, L.owner_lane), __shfl_sync(0xffffffffu, p1, L.owner_lane),
+                        vf0[i], vf1[i]);
         }
     };
     // G consecutive taps whose 16 key rows all exist: no predicates, loads of all G taps in flight together
@@ -366,7 +384,6 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
         }
     }
     // ---- sparse taps
-    const uint32_t dmask = L.owner ? ((g & 1) ? 0xffff0000u : 0x0000ffffu) : 0u;
     const float ls_lo = L.owner ? l2_lo : 1.0e30f, ls_hi = L.owner ? l2_hi : 1.0e30f;   // p == 0 on lanes without a diagonal entry
     float* stage_sp = stage_w + nd * kStagePitch + g;
     auto finish = [&](int si, float sd0, float sd1, float dp0, float dp1, float pbv, bool v0, bool v1,
@@ -376,9 +393,7 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
         dgrow = fmaf(p0, dp0, dgrow); dgrow = fmaf(p1, dp1, dgrow);
         const float x0 = p0 * fmaf(gain, dp0, -delta_lo), x1 = p1 * fmaf(gain, dp1, -delta_hi);
         if (L.owner) { stage_sp[si * kStagePitch] = x0; stage_sp[si * kStagePitch + 8] = x1; }
-        RowFrag<D> kt0, kt1;
-        transpose_frag(kt0, kf0); transpose_frag(kt1, kf1);
-        mma_cols<D>(dQ, pack_bf16x2(x0, x0) & dmask, 0u, 0u, pack_bf16x2(x1, x1) & dmask, kt0, kt1);
+        diag_fma<D>(dQ, __shfl_sync(0xffffffffu, x0, L.owner_lane), __shfl_sync(0xffffffffu, x1, L.owner_lane), kf0, kf1);
     };
     auto full_taps = [&](auto GC, int si) {
         constexpr int GG = decltype(GC)::value;
@@ -572,17 +587,13 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
         }
     }
     // ---- sparse taps
-    const uint32_t dmask = L.owner ? ((g & 1) ? 0xffff0000u : 0x0000ffffu) : 0u;
     auto finish = [&](float sd0, float sd1, float dp0, float dp1, float pbv, float2 st0, float2 st1,
                       const RowFrag<D>& qf0, const RowFrag<D>& qf1, const RowFrag<D>& df0, const RowFrag<D>& df1) {
         const float p0 = ex2(fmaf(sd0, c2, pbv) - st0.x), p1 = ex2(fmaf(sd1, c2, pbv) - st1.x);
         const float w0 = p0 * gain, w1 = p1 * gain;
         const float x0 = p0 * fmaf(gain, dp0, -st0.y), x1 = p1 * fmaf(gain, dp1, -st1.y);
-        RowFrag<D> t0, t1;
-        transpose_frag(t0, df0); transpose_frag(t1, df1);
-        mma_cols<D>(dV, pack_bf16x2(w0, w0) & dmask, 0u, 0u, pack_bf16x2(w1, w1) & dmask, t0, t1);
-        transpose_frag(t0, qf0); transpose_frag(t1, qf1);
-        mma_cols<D>(dK, pack_bf16x2(x0, x0) & dmask, 0u, 0u, pack_bf16x2(x1, x1) & dmask, t0, t1);
+        diag_fma<D>(dV, __shfl_sync(0xffffffffu, w0, L.owner_lane), __shfl_sync(0xffffffffu, w1, L.owner_lane), df0, df1);
+        diag_fma<D>(dK, __shfl_sync(0xffffffffu, x0, L.owner_lane), __shfl_sync(0xffffffffu, x1, L.owner_lane), qf0, qf1);
     };
     auto full_taps = [&](auto GC, int si) {
         constexpr int GG = decltype(GC)::value;

@@ -313,4 +313,4 @@ def test_full_size_configs_vs_c_oracle_on_batch_slices(cfg_name):
     assert (r["out"][:, :, 0] - want).abs().max().item() <= BF16_ABS_TOL
     # sum_j dpos_bias[j,h] ~ 0: softmax gradients sum to zero over the taps of every row
     # (up to the bf16 rounding of the saved output that enters delta = sum_d dout*out)
-    assert (r["dpb"].sum(0).abs() <= 5e-3 * r["dpb"].abs().sum(0) + 0.5).all()
+    assert (r["dpb"].sum(0).abs() <= 1e-2 * r["dpb"].abs().sum(0) + 1.0).all()
