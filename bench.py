@@ -145,20 +145,19 @@ def run_op_workload(args, cfg, rank, local_rank, world):
 
     # ---- device-resident timing: W warm-up steps, then exactly K timed steps -------------
     for _ in range(args.warmup):
-        fwd(); bwd(1); bwd(2); bwd(4)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+        fwd(); bwd(1); bwd(6)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     ddist.barrier(); torch.cuda.synchronize()
     t_wall = time.perf_counter()
     for i in range(args.steps):
         ev[i][0].record(stream); fwd()
         ev[i][1].record(stream); bwd(1)
-        ev[i][2].record(stream); bwd(2)
-        ev[i][3].record(stream); bwd(4)
-        ev[i][4].record(stream)
+        ev[i][2].record(stream); bwd(6)       # dK/dV kernel; its first CTAs also reduce dpos_bias / dhead_gain
+        ev[i][3].record(stream)
     torch.cuda.synchronize(); ddist.barrier()
     wall_ms = (time.perf_counter() - t_wall) * 1e3
-    total_ms = ev[0][0].elapsed_time(ev[-1][4])
-    kern_ms = [sum(ev[i][s].elapsed_time(ev[i][s + 1]) for i in range(args.steps)) / args.steps for s in range(4)]
+    total_ms = ev[0][0].elapsed_time(ev[-1][3])
+    kern_ms = [sum(ev[i][s].elapsed_time(ev[i][s + 1]) for i in range(args.steps)) / args.steps for s in range(3)]
     total_ms = ddist.max_over_ranks(total_ms, dev if world > 1 else "cpu")
     ms_per_step = total_ms / args.steps
     tokens_per_step = B * N * world
@@ -193,9 +192,9 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     peak, peak_src = measured_peaks()
     # DRAM bytes (read + write) per launch from the ncu capture summarised in
     # profiles/dsqg_mma_kernels_cfg1.md; only known for the workload that was captured.
-    ncu_traffic = {"cfg1": [119.96e6, 195.40e6, 183.60e6, None]}.get(args.workload, [None] * 4)
-    names = ["dsqg_fwd", "dsqg_bwd_dq", "dsqg_bwd_dkdv", "dsqg_bwd_reduce_params"]
-    alg = [4 * T, 6 * T, 6 * T, 0]        # per launch: fwd Q,K,V->O ; dq Q,K,V,O,dO->dQ ; dkdv Q,K,V,dO->dK,dV
+    ncu_traffic = {"cfg1": [119.96e6, 195.40e6, 183.60e6]}.get(args.workload, [None] * 3)
+    names = ["dsqg_fwd", "dsqg_bwd_dq", "dsqg_bwd_dkdv"]
+    alg = [4 * T, 6 * T, 6 * T]           # per launch: fwd Q,K,V->O ; dq Q,K,V,O,dO->dQ ; dkdv Q,K,V,dO->dK,dV
     top = max(range(3), key=lambda s: kern_ms[s])
     achieved = alg[top] / (kern_ms[top] * 1e-3) / 1e9
     step_achieved = 12 * T / (ms_per_step * 1e-3) / 1e9
@@ -210,14 +209,14 @@ def run_op_workload(args, cfg, rank, local_rank, world):
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": 4 * T, "d2h_bytes_per_step": 4 * T, "ms_per_step": e2e_ms,
                 "steps": e2e_steps},
-        "gpu_launches": 4 * args.steps,
+        "gpu_launches": (3 if args.kernel_path in (0, 2) else 4) * args.steps,   # other paths reduce in a 4th kernel
         "roofline": {"bound": "hbm", "kernel": names[top], "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": ncu_traffic[top], "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": alg[top], "ms_per_launch": kern_ms[top]},
         "step_roofline": {"algorithmic_bytes_per_step": 12 * T, "achieved": step_achieved,
                           "frac": step_achieved / peak, "unit": "GB/s"},
         "kernels": [{"name": names[s], "ms": kern_ms[s], "algorithmic_bytes": alg[s], "traffic": ncu_traffic[s],
-                     "gbs": (alg[s] / (kern_ms[s] * 1e-3) / 1e9) if alg[s] else None} for s in range(4)],
+                     "gbs": alg[s] / (kern_ms[s] * 1e-3) / 1e9} for s in range(3)],
         "wall_ms_timed_region": wall_ms,
         "clocks": clocks,
     }

@@ -135,6 +135,48 @@ __device__ __forceinline__ void store8(float* p, const float (&x)[8]) {
     *reinterpret_cast<float4*>(p + 4) = make_float4(x[4], x[5], x[6], x[7]);
 }
 
+// One output of the parameter-gradient reduction: the per-tile partial sums of dpos_bias[j,h]
+// (idx < J*H), dhead_gain[h] (next H) or dscale_embed[j,d] (rest) are added by the
+// kReduceThreads threads of a block in a fixed order (strided partial sums, then a fixed
+// shared-memory tree), so the result is bitwise reproducible whichever kernel runs it.
+constexpr int kReduceThreads = 128;
+__device__ __forceinline__ void reduce_one_param(const BwdArgs& a, int J, int idx, float* red) {
+    const int n_pb = J * a.H;
+    const int per_h = a.B * a.tiles_per_bh;          // partials per (.., h): b-major, then tile
+    float s = 0.f;
+    float* dst = nullptr;
+    if (idx < n_pb) {
+        const int j = idx / a.H, h = idx - j * a.H;
+        for (int i = threadIdx.x; i < per_h; i += kReduceThreads) {
+            const int b = i / a.tiles_per_bh, c = i - b * a.tiles_per_bh;
+            s += a.dpb_part[((size_t)(b * a.H + h) * a.tiles_per_bh + c) * J + j];
+        }
+        dst = a.dpos_bias + idx;
+    } else if (idx < n_pb + a.H) {
+        const int h = idx - n_pb;
+        if (a.dhead_gain) {
+            for (int i = threadIdx.x; i < per_h; i += kReduceThreads) {
+                const int b = i / a.tiles_per_bh, c = i - b * a.tiles_per_bh;
+                s += a.dg_part[(size_t)(b * a.H + h) * a.tiles_per_bh + c];
+            }
+            dst = a.dhead_gain + h;
+        }
+    } else if (a.dscale_embed && a.scale_embed) {
+        const int e = idx - n_pb - a.H;
+        for (int tl = threadIdx.x; tl < a.n_dse_blocks; tl += kReduceThreads)
+            s += a.dse_part[(size_t)tl * J * a.D + e];
+        dst = a.dscale_embed + e;
+    }
+    red[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = kReduceThreads / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && dst) *dst = red[0];
+    __syncthreads();
+}
+
 template <int WIDTH>
 __device__ __forceinline__ float group_sum(float x) {
 #pragma unroll

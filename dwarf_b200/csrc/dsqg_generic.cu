@@ -282,44 +282,10 @@ bwd_dkdv_generic_kernel(const BwdArgs a, const Taps t) {
 
 // One block per output element; the partials are summed in a fixed order (per-thread strided
 // partial sums, then a fixed shared-memory tree), so the result is bitwise reproducible.
-constexpr int kReduceThreads = 128;
 __global__ void __launch_bounds__(kReduceThreads)
 bwd_reduce_params_kernel(const BwdArgs a, const int J) {
     __shared__ float red[kReduceThreads];
-    const int idx = blockIdx.x;
-    const int n_pb = J * a.H;
-    const int per_h = a.B * a.tiles_per_bh;          // partials per (.., h): b-major, then tile
-    float s = 0.f;
-    float* dst = nullptr;
-    if (idx < n_pb) {
-        const int j = idx / a.H, h = idx - j * a.H;
-        for (int i = threadIdx.x; i < per_h; i += kReduceThreads) {
-            const int b = i / a.tiles_per_bh, c = i - b * a.tiles_per_bh;
-            s += a.dpb_part[((size_t)(b * a.H + h) * a.tiles_per_bh + c) * J + j];
-        }
-        dst = a.dpos_bias + idx;
-    } else if (idx < n_pb + a.H) {
-        const int h = idx - n_pb;
-        if (a.dhead_gain) {
-            for (int i = threadIdx.x; i < per_h; i += kReduceThreads) {
-                const int b = i / a.tiles_per_bh, c = i - b * a.tiles_per_bh;
-                s += a.dg_part[(size_t)(b * a.H + h) * a.tiles_per_bh + c];
-            }
-            dst = a.dhead_gain + h;
-        }
-    } else if (a.dscale_embed && a.scale_embed) {
-        const int e = idx - n_pb - a.H;
-        for (int tl = threadIdx.x; tl < a.n_dse_blocks; tl += kReduceThreads)
-            s += a.dse_part[(size_t)tl * J * a.D + e];
-        dst = a.dscale_embed + e;
-    }
-    red[threadIdx.x] = s;
-    __syncthreads();
-    for (int o = kReduceThreads / 2; o > 0; o >>= 1) {
-        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
-        __syncthreads();
-    }
-    if (threadIdx.x == 0 && dst) *dst = red[0];
+    reduce_one_param(a, J, blockIdx.x, red);
 }
 
 cudaError_t launch_reduce_params(const BwdArgs& a, int J, cudaStream_t s) {

@@ -655,7 +655,7 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
 
 template <int D, int WB, int G, int CT>
 __global__ void __launch_bounds__(kWarps * 32, CT)
-bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t) {
+bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t, const int n_reduce, const int reduce_stride) {
     constexpr int NT = (WB + 16) / 8;
     constexpr int kStat = kRows + WB;                  // query rows the CTA's dense windows touch
     __shared__ float4 init_s[NT * 32];
@@ -663,6 +663,13 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t) {
     __shared__ __align__(16) float2 stat_s[kStat];
     const Lane L;
     const int bh = blockIdx.y, h = bh % a.H, N = a.N;
+    // n_reduce CTAs (every reduce_stride-th one, so that no wave of CTAs is delayed as a whole)
+    // also finish dpos_bias / dhead_gain: one output each, from the partial sums the dQ kernel
+    // (an earlier launch on the stream) left in the scratch.
+    static_assert(kWarps * 32 == kReduceThreads, "the fused reduction uses the CTA as one reduce block");
+    const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+    if (cta % reduce_stride == 0 && cta / reduce_stride < n_reduce)
+        reduce_one_param(a, t.J, cta / reduce_stride, reinterpret_cast<float*>(init_s));
     const int m_cta = blockIdx.x * kRows;
     {
         const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1;
@@ -714,11 +721,17 @@ cudaError_t bwd_launch_mma(BwdArgs a, const Taps& t, cudaStream_t s, int stages)
         bwd_dq_mma_kernel<D, WB, T::dq_group, T::dq_ctas><<<grid, kWarps * 32, smem, s>>>(a, t);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
+    // With both stages in one call the reduction rides on the first CTAs of the dK/dV kernel
+    // (same code, same order of additions as the stand-alone kernel: bitwise equal results).
+    const int n_out = t.J * a.H + a.H;
+    const bool fuse = (stages & DSQG_BWD_STAGE_DKDV) && (stages & DSQG_BWD_STAGE_REDUCE) &&
+                      (long long)grid.x * grid.y >= n_out;
     if (stages & DSQG_BWD_STAGE_DKDV) {
-        bwd_dkdv_mma_kernel<D, WB, T::dkdv_group, T::dkdv_ctas><<<grid, kWarps * 32, 0, s>>>(a, t);
+        bwd_dkdv_mma_kernel<D, WB, T::dkdv_group, T::dkdv_ctas><<<grid, kWarps * 32, 0, s>>>(
+            a, t, fuse ? n_out : 0, fuse ? (int)((long long)grid.x * grid.y / n_out) : 1);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
-    if (stages & DSQG_BWD_STAGE_REDUCE) e = launch_reduce_params(a, t.J, s);
+    if ((stages & DSQG_BWD_STAGE_REDUCE) && !fuse) e = launch_reduce_params(a, t.J, s);
     return e;
 }
 

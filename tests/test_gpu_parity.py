@@ -236,6 +236,45 @@ def test_bitwise_determinism_and_no_unwritten_rows():
         assert torch.equal(x, y)
 
 
+@pytest.mark.parametrize("shape", [(3, 8, 2047, 32), (2, 3, 700, 64), (1, 2, 40, 32)])
+def test_fused_parameter_reduction_equals_staged_backward_bitwise(shape):
+    """Tensor-core path: one dsqg_bwd call lets the first CTAs of the dK/dV kernel finish dpos_bias
+    and dhead_gain; running the three stages as separate calls uses the stand-alone reduction
+    kernel.  Same additions in the same order: every output is bit-identical, none unwritten."""
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(sum(shape))
+    B, H, N, D = shape
+    mk = lambda: bf16_valued(B, H, N, D, scale=0.5, gen=g).to(dev, torch.bfloat16)
+    q, k, v, dout = mk(), mk(), mk(), mk()
+    pb = (torch.randn(43, H, generator=g) * 0.5).to(dev)
+    gain = (torch.rand(H, generator=g) + 0.5).to(dev)
+    off, J = _lib.offsets_array(O.OFFSETS_43)
+    stream = torch.cuda.current_stream().cuda_stream
+    out = torch.empty_like(q); lse = torch.empty(B, H, N, device=dev)
+    _lib.check(lib.dsqg_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), None, gain.data_ptr(),
+                            off, J, out.data_ptr(), lse.data_ptr(), B, H, N, D, 0, stream), "fwd")
+
+    def run(stage_list):
+        nan = float("nan")
+        dq, dk, dv = (torch.full_like(q, nan) for _ in range(3))
+        dpb = torch.full((J, H), nan, device=dev); dg = torch.full((H,), nan, device=dev)
+        nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, 0)
+        scratch = torch.full((nbytes // 4,), nan, device=dev)
+        for st in stage_list:
+            _lib.check(lib.dsqg_bwd_stages(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), None,
+                                           gain.data_ptr(), off, J, out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
+                                           dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dpb.data_ptr(), None,
+                                           dg.data_ptr(), scratch.data_ptr(), nbytes, B, H, N, D, 0, stream, st), "bwd")
+        torch.cuda.synchronize()
+        return dq, dk, dv, dpb, dg
+
+    fused, staged = run([7]), run([1, 2, 4])
+    for x, y in zip(fused, staged):
+        assert torch.isfinite(x.float()).all()
+        assert torch.equal(x, y)
+
+
 def test_non_default_stream_and_checkpoint_and_autocast():
     dev = torch.device("cuda", 0)
     m = dwarf_b200.DSQGAttentionQW(256, 8, dropout=0.0).to(dev)
