@@ -458,20 +458,23 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
+    # stdout carries exactly one JSON line: whatever libraries write to file descriptor 1 while
+    # the benchmark runs (NCCL's version banner, for one) is sent to stderr instead
+    sys.stdout.flush()
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
     from dwarf_b200 import dist as ddist, synth
     rank, local_rank, world = ddist.env_world()
 
     if args.impl == "reference":
         if rank == 0:
             cfg = synth.OP_CONFIGS["cfg1" if args.workload in ("cfg3", "cfg4") else args.workload]
-            print(json.dumps(run_reference_arm(args, cfg)), flush=True)
+            print(json.dumps(run_reference_arm(args, cfg)), file=json_out, flush=True)
         return 0
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the DSQG kernels have no CPU fallback")
-    # keep stdout to the one JSON line: NCCL's version banner goes there at NCCL_DEBUG=VERSION
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"
     ddist.init_process_group("nccl")
     if args.kernel_path:
         from dwarf_b200 import _lib
@@ -491,7 +494,7 @@ def main():
                                     "sample": f"{sample_B} of {cfg.B} batch entries ({sample_B * cfg.N} tokens), "
                                               f"fwd+bwd via autograd in fp32, best of 4 ({secs:.2f} s)"}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=json_out, flush=True)
     if torch.distributed.is_initialized():
         torch.distributed.destroy_process_group()
     return 0

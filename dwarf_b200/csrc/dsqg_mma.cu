@@ -1,4 +1,5 @@
-// Tensor-core DSQG kernels (bf16 storage, fp32 accumulate) for D in {32, 64}.
+// Tensor-core DSQG kernels (bf16 storage, fp32 accumulate) for D in {32, 64} (dense windows up
+// to 64 wide) and D in {96, 128} (dense windows up to 32 wide).
 //
 // One warp owns 16 consecutive rows of one (batch, head) sequence.  The dense window is a
 // banded GEMM: the 16 query rows against the WB+16 key rows [g0-WB, g0+16) with
@@ -244,7 +245,7 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
 
 // Tuning per head dimension (measured on B200): warps per CTA, sparse taps folded together,
 // resident CTAs per SM the register budget is set for.
-template <int D> struct FwdTune { static constexpr int warps = 4, group = D == 32 ? 2 : 3, ctas = D == 32 ? 5 : 4; };
+template <int D> struct FwdTune { static constexpr int warps = 4, group = D == 32 ? 2 : (D == 64 ? 3 : 1), ctas = D == 32 ? 5 : (D == 64 ? 4 : (D == 96 ? 3 : 2)); };
 
 template <int D, int WB>
 __global__ void __launch_bounds__(FwdTune<D>::warps * 32, FwdTune<D>::ctas)
@@ -288,8 +289,8 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
 // Tuning per head dimension (measured on B200): sparse taps whose loads are issued together and
 // resident CTAs per SM the register budget is set for (spills against warps in flight).
 template <int D> struct BwdTune {
-    static constexpr int dq_group = 1, dq_ctas = D == 32 ? 6 : 4;
-    static constexpr int dkdv_group = D == 32 ? 2 : 1, dkdv_ctas = D == 32 ? 4 : 3;
+    static constexpr int dq_group = 1, dq_ctas = D == 32 ? 6 : (D == 64 ? 4 : 2);
+    static constexpr int dkdv_group = D == 32 ? 2 : 1, dkdv_ctas = D == 32 ? 4 : (D == 64 ? 3 : 2);
 };
 constexpr int kStagePitch = kRows + 3;      // 67: 2-way bank conflicts on the scattered writes, none on the column sums
 
@@ -743,8 +744,9 @@ int band_width(const Taps& t) {
 }  // namespace
 
 bool mma_path_supported(int dtype, int D, const Taps& t, bool has_scale_embed) {
-    return dtype == DSQG_DTYPE_BF16 && (D == 32 || D == 64) && !has_scale_embed &&
-           t.n_sparse <= kMaxSparse && band_width(t) != 0;
+    const int wb = band_width(t);
+    return dtype == DSQG_DTYPE_BF16 && !has_scale_embed && t.n_sparse <= kMaxSparse &&
+           (((D == 32 || D == 64) && wb != 0) || ((D == 96 || D == 128) && wb == 32));
 }
 
 #define DSQG_MMA_DISPATCH(FN, ...)                                             \
@@ -755,6 +757,8 @@ bool mma_path_supported(int dtype, int D, const Taps& t, bool has_scale_embed) {
             if (wb_ == 48) return FN<32, 48>(__VA_ARGS__);                     \
             return FN<32, 64>(__VA_ARGS__);                                    \
         }                                                                      \
+        if (a.D == 96) return FN<96, 32>(__VA_ARGS__);                         \
+        if (a.D == 128) return FN<128, 32>(__VA_ARGS__);                       \
         if (wb_ == 32) return FN<64, 32>(__VA_ARGS__);                         \
         if (wb_ == 48) return FN<64, 48>(__VA_ARGS__);                         \
         return FN<64, 64>(__VA_ARGS__);                                        \

@@ -85,6 +85,30 @@ def test_bf16_forward_backward_vs_oracle(shape, offsets, kernel_path):
     assert_param_grad_close(r["dgain"], ref["dgain"], "dgain", PARAM_REL_TOL_BF16)
 
 
+@pytest.mark.parametrize("shape", [(1, 2, 333, 96), (2, 2, 1700, 128), (1, 3, 40, 128)])
+@pytest.mark.parametrize("path", ["auto", "generic"])
+def test_bf16_wide_heads_vs_oracle(shape, path):
+    """D = 96 and 128: tensor-core kernels for the 32-wide dense window, generic kernels forced
+    as the cross-check."""
+    lib = _lib.load()
+    lib.dsqg_set_kernel_path(1 if path == "generic" else 0)
+    try:
+        B, H, N, D = shape
+        g = torch.Generator().manual_seed(7 + N + D)
+        q, k, v = (bf16_valued(B, H, N, D, scale=0.5, gen=g) for _ in range(3))
+        dout = bf16_valued(B, H, N, D, gen=g)
+        pb = synth.log_linear_pos_bias(O.OFFSETS_43, H) + torch.randn(43, H, generator=g) * 0.05
+        gain = torch.rand(H, generator=g) * 0.4 + 0.8
+        ref = oracle_fwd_bwd(q, k, v, pb, dout, None, gain, O.OFFSETS_43)
+        r = cuda_fwd_bwd(q, k, v, pb, dout, None, gain, O.OFFSETS_43, torch.bfloat16)
+        for nm in ("out", "dq", "dk", "dv"):
+            assert_bf16_close(r[nm], ref[nm], nm)
+        assert_param_grad_close(r["dpb"], ref["dpb"], "dpb", PARAM_REL_TOL_BF16)
+        assert_param_grad_close(r["dgain"], ref["dgain"], "dgain", PARAM_REL_TOL_BF16)
+    finally:
+        lib.dsqg_set_kernel_path(0)
+
+
 @pytest.mark.parametrize("shape", [(1, 4, 64, 32), (2, 2, 1600, 32), (1, 3, 200, 64), (1, 2, 100, 80)])
 def test_bf16_scale_embed_and_gain_vs_oracle(shape):
     B, H, N, D = shape
