@@ -71,7 +71,8 @@ cudaError_t launch_ring_prefill(const void* k, const void* v, void* k_ring, void
 
 cudaError_t launch_fwd_mma(const FwdArgs& a, const Taps& t, cudaStream_t s);
 cudaError_t launch_bwd_mma(const BwdArgs& a, const Taps& t, cudaStream_t s, int stages);
-bool mma_path_supported(int dtype, int D, const Taps& t, bool has_scale_embed);
+bool mma_path_supported(int dtype, int D, const Taps& t, bool has_scale_embed);   // backward
+bool mma_fwd_supported(int dtype, int D, const Taps& t, bool has_scale_embed);
 cudaError_t launch_fwd_tma(const FwdArgs& a, const Taps& t, cudaStream_t s);
 bool tma_fwd_supported(int dtype, int D, int N, const Taps& t, bool has_scale_embed);
 cudaError_t read_device_error_fwd_tma(int* value, bool reset);

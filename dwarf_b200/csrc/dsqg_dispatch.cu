@@ -15,7 +15,7 @@ static std::atomic<int> g_path{0};
 cudaError_t launch_fwd(const FwdArgs& a, const Taps& t, int dtype, cudaStream_t s) {
     const int path = g_path.load();
     if (path == 3 && tma_fwd_supported(dtype, a.D, a.N, t, a.scale_embed != nullptr)) return launch_fwd_tma(a, t, s);
-    if (path != 1 && mma_path_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_mma(a, t, s);
+    if (path != 1 && mma_fwd_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_mma(a, t, s);
     return launch_fwd_generic(a, t, dtype, s);
 }
 

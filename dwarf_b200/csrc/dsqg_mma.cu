@@ -73,9 +73,44 @@ __device__ __forceinline__ void load_row_at(RowFrag<D>& f, const __nv_bfloat16* 
     }
 }
 
-template <int D, int WB, bool INTERIOR, int kTapGroup>
+// Shared-memory tables of the scale_embed variants (reference: kernels/dsqg_attention_v3.py:112-118,
+// s_j += q.scale_embed[j] / sqrt(D)).  se_hi + se_lo are the bf16 halves of scale_embed (their sum
+// carries 16 mantissa bits), pbs[j] = pos_bias[j,h] / scale, and qs (one tile per warp,
+// [16][pitch] floats + one dump word holding the mask value) receives q.scale_embed[j] + pbs[j]
+// for the warp's rows.  off[] maps dense-window accumulator slots to tile entries (or the dump).
+struct SeTables {
+    const __nv_bfloat16* se_hi; const __nv_bfloat16* se_lo;
+    const float* pbs; const int4* off; float* qs;
+    int Jp, pitch, nd;
+};
+
+// qs[row][j] = q[row].scale_embed[j] + pbs[j] for the 16 rows held as A fragments qa (rows g) / qb (rows g+8)
+template <int D>
+__device__ __forceinline__ void build_qs_tile(const SeTables& se, const RowFrag<D>& qa, const RowFrag<D>& qb, int g, int tig) {
+#pragma unroll 1
+    for (int m = 0; m < se.Jp / 8; ++m) {
+        const float2 pb2 = *reinterpret_cast<const float2*>(se.pbs + 8 * m + 2 * tig);
+        float c[4] = {pb2.x, pb2.y, pb2.x, pb2.y};
+        RowFrag<D> sf;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const uint4* src = reinterpret_cast<const uint4*>((half ? se.se_lo : se.se_hi) + (8 * m + g) * D + 8 * tig);
+#pragma unroll
+            for (int cc = 0; cc < D / 32; ++cc) {
+                const uint4 u = src[4 * cc];
+                sf.r[4 * cc + 0] = u.x; sf.r[4 * cc + 1] = u.y; sf.r[4 * cc + 2] = u.z; sf.r[4 * cc + 3] = u.w;
+            }
+            mma_rows(c, qa, qb, sf);
+        }
+        *reinterpret_cast<float2*>(se.qs + g * se.pitch + 8 * m + 2 * tig) = make_float2(c[0], c[1]);
+        *reinterpret_cast<float2*>(se.qs + (g + 8) * se.pitch + 8 * m + 2 * tig) = make_float2(c[2], c[3]);
+    }
+    __syncwarp();
+}
+
+template <int D, int WB, bool INTERIOR, int kTapGroup, bool SE>
 __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s, const int2* tap_s, int ns,
-                                         int bh, int h, int g0, const Lane& L) {
+                                         int bh, int h, int g0, const Lane& L, const SeTables& se) {
     constexpr int NT = (WB + 16) / 8;
     const int N = a.N, g = L.g, tig = L.tig;
     const int row_lo = g0 + g, row_hi = row_lo + 8;
@@ -91,13 +126,19 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
     RowFrag<D> qa, qb;
     load_row(qa, qp + (size_t)row_lo * D, tig, ok_lo);
     load_row(qb, qp + (size_t)row_hi * D, tig, ok_hi);
+    if (SE) build_qs_tile<D>(se, qa, qb, g, tig);
 
     // ---- dense window: key row of n-tile nt for this thread is kb0 + 8 nt + g = row_lo - WB + 8 nt
     float S[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        const float4 ini = init_s[nt * 32 + L.lane];
-        S[nt][0] = ini.x; S[nt][1] = ini.y; S[nt][2] = ini.z; S[nt][3] = ini.w;
+        if (SE) {
+            const int4 qo = se.off[nt * 32 + L.lane];
+            S[nt][0] = se.qs[qo.x]; S[nt][1] = se.qs[qo.y]; S[nt][2] = se.qs[qo.z]; S[nt][3] = se.qs[qo.w];
+        } else {
+            const float4 ini = init_s[nt * 32 + L.lane];
+            S[nt][0] = ini.x; S[nt][1] = ini.y; S[nt][2] = ini.z; S[nt][3] = ini.w;
+        }
         RowFrag<D> kf;
         if (INTERIOR) {
             load_row_at(kf, kl + (8 * nt - WB) * D);
@@ -200,8 +241,14 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
             float s0[4], s1[4];
             mma_rows_z(s0, qa, qb, kf0[i]);
             mma_rows_z(s1, qa, qb, kf1[i]);
-            x0[i] = fmaf((g & 1) ? s0[1] : s0[0], c2, pbv[i]);
-            x1[i] = fmaf((g & 1) ? s1[3] : s1[2], c2, pbv[i]);
+            const float d0 = (g & 1) ? s0[1] : s0[0], d1 = (g & 1) ? s1[3] : s1[2];
+            if (SE) {
+                x0[i] = (d0 + se.qs[g * se.pitch + se.nd + si + i]) * c2;
+                x1[i] = (d1 + se.qs[(g + 8) * se.pitch + se.nd + si + i]) * c2;
+            } else {
+                x0[i] = fmaf(d0, c2, pbv[i]);
+                x1[i] = fmaf(d1, c2, pbv[i]);
+            }
         }
         fold(GC, x0, x1, vf0, vf1);
     };
@@ -227,8 +274,11 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
             float s0[4], s1[4];
             mma_rows_z(s0, qa, qb, kf0);
             mma_rows_z(s1, qa, qb, kf1);
-            const float x0[1] = {v0 ? fmaf((g & 1) ? s0[1] : s0[0], c2, pbv) : kNeg};
-            const float x1[1] = {v1 ? fmaf((g & 1) ? s1[3] : s1[2], c2, pbv) : kNeg};
+            const float d0 = (g & 1) ? s0[1] : s0[0], d1 = (g & 1) ? s1[3] : s1[2];
+            const float y0 = SE ? (d0 + se.qs[g * se.pitch + se.nd + si]) * c2 : fmaf(d0, c2, pbv);
+            const float y1 = SE ? (d1 + se.qs[(g + 8) * se.pitch + se.nd + si]) * c2 : fmaf(d1, c2, pbv);
+            const float x0[1] = {v0 ? y0 : kNeg};
+            const float x1[1] = {v1 ? y1 : kNeg};
             fold(std::integral_constant<int, 1>(), x0, x1, vf0, vf1);
         }
     }
@@ -247,16 +297,69 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
 // resident CTAs per SM the register budget is set for.
 template <int D> struct FwdTune { static constexpr int warps = 4, group = D == 32 ? 2 : (D == 64 ? 3 : 1), ctas = D == 32 ? 5 : (D == 64 ? 4 : (D == 96 ? 3 : 2)); };
 
-template <int D, int WB>
+// Fills the shared tables of the scale_embed variants (all threads of the CTA; the caller syncs).
+// smem layout: se_hi [Jp][D] bf16 | se_lo [Jp][D] bf16 | pbs [Jp] f32 | off [NT*32] int4 | qs [warps][16*pitch+4] f32
+template <int D, int WB, int W>
+__device__ __forceinline__ SeTables fill_se_tables(unsigned char* smem, const float* scale_embed, const float* pos_bias,
+                                                   const Taps& t, int H, int h, float scale, int warp, bool transposed) {
+    constexpr int NT = (WB + 16) / 8;
+    const int J = t.J, Jp = (J + 7) / 8 * 8, pitch = Jp + 2;
+    __nv_bfloat16* se_hi = reinterpret_cast<__nv_bfloat16*>(smem);
+    __nv_bfloat16* se_lo = se_hi + Jp * D;
+    float* pbs = reinterpret_cast<float*>(se_lo + Jp * D);
+    int4* off = reinterpret_cast<int4*>(pbs + Jp);
+    float* qs = reinterpret_cast<float*>(off + NT * 32);
+    for (int e = threadIdx.x; e < Jp * D / 2; e += W * 32) {
+        const int j = (2 * e) / D;
+        float2 x = make_float2(0.f, 0.f);
+        if (j < J) x = *reinterpret_cast<const float2*>(scale_embed + 2 * e);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(x.x, x.y);
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(x.x - __low2float(hi), x.y - __high2float(hi));
+        reinterpret_cast<__nv_bfloat162*>(se_hi)[e] = hi;
+        reinterpret_cast<__nv_bfloat162*>(se_lo)[e] = lo;
+    }
+    const float inv_scale = 1.f / scale;
+    for (int j = threadIdx.x; j < Jp; j += W * 32) pbs[j] = j < J ? pos_bias[j * H + h] * inv_scale : 0.f;
+    const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1;
+    for (int e = threadIdx.x; e < NT * 32; e += W * 32) {
+        const int nt = e >> 5, gg = (e & 31) >> 2, tt = e & 3;
+        int o[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int i = gg + 8 * (r >> 1), cc = 8 * nt + 2 * tt + (r & 1);
+            // forward / dQ: rows are queries, columns keys (delta = WB + i - cc); dK/dV: rows keys, columns queries
+            const int delta = transposed ? cc - i : WB + i - cc;
+            const int row = transposed ? cc : i;          // tile row = query index inside the tile
+            o[r] = (delta >= d_lo && delta <= d_hi) ? row * pitch + (delta - d_lo) : 16 * pitch;
+        }
+        off[e] = make_int4(o[0], o[1], o[2], o[3]);
+    }
+    float* qs_w = qs + warp * (16 * pitch + 4);
+    if ((threadIdx.x & 31) == 0) qs_w[16 * pitch] = kNeg;      // the dump entry: masked
+    SeTables s;
+    s.se_hi = se_hi; s.se_lo = se_lo; s.pbs = pbs; s.off = off; s.qs = qs_w;
+    s.Jp = Jp; s.pitch = pitch; s.nd = t.n_dense;
+    return s;
+}
+inline size_t se_tables_bytes(int J, int D, int NT, int warps, int tile_rows) {
+    const int Jp = (J + 7) / 8 * 8;
+    return (size_t)2 * Jp * D * 2 + (size_t)Jp * 4 + (size_t)NT * 32 * 16 + (size_t)warps * (tile_rows * (Jp + 2) + 4) * 4;
+}
+
+template <int D, int WB, bool SE>
 __global__ void __launch_bounds__(FwdTune<D>::warps * 32, FwdTune<D>::ctas)
 fwd_mma_kernel(const FwdArgs a, const Taps t) {
     constexpr int W = FwdTune<D>::warps, G = FwdTune<D>::group;
     constexpr int NT = (WB + 16) / 8;
-    __shared__ float4 init_s[NT * 32];
+    extern __shared__ __align__(16) unsigned char se_smem[];
+    __shared__ float4 init_s[SE ? 1 : NT * 32];
     __shared__ int2 tap_s[DSQG_MAX_TAPS];
     const Lane L;
     const int bh = blockIdx.y, h = bh % a.H, N = a.N;
-    {
+    SeTables se = {};
+    if (SE) {
+        se = fill_se_tables<D, WB, W>(se_smem, a.scale_embed, a.pos_bias, t, a.H, h, a.scale, L.warp, false);
+    } else {
         const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1;
         const float inv_scale = 1.f / a.scale;
         for (int e = threadIdx.x; e < NT * 32; e += W * 32) {
@@ -269,23 +372,16 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
             }
             init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
         }
-        for (int si = threadIdx.x; si < t.n_sparse; si += W * 32)
-            tap_s[si] = make_int2(t.sparse[si], __float_as_int(a.pos_bias[(t.n_dense + si) * a.H + h] * kLog2e));
     }
+    for (int si = threadIdx.x; si < t.n_sparse; si += W * 32)
+        tap_s[si] = make_int2(t.sparse[si], __float_as_int(a.pos_bias[(t.n_dense + si) * a.H + h] * kLog2e));
     __syncthreads();
     const int g0 = blockIdx.x * (16 * W) + L.warp * 16;
     if (g0 >= N) return;
-    if (g0 >= WB && g0 + 16 <= N) fwd_tile<D, WB, true, G>(a, init_s, tap_s, t.n_sparse, bh, h, g0, L);
-    else fwd_tile<D, WB, false, G>(a, init_s, tap_s, t.n_sparse, bh, h, g0, L);
+    if (g0 >= WB && g0 + 16 <= N) fwd_tile<D, WB, true, G, SE>(a, init_s, tap_s, t.n_sparse, bh, h, g0, L, se);
+    else fwd_tile<D, WB, false, G, SE>(a, init_s, tap_s, t.n_sparse, bh, h, g0, L, se);
 }
 
-// ------------------------------------------------------------------------------ backward: dQ
-// Also writes rowstat[n] = {lse[n]*log2(e) (0 for fully masked rows), sum_d dout*out} for the
-// dK/dV kernel and the per-CTA partial sums of dpos_bias (through a [J+1][kStagePitch] staging
-// tile in shared memory, summed in a fixed order; row J is a dump for out-of-band entries) and
-// of dhead_gain.  Every staging entry of a tile is written exactly once, so the tile is not
-// cleared.  As in the forward, mask and bias of the dense window are the initial value of the
-// score accumulators, and the staging offsets of the dense entries come from a per-lane table.
 // Tuning per head dimension (measured on B200): sparse taps whose loads are issued together and
 // resident CTAs per SM the register budget is set for (spills against warps in flight).
 template <int D> struct BwdTune {
@@ -700,9 +796,22 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t, const int n_reduce, const int
 
 template <int D, int WB>
 cudaError_t fwd_launch_mma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
-    constexpr int rows = 16 * FwdTune<D>::warps;
+    constexpr int W = FwdTune<D>::warps, rows = 16 * W;
     dim3 grid((a.N + rows - 1) / rows, a.B * a.H);
-    fwd_mma_kernel<D, WB><<<grid, FwdTune<D>::warps * 32, 0, s>>>(a, t);
+    if (a.scale_embed) {
+        if constexpr (D <= 64) {
+            const size_t smem = se_tables_bytes(t.J, D, (WB + 16) / 8, W, 16);
+            if (smem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<D, WB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e != cudaSuccess) return e;
+            }
+            fwd_mma_kernel<D, WB, true><<<grid, W * 32, smem, s>>>(a, t);
+        } else {
+            return cudaErrorInvalidValue;
+        }
+    } else {
+        fwd_mma_kernel<D, WB, false><<<grid, W * 32, 0, s>>>(a, t);
+    }
     return cudaGetLastError();
 }
 
@@ -743,10 +852,16 @@ int band_width(const Taps& t) {
 
 }  // namespace
 
-bool mma_path_supported(int dtype, int D, const Taps& t, bool has_scale_embed) {
+static bool mma_shape_supported(int dtype, int D, const Taps& t) {
     const int wb = band_width(t);
-    return dtype == DSQG_DTYPE_BF16 && !has_scale_embed && t.n_sparse <= kMaxSparse &&
+    return dtype == DSQG_DTYPE_BF16 && t.n_sparse <= kMaxSparse &&
            (((D == 32 || D == 64) && wb != 0) || ((D == 96 || D == 128) && wb == 32));
+}
+bool mma_fwd_supported(int dtype, int D, const Taps& t, bool has_scale_embed) {
+    return mma_shape_supported(dtype, D, t) && (!has_scale_embed || D <= 64);
+}
+bool mma_path_supported(int dtype, int D, const Taps& t, bool has_scale_embed) {
+    return mma_shape_supported(dtype, D, t) && !has_scale_embed;
 }
 
 #define DSQG_MMA_DISPATCH(FN, ...)                                             \
