@@ -100,7 +100,10 @@ size_t dsqg_bwd_scratch_bytes(int J, int B, int H, int N, int D, int has_scale_e
     size_t need = bwd_scratch_need(kMinRowsPerBwdTile, J, B, H, N, D, false);
     const size_t tma = bwd_scratch_need_tma(J, B, H, N);      // persistent kernels: partials per (CTA, sequence, warp)
     if (tma > need) need = tma;
-    return need + (has_scale_embed ? bwd_scratch_need(512, J, B, H, N, D, true) : 0);
+    if (!has_scale_embed) return need;
+    need += bwd_scratch_need(512, J, B, H, N, D, true);
+    const size_t mma_se = bwd_scratch_need_mma_se(J, B, H, N, D);
+    return mma_se > need ? mma_se : need;
 }
 
 int dsqg_bwd(const void* q, const void* k, const void* v,

@@ -9,10 +9,13 @@
 // follow (p.v, ds.k, ds.q, p.dO) scale row g of a tile the thread already holds as a row
 // fragment, so they are plain fp32 FMAs on the thread's accumulators (no transposes, no tensor
 // core: measured faster than a diagonal A fragment).  The math is that of the DWARF reference kernels
-// (kernels/dsqg_attention_v3.py:60-163 forward, :198-275 dQ, :282-352 dK/dV) without the
-// scale_embed term (shapes with scale_embed use the generic kernels), with the per-head
-// output gain of train/train_2048_condU.py:187 fused in.  See dsqg_mma.cuh for the
-// fragment conventions.
+// (kernels/dsqg_attention_v3.py:60-163 forward, :198-275 dQ, :282-352 dK/dV), with the per-head
+// output gain of train/train_2048_condU.py:187 fused in.  See dsqg_mma.cuh for the fragment
+// conventions.  scale_embed (D <= 64): q.scale_embed[j] is computed per 16-row tile with
+// split-bf16 MMAs into a shared-memory tile that also carries the position bias and replaces
+// the start-value table; the dQ kernel adds dS.scale_embed (MMA, dS from its staging tile),
+// produces dscale_embed partials per 64-row tile (dS^T.Q, MMA; dse_group_kernel adds groups of
+// eight tiles) and leaves the per-row tile in global memory for the dK/dV kernel.
 #include "dsqg_mma.cuh"
 #include <type_traits>
 
@@ -87,7 +90,7 @@ struct SeTables {
 // qs[row][j] = q[row].scale_embed[j] + pbs[j] for the 16 rows held as A fragments qa (rows g) / qb (rows g+8)
 template <int D>
 __device__ __forceinline__ void build_qs_tile(const SeTables& se, const RowFrag<D>& qa, const RowFrag<D>& qb, int g, int tig) {
-#pragma unroll 1
+#pragma unroll 2
     for (int m = 0; m < se.Jp / 8; ++m) {
         const float2 pb2 = *reinterpret_cast<const float2*>(se.pbs + 8 * m + 2 * tig);
         float c[4] = {pb2.x, pb2.y, pb2.x, pb2.y};
@@ -301,7 +304,8 @@ template <int D> struct FwdTune { static constexpr int warps = 4, group = D == 3
 // smem layout: se_hi [Jp][D] bf16 | se_lo [Jp][D] bf16 | pbs [Jp] f32 | off [NT*32] int4 | qs [warps][16*pitch+4] f32
 template <int D, int WB, int W>
 __device__ __forceinline__ SeTables fill_se_tables(unsigned char* smem, const float* scale_embed, const float* pos_bias,
-                                                   const Taps& t, int H, int h, float scale, int warp, bool transposed) {
+                                                   const Taps& t, int H, int h, float scale, int warp, bool transposed,
+                                                   const void* se_pre = nullptr) {
     constexpr int NT = (WB + 16) / 8;
     const int J = t.J, Jp = (J + 7) / 8 * 8, pitch = Jp + 2;
     __nv_bfloat16* se_hi = reinterpret_cast<__nv_bfloat16*>(smem);
@@ -309,6 +313,17 @@ __device__ __forceinline__ SeTables fill_se_tables(unsigned char* smem, const fl
     float* pbs = reinterpret_cast<float*>(se_lo + Jp * D);
     int4* off = reinterpret_cast<int4*>(pbs + Jp);
     float* qs = reinterpret_cast<float*>(off + NT * 32);
+    if (se_pre) {                                        // already split by se_prep_kernel: copy
+        const uint4* src = static_cast<const uint4*>(se_pre);
+        const int n16 = 2 * Jp * D * 2 / 16;
+        for (int e0 = threadIdx.x; e0 < n16; e0 += 4 * W * 32) {          // four loads in flight per thread
+            uint4 x[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { const int e = e0 + u * W * 32; x[u] = e < n16 ? __ldg(src + e) : make_uint4(0u, 0u, 0u, 0u); }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { const int e = e0 + u * W * 32; if (e < n16) reinterpret_cast<uint4*>(se_hi)[e] = x[u]; }
+        }
+    } else
     for (int e = threadIdx.x; e < Jp * D / 2; e += W * 32) {
         const int j = (2 * e) / D;
         float2 x = make_float2(0.f, 0.f);
@@ -341,7 +356,7 @@ __device__ __forceinline__ SeTables fill_se_tables(unsigned char* smem, const fl
     s.Jp = Jp; s.pitch = pitch; s.nd = t.n_dense;
     return s;
 }
-inline size_t se_tables_bytes(int J, int D, int NT, int warps, int tile_rows) {
+__host__ __device__ inline size_t se_tables_bytes(int J, int D, int NT, int warps, int tile_rows) {
     const int Jp = (J + 7) / 8 * 8;
     return (size_t)2 * Jp * D * 2 + (size_t)Jp * 4 + (size_t)NT * 32 * 16 + (size_t)warps * (tile_rows * (Jp + 2) + 4) * 4;
 }
@@ -386,14 +401,27 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
 // resident CTAs per SM the register budget is set for (spills against warps in flight).
 template <int D> struct BwdTune {
     static constexpr int dq_group = 1, dq_ctas = D == 32 ? 6 : (D == 64 ? 4 : 2);
+    static constexpr int dq_ctas_se = D == 32 ? 4 : 3;      // with scale_embed: more shared memory and registers per CTA
     static constexpr int dkdv_group = D == 32 ? 2 : 1, dkdv_ctas = D == 32 ? 4 : (D == 64 ? 3 : 2);
 };
 constexpr int kStagePitch = kRows + 3;      // 67: 2-way bank conflicts on the scattered writes, none on the column sums
+constexpr int kStagePitchSe = kRows + 4;    // 68 with scale_embed: rows are read back as 8-byte pairs by the dS MMAs
+template <bool SE> struct StagePitch { static constexpr int v = SE ? kStagePitchSe : kStagePitch; };
 
-template <int D, int WB, bool INTERIOR, int G>
+// Extras of the dQ kernel with scale_embed.
+//   seb:  scale_embed as B fragments of dS.SE (global memory, written by se_prep_kernel)
+//   q_s:  the CTA's 64 query rows as bf16 in shared memory, row pitch 2D+16 bytes (conflict-free ldmatrix)
+struct SeBwd {
+    const uint2* seb; unsigned char* q_s;
+    int JS;            // J rounded up to 16
+};
+
+template <int D, int WB, bool INTERIOR, int G, bool SE>
 __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s, const int4* soff_s, const int2* tap_s,
-                                         float* stage_w, int nd, int ns, int bh, int h, int g0, const Lane& L) {
+                                         float* stage_w, int nd, int ns, int bh, int h, int g0, const Lane& L,
+                                         const SeTables& se, const SeBwd& sb) {
     constexpr int NT = (WB + 16) / 8;
+    constexpr int SP = StagePitch<SE>::v;
     const int N = a.N, g = L.g, tig = L.tig;
     const int row_lo = g0 + g, row_hi = row_lo + 8;
     const bool ok_lo = INTERIOR || row_lo < N, ok_hi = INTERIOR || row_hi < N;
@@ -413,6 +441,25 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
     load_row(qb, qp + (size_t)row_hi * D, tig, ok_hi);
     load_row(da, dop + (size_t)row_lo * D, tig, ok_lo);
     load_row(db, dop + (size_t)row_hi * D, tig, ok_hi);
+    if (SE) {
+        build_qs_tile<D>(se, qa, qb, g, tig);
+        // the tile goes to global memory for the dK/dV kernel (rows of this warp, Jp floats each)
+        float2* dst = reinterpret_cast<float2*>(a.qs_rows + ((size_t)bh * N + g0) * se.Jp);
+        const int half = se.Jp / 2;
+#pragma unroll 1
+        for (int r = 0; r < 16; ++r) {
+            if (!INTERIOR && g0 + r >= N) break;
+            for (int c = L.lane; c < half; c += 32)
+                dst[r * half + c] = *reinterpret_cast<const float2*>(se.qs + r * se.pitch + 2 * c);
+        }
+        // and the query rows to shared memory for the CTA's dscale_embed partial
+        unsigned char* qrow = sb.q_s + (size_t)(L.warp * 16 + g) * (2 * D + 16) + 16 * tig;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+            *reinterpret_cast<uint4*>(qrow + 64 * c) = make_uint4(qa.r[4 * c], qa.r[4 * c + 1], qa.r[4 * c + 2], qa.r[4 * c + 3]);
+            *reinterpret_cast<uint4*>(qrow + 8 * (2 * D + 16) + 64 * c) = make_uint4(qb.r[4 * c], qb.r[4 * c + 1], qb.r[4 * c + 2], qb.r[4 * c + 3]);
+        }
+    }
     float delta_lo, delta_hi;
     {
         RowFrag<D> oa, ob;
@@ -439,9 +486,15 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
             const int nt = 2 * c + hf;
-            const float4 ini = init_s[nt * 32 + L.lane];
             const int4 so = soff_s[nt * 32 + L.lane];
-            float s[4] = {ini.x, ini.y, ini.z, ini.w}, dp[4];
+            float s[4], dp[4];
+            if (SE) {
+                const int4 qo = se.off[nt * 32 + L.lane];
+                s[0] = se.qs[qo.x]; s[1] = se.qs[qo.y]; s[2] = se.qs[qo.z]; s[3] = se.qs[qo.w];
+            } else {
+                const float4 ini = init_s[nt * 32 + L.lane];
+                s[0] = ini.x; s[1] = ini.y; s[2] = ini.z; s[3] = ini.w;
+            }
             RowFrag<D> vf;
             if (INTERIOR) {
                 load_row_at(kf[hf], kl + (8 * nt - WB) * D);
@@ -482,14 +535,21 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
     }
     // ---- sparse taps
     const float ls_lo = L.owner ? l2_lo : 1.0e30f, ls_hi = L.owner ? l2_hi : 1.0e30f;   // p == 0 on lanes without a diagonal entry
-    float* stage_sp = stage_w + nd * kStagePitch + g;
+    float* stage_sp = stage_w + nd * SP + g;
     auto finish = [&](int si, float sd0, float sd1, float dp0, float dp1, float pbv, bool v0, bool v1,
                       const RowFrag<D>& kf0, const RowFrag<D>& kf1) {
-        const float p0 = v0 ? ex2(fmaf(sd0, c2, pbv) - ls_lo) : 0.f;
-        const float p1 = v1 ? ex2(fmaf(sd1, c2, pbv) - ls_hi) : 0.f;
+        float y0, y1;
+        if (SE) {
+            y0 = (sd0 + se.qs[g * se.pitch + nd + si]) * c2;
+            y1 = (sd1 + se.qs[(g + 8) * se.pitch + nd + si]) * c2;
+        } else {
+            y0 = fmaf(sd0, c2, pbv); y1 = fmaf(sd1, c2, pbv);
+        }
+        const float p0 = v0 ? ex2(y0 - ls_lo) : 0.f;
+        const float p1 = v1 ? ex2(y1 - ls_hi) : 0.f;
         dgrow = fmaf(p0, dp0, dgrow); dgrow = fmaf(p1, dp1, dgrow);
         const float x0 = p0 * fmaf(gain, dp0, -delta_lo), x1 = p1 * fmaf(gain, dp1, -delta_hi);
-        if (L.owner) { stage_sp[si * kStagePitch] = x0; stage_sp[si * kStagePitch + 8] = x1; }
+        if (L.owner) { stage_sp[si * SP] = x0; stage_sp[si * SP + 8] = x1; }
         diag_fma<D>(dQ, __shfl_sync(0xffffffffu, x0, L.owner_lane), __shfl_sync(0xffffffffu, x1, L.owner_lane), kf0, kf1);
     };
     auto full_taps = [&](auto GC, int si) {
@@ -540,23 +600,81 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
         }
     }
     if (L.owner)                                          // taps no row of the tile reaches: zero entries
-        for (; si < ns; ++si) { stage_sp[si * kStagePitch] = 0.f; stage_sp[si * kStagePitch + 8] = 0.f; }
+        for (; si < ns; ++si) { stage_sp[si * SP] = 0.f; stage_sp[si * SP + 8] = 0.f; }
+    if (SE) {
+        // dQ += dS.scale_embed: the warp's ds values are complete in its 16 staging columns
+        __syncwarp();
+#pragma unroll 1
+        for (int kk = 0; kk < sb.JS / 16; ++kk) {
+            const float* col = stage_w + (16 * kk + 2 * tig) * SP + g;
+            const uint32_t a0 = pack_bf16x2(col[0], col[SP]), a1 = pack_bf16x2(col[8], col[SP + 8]);
+            const uint32_t a2 = pack_bf16x2(col[8 * SP], col[9 * SP]), a3 = pack_bf16x2(col[8 * SP + 8], col[9 * SP + 8]);
+#pragma unroll
+            for (int jn = 0; jn < D / 8; ++jn) {
+                const uint2 b = __ldg(sb.seb + (kk * (D / 8) + jn) * 32 + L.lane);
+                mma16816(dQ[jn], a0, a1, a2, a3, b.x, b.y);
+            }
+        }
+    }
     __nv_bfloat16* dqp = static_cast<__nv_bfloat16*>(a.dq) + base;
     store_acc_rows<D>(dQ, dqp + (size_t)row_lo * D, dqp + (size_t)row_hi * D, ok_lo, ok_hi, a.scale, a.scale, tig);
     return dgrow;
 }
 
-template <int D, int WB, int G, int CT>
+// One block: scale_embed split into bf16 halves [2][Jp][D] and, behind them, its B fragments for
+// dQ += dS.scale_embed, [JS/16][D/8][32] x uint2 in the element order of the dQ accumulators
+// (n-tile jn, column g  <->  d = 32 (jn/4) + 8 (g>>1) + 2 (jn%4) + (g&1)); rows j >= J are zero.
+template <int D>
+__global__ void se_prep_kernel(const float* __restrict__ scale_embed, int J, void* out) {
+    const int Jp = (J + 7) / 8 * 8, JS = (J + 15) / 16 * 16;
+    __nv_bfloat162* hi = static_cast<__nv_bfloat162*>(out);
+    __nv_bfloat162* lo = hi + Jp * D / 2;
+    for (int e = threadIdx.x; e < Jp * D / 2; e += blockDim.x) {
+        const int j = (2 * e) / D;
+        float2 x = make_float2(0.f, 0.f);
+        if (j < J) x = *reinterpret_cast<const float2*>(scale_embed + 2 * e);
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(x.x, x.y);
+        hi[e] = h2;
+        lo[e] = __floats2bfloat162_rn(x.x - __low2float(h2), x.y - __high2float(h2));
+    }
+    uint2* seb = reinterpret_cast<uint2*>(lo + Jp * D / 2);
+    for (int e = threadIdx.x; e < (JS / 16) * (D / 8) * 32; e += blockDim.x) {
+        const int ln = e & 31, jn = (e >> 5) % (D / 8), kk = (e >> 5) / (D / 8);
+        const int gg = ln >> 2, tt = ln & 3;
+        const int d = 32 * (jn / 4) + 8 * (gg >> 1) + 2 * (jn % 4) + (gg & 1);
+        const int j0 = 16 * kk + 2 * tt;
+        auto sev = [&](int j) { return j < J ? scale_embed[j * D + d] : 0.f; };
+        seb[e] = make_uint2(pack_bf16x2(sev(j0), sev(j0 + 1)), pack_bf16x2(sev(j0 + 8), sev(j0 + 9)));
+    }
+}
+
+inline size_t dq_smem_bytes(int J, int D, int NT, bool se) {
+    const int JS = se ? (J + 15) / 16 * 16 : J;
+    size_t n = sizeof(float) * ((size_t)(JS + 1) * (se ? kStagePitchSe : kStagePitch) + kWarps * 32);
+    if (se) {
+        n = (n + 15) / 16 * 16;
+        n += se_tables_bytes(J, D, NT, kWarps, 16);
+        n = (n + 15) / 16 * 16;
+        n += (size_t)kRows * (2 * D + 16);
+    }
+    return n;
+}
+
+template <int D, int WB, int G, int CT, bool SE>
 __global__ void __launch_bounds__(kWarps * 32, CT)
 bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
     constexpr int NT = (WB + 16) / 8;
-    extern __shared__ float stage[];                   // [J + 1][kStagePitch] ds values, then [128] dgain terms
-    __shared__ float4 init_s[NT * 32];
+    constexpr int SP = StagePitch<SE>::v;
+    extern __shared__ __align__(16) float stage[];     // [JS + 1][SP] ds values, then [128] dgain terms, then the scale_embed extras
+    __shared__ float4 init_s[SE ? 1 : NT * 32];
     __shared__ int4 soff_s[NT * 32];
     __shared__ int2 tap_s[DSQG_MAX_TAPS];
     const Lane L;
     const int bh = blockIdx.y, h = bh % a.H, N = a.N, J = t.J;
-    float* dg_s = stage + (J + 1) * kStagePitch;
+    const int JS = SE ? (J + 15) / 16 * 16 : J;         // staging rows (row JS is the dump for out-of-band entries)
+    float* dg_s = stage + (JS + 1) * SP;
+    SeTables se = {};
+    SeBwd sb = {};
     {
         const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1;
         const float inv_scale = 1.f / a.scale;
@@ -569,32 +687,76 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
                 const int i = gg + 8 * (r >> 1);
                 const int delta = WB + i - (8 * nt + 2 * tt + (r & 1));
                 const bool inband = delta >= d_lo && delta <= d_hi;
-                v[r] = inband ? a.pos_bias[(delta - d_lo) * a.H + h] * inv_scale : kNeg;
-                o[r] = (inband ? delta - d_lo : J) * kStagePitch + i;
+                v[r] = (!SE && inband) ? a.pos_bias[(delta - d_lo) * a.H + h] * inv_scale : kNeg;
+                o[r] = (inband ? delta - d_lo : JS) * SP + i;
             }
-            init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
+            if (!SE) init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
             soff_s[e] = make_int4(o[0], o[1], o[2], o[3]);
         }
         for (int si = threadIdx.x; si < t.n_sparse; si += kWarps * 32)
             tap_s[si] = make_int2(t.sparse[si], __float_as_int(a.pos_bias[(t.n_dense + si) * a.H + h] * kLog2e));
+        if (SE) {
+            unsigned char* p = reinterpret_cast<unsigned char*>(dg_s + kWarps * 32);
+            p = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(p) + 15) & ~uintptr_t(15));
+            se = fill_se_tables<D, WB, kWarps>(p, a.scale_embed, a.pos_bias, t, a.H, h, a.scale, L.warp, false, a.se_pre);
+            p += se_tables_bytes(J, D, NT, kWarps, 16);
+            p = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(p) + 15) & ~uintptr_t(15));
+            sb.JS = JS;
+            sb.seb = reinterpret_cast<const uint2*>(static_cast<const unsigned char*>(a.se_pre) + (size_t)2 * ((J + 7) / 8 * 8) * D * 2);
+            sb.q_s = p;
+            // staging rows J .. JS-1 take part in the dS MMAs: zero
+            for (int e = threadIdx.x; e < (JS - J) * kRows; e += kWarps * 32)
+                stage[(J + e / kRows) * SP + e % kRows] = 0.f;
+        }
     }
     __syncthreads();
     const int g0 = blockIdx.x * kRows + L.warp * 16;
     float* stage_w = stage + L.warp * 16;
     float dgrow = 0.f;
-    if (g0 >= N) {                                      // no rows: this warp's staging columns are zero
-        for (int e = L.lane; e < J * 16; e += 32) stage_w[(e >> 4) * kStagePitch + (e & 15)] = 0.f;
+    if (g0 >= N) {                                      // no rows: this warp's staging columns (and query rows) are zero
+        for (int e = L.lane; e < J * 16; e += 32) stage_w[(e >> 4) * SP + (e & 15)] = 0.f;
+        if (SE)
+            for (int e = L.lane; e < 16 * (2 * D + 16) / 16; e += 32)
+                reinterpret_cast<uint4*>(sb.q_s + (size_t)L.warp * 16 * (2 * D + 16))[e] = make_uint4(0u, 0u, 0u, 0u);
     } else if (g0 >= WB && g0 + 16 <= N) {
-        dgrow = dq_tile<D, WB, true, G>(a, init_s, soff_s, tap_s, stage_w, t.n_dense, t.n_sparse, bh, h, g0, L);
+        dgrow = dq_tile<D, WB, true, G, SE>(a, init_s, soff_s, tap_s, stage_w, t.n_dense, t.n_sparse, bh, h, g0, L, se, sb);
     } else {
-        dgrow = dq_tile<D, WB, false, G>(a, init_s, soff_s, tap_s, stage_w, t.n_dense, t.n_sparse, bh, h, g0, L);
+        dgrow = dq_tile<D, WB, false, G, SE>(a, init_s, soff_s, tap_s, stage_w, t.n_dense, t.n_sparse, bh, h, g0, L, se, sb);
     }
     dg_s[threadIdx.x] = dgrow;
     __syncthreads();
     const int tile = bh * a.tiles_per_bh + blockIdx.x;
+    if (SE) {
+        // CTA partial of dscale_embed = scale * dS^T[JS x 64] . Q[64 x D]; warp w takes n-tiles w, w+4, ...
+        constexpr int QP = 2 * D + 16;
+        const uint32_t q_base = static_cast<uint32_t>(__cvta_generic_to_shared(sb.q_s));
+#pragma unroll 1
+        for (int jn = L.warp; jn < D / 8; jn += kWarps) {
+#pragma unroll 1
+            for (int mt = 0; mt < JS / 16; ++mt) {
+                float c[4];
+#pragma unroll
+                for (int kk = 0; kk < kRows / 16; ++kk) {
+                    const float* r0 = stage + (16 * mt + L.g) * SP + 16 * kk + 2 * L.tig;
+                    const float2 u0 = *reinterpret_cast<const float2*>(r0), u1 = *reinterpret_cast<const float2*>(r0 + 8 * SP);
+                    const float2 u2 = *reinterpret_cast<const float2*>(r0 + 8), u3 = *reinterpret_cast<const float2*>(r0 + 8 * SP + 8);
+                    uint32_t b0, b1;
+                    const uint32_t addr = q_base + (16 * kk + (L.lane & 15)) * QP + 16 * jn;
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+                    const uint32_t a0 = pack_bf16x2(u0.x, u0.y), a1 = pack_bf16x2(u1.x, u1.y);
+                    const uint32_t a2 = pack_bf16x2(u2.x, u2.y), a3 = pack_bf16x2(u3.x, u3.y);
+                    if (kk == 0) mma16816_z(c, a0, a1, a2, a3, b0, b1); else mma16816(c, a0, a1, a2, a3, b0, b1);
+                }
+                // the tile's partial goes to global memory; dse_group_kernel adds the tiles of a group
+                float* dst = a.dse_tmp + (size_t)tile * J * D + (16 * mt + L.g) * D + 8 * jn + 2 * L.tig;
+                if (16 * mt + L.g < J) *reinterpret_cast<float2*>(dst) = make_float2(c[0] * a.scale, c[1] * a.scale);
+                if (16 * mt + L.g + 8 < J) *reinterpret_cast<float2*>(dst + 8 * D) = make_float2(c[2] * a.scale, c[3] * a.scale);
+            }
+        }
+    }
     if (threadIdx.x < J) {
         float s = 0.f;
-        const float* row = stage + threadIdx.x * kStagePitch;
+        const float* row = stage + threadIdx.x * SP;
 #pragma unroll 8
         for (int r = 0; r < kRows; ++r) s += row[r];
         a.dpb_part[(size_t)tile * J + threadIdx.x] = s;
@@ -605,14 +767,37 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
     }
 }
 
+// dscale_embed partials: one block per group of kSeGroup consecutive 64-row tiles of a sequence adds
+// the tiles' partials (written by the dQ kernel) in tile order.
+__global__ void __launch_bounds__(256)
+dse_group_kernel(const float* __restrict__ tmp, float* __restrict__ part, int tiles_per_bh, int groups_bh, int JD) {
+    const int bh = blockIdx.y, grp = blockIdx.x, first = grp * kSeGroup;
+    const int members = tiles_per_bh - first < kSeGroup ? tiles_per_bh - first : kSeGroup;
+    const float* src = tmp + ((size_t)bh * tiles_per_bh + first) * JD;
+    float* out = part + ((size_t)bh * groups_bh + grp) * JD;
+    for (int e = threadIdx.x; e < JD; e += 256) {
+        float x[kSeGroup];
+#pragma unroll
+        for (int r = 0; r < kSeGroup; ++r) x[r] = r < members ? __ldg(src + (size_t)r * JD + e) : 0.f;
+        float s = x[0];
+#pragma unroll
+        for (int r = 1; r < kSeGroup; ++r) s += x[r];
+        out[e] = s;
+    }
+}
+
 // ------------------------------------------------------------------------------ backward: dK, dV
 // The warp owns 16 key rows; the roles of rows and columns are swapped: S^T = K.Q^T over the
 // query rows [m0, m0+16+WB) for the dense window and the diagonal of the tile at m0+delta for
 // every sparse tap.  Key rows are owned by exactly one warp: no atomics.  The per-query
 // statistics {lse*log2(e), delta} of the CTA's dense query range sit in shared memory.
-template <int D, int WB, bool INTERIOR, int G>
+// With scale_embed the score accumulators of the dense window start from qsd, the CTA's copy of the
+// dense part of qs_rows (row = query, nd + 1 columns, the last one holding the mask value), and a
+// sparse tap adds the entry of its query row read from global memory.
+template <int D, int WB, bool INTERIOR, int G, bool SE>
 __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s, const int2* tap_s, const float2* stat_w,
-                                          int ns, int bh, int h, int m0, const Lane& L) {
+                                          int ns, int bh, int h, int m0, const Lane& L, const float* qsd_w,
+                                          const int4* qoff, int nd, int Jp) {
     constexpr int NT = (WB + 16) / 8;
     const int N = a.N, g = L.g, tig = L.tig;
     const int row_lo = m0 + g, row_hi = row_lo + 8;
@@ -642,8 +827,14 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
             const int nt = 2 * c + hf;
-            const float4 ini = init_s[nt * 32 + L.lane];
-            float s[4] = {ini.x, ini.y, ini.z, ini.w}, dp[4];
+            float s[4], dp[4];
+            if (SE) {
+                const int4 qo = qoff[nt * 32 + L.lane];
+                s[0] = qsd_w[qo.x]; s[1] = qsd_w[qo.y]; s[2] = qsd_w[qo.z]; s[3] = qsd_w[qo.w];
+            } else {
+                const float4 ini = init_s[nt * 32 + L.lane];
+                s[0] = ini.x; s[1] = ini.y; s[2] = ini.z; s[3] = ini.w;
+            }
             if (INTERIOR) {
                 load_row_at(qf[hf], ql + 8 * nt * D);
                 load_row_at(df[hf], dl + 8 * nt * D);
@@ -684,9 +875,13 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
         }
     }
     // ---- sparse taps
-    auto finish = [&](float sd0, float sd1, float dp0, float dp1, float pbv, float2 st0, float2 st1,
+    const float* qs_r = SE ? a.qs_rows + ((size_t)bh * N + row_lo) * Jp + nd : nullptr;   // entry of tap si of query row row_lo + delta: qs_r[delta * Jp + si]
+    // b0/b1: what is added to the raw score: the bias in log2 units (plain) or the qs_rows entry of
+    // the query row, in units of 1/scale (scale_embed)
+    auto finish = [&](float sd0, float sd1, float dp0, float dp1, float b0, float b1, float2 st0, float2 st1,
                       const RowFrag<D>& qf0, const RowFrag<D>& qf1, const RowFrag<D>& df0, const RowFrag<D>& df1) {
-        const float p0 = ex2(fmaf(sd0, c2, pbv) - st0.x), p1 = ex2(fmaf(sd1, c2, pbv) - st1.x);
+        const float y0 = SE ? (sd0 + b0) * c2 : fmaf(sd0, c2, b0), y1 = SE ? (sd1 + b1) * c2 : fmaf(sd1, c2, b1);
+        const float p0 = ex2(y0 - st0.x), p1 = ex2(y1 - st1.x);
         const float w0 = p0 * gain, w1 = p1 * gain;
         const float x0 = p0 * fmaf(gain, dp0, -st0.y), x1 = p1 * fmaf(gain, dp1, -st1.y);
         diag_fma<D>(dV, __shfl_sync(0xffffffffu, w0, L.owner_lane), __shfl_sync(0xffffffffu, w1, L.owner_lane), df0, df1);
@@ -696,12 +891,17 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
         constexpr int GG = decltype(GC)::value;
         RowFrag<D> qf0[GG], qf1[GG], df0[GG], df1[GG];
         float2 st0[GG], st1[GG];
-        float pbv[GG];
+        float b0[GG], b1[GG];
 #pragma unroll
         for (int i = 0; i < GG; ++i) {
             const int2 tp = tap_s[si + i];
             const ptrdiff_t off = (ptrdiff_t)tp.x * D;
-            pbv[i] = __int_as_float(tp.y);
+            if (SE) {
+                b0[i] = __ldg(qs_r + (size_t)tp.x * Jp + si + i);
+                b1[i] = __ldg(qs_r + (size_t)(tp.x + 8) * Jp + si + i);
+            } else {
+                b0[i] = b1[i] = __int_as_float(tp.y);
+            }
             load_row_at(qf0[i], ql + off);
             load_row_at(qf1[i], ql + off + 8 * D);
             load_row_at(df0[i], dl + off);
@@ -715,7 +915,7 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
             mma_rows_z(s0, ka, kb, qf0[i]); mma_rows_z(s1, ka, kb, qf1[i]);
             mma_rows_z(e0, va, vb, df0[i]); mma_rows_z(e1, va, vb, df1[i]);
             finish((g & 1) ? s0[1] : s0[0], (g & 1) ? s1[3] : s1[2], (g & 1) ? e0[1] : e0[0], (g & 1) ? e1[3] : e1[2],
-                   pbv[i], st0[i], st1[i], qf0[i], qf1[i], df0[i], df1[i]);
+                   b0[i], b1[i], st0[i], st1[i], qf0[i], qf1[i], df0[i], df1[i]);
         }
     };
     int si = 0;
@@ -727,8 +927,12 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
         if (m0 + 16 + delta <= N) {
             full_taps(std::integral_constant<int, 1>(), si);
         } else {
-            const float pbv = __int_as_float(tap_s[si].y);
             const bool v0 = row_lo + delta < N, v1 = row_hi + delta < N;
+            float b0 = __int_as_float(tap_s[si].y), b1 = b0;
+            if (SE) {
+                b0 = v0 ? __ldg(qs_r + (size_t)delta * Jp + si) : 0.f;
+                b1 = v1 ? __ldg(qs_r + (size_t)(delta + 8) * Jp + si) : 0.f;
+            }
             const ptrdiff_t off = (ptrdiff_t)delta * D - 8 * tig;
             RowFrag<D> qf0, qf1, df0, df1;
             load_row(qf0, ql + off, tig, v0);
@@ -741,7 +945,7 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
             mma_rows_z(s0, ka, kb, qf0); mma_rows_z(s1, ka, kb, qf1);
             mma_rows_z(e0, va, vb, df0); mma_rows_z(e1, va, vb, df1);
             finish((g & 1) ? s0[1] : s0[0], (g & 1) ? s1[3] : s1[2], (g & 1) ? e0[1] : e0[0], (g & 1) ? e1[3] : e1[2],
-                   pbv, st0, st1, qf0, qf1, df0, df1);
+                   b0, b1, st0, st1, qf0, qf1, df0, df1);
         }
     }
     __nv_bfloat16* dkp = static_cast<__nv_bfloat16*>(a.dk) + base;
@@ -750,48 +954,84 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
     store_acc_rows<D>(dV, dvp + (size_t)row_lo * D, dvp + (size_t)row_hi * D, ok_lo, ok_hi, 1.f, 1.f, tig);
 }
 
-template <int D, int WB, int G, int CT>
+inline size_t dkdv_smem_bytes(int n_dense, int WB, bool se) {
+    return se ? (size_t)(kRows + WB) * (n_dense + 1) * 4 : 0;
+}
+
+template <int D, int WB, int G, int CT, bool SE>
 __global__ void __launch_bounds__(kWarps * 32, CT)
 bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t, const int n_reduce, const int reduce_stride) {
     constexpr int NT = (WB + 16) / 8;
     constexpr int kStat = kRows + WB;                  // query rows the CTA's dense windows touch
-    __shared__ float4 init_s[NT * 32];
+    extern __shared__ __align__(16) float qsd[];       // scale_embed: [kStat][n_dense + 1]
+    __shared__ float4 init_s[NT * 32];                 // plain: score start values; scale_embed: int4 offsets into qsd
     __shared__ int2 tap_s[DSQG_MAX_TAPS];
     __shared__ __align__(16) float2 stat_s[kStat];
     const Lane L;
     const int bh = blockIdx.y, h = bh % a.H, N = a.N;
     // n_reduce CTAs (every reduce_stride-th one, so that no wave of CTAs is delayed as a whole)
-    // also finish dpos_bias / dhead_gain: one output each, from the partial sums the dQ kernel
+    // also finish the parameter gradients: one output each, from the partial sums the dQ kernel
     // (an earlier launch on the stream) left in the scratch.
     static_assert(kWarps * 32 == kReduceThreads, "the fused reduction uses the CTA as one reduce block");
     const int cta = blockIdx.y * gridDim.x + blockIdx.x;
     if (cta % reduce_stride == 0 && cta / reduce_stride < n_reduce)
         reduce_one_param(a, t.J, cta / reduce_stride, reinterpret_cast<float*>(init_s));
     const int m_cta = blockIdx.x * kRows;
+    const int nd = t.n_dense, ndp = nd + 1, Jp = (t.J + 7) / 8 * 8;
     {
         const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1;
         const float inv_scale = 1.f / a.scale;
         for (int e = threadIdx.x; e < NT * 32; e += kWarps * 32) {
             const int nt = e >> 5, gg = (e & 31) >> 2, tt = e & 3;
             float v[4];
+            int o[4];
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
-                const int delta = 8 * nt + 2 * tt + (r & 1) - (gg + 8 * (r >> 1));
-                v[r] = (delta >= d_lo && delta <= d_hi) ? a.pos_bias[(delta - d_lo) * a.H + h] * inv_scale : kNeg;
+                const int cc = 8 * nt + 2 * tt + (r & 1);
+                const int delta = cc - (gg + 8 * (r >> 1));
+                const bool inband = delta >= d_lo && delta <= d_hi;
+                v[r] = (!SE && inband) ? a.pos_bias[(delta - d_lo) * a.H + h] * inv_scale : kNeg;
+                o[r] = cc * ndp + (inband ? delta - d_lo : nd);       // column nd of every row holds the mask value
             }
-            init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
+            if (SE) reinterpret_cast<int4*>(init_s)[e] = make_int4(o[0], o[1], o[2], o[3]);
+            else init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
         }
         for (int si = threadIdx.x; si < t.n_sparse; si += kWarps * 32)
             tap_s[si] = make_int2(t.sparse[si], __float_as_int(a.pos_bias[(t.n_dense + si) * a.H + h] * kLog2e));
         const float2* rs = reinterpret_cast<const float2*>(a.delta) + (size_t)bh * N;
         for (int i = threadIdx.x; i < kStat; i += kWarps * 32)
             stat_s[i] = m_cta + i < N ? rs[m_cta + i] : make_float2(0.f, 0.f);
+        if (SE) {
+            const float* src = a.qs_rows + ((size_t)bh * N + m_cta) * Jp;
+            // warp w copies rows w, w+4, ...; eight rows per batch so that their loads overlap
+            constexpr int kBatch = 8;
+            for (int c = L.lane; c < ndp; c += 32) {
+#pragma unroll 1
+                for (int r0 = L.warp; r0 < kStat; r0 += kWarps * kBatch) {
+                    float x[kBatch];
+#pragma unroll
+                    for (int u = 0; u < kBatch; ++u) {
+                        const int r = r0 + kWarps * u;
+                        x[u] = (c < nd && r < kStat && m_cta + r < N) ? __ldg(src + (size_t)r * Jp + c) : (c == nd ? kNeg : 0.f);
+                    }
+#pragma unroll
+                    for (int u = 0; u < kBatch; ++u) {
+                        const int r = r0 + kWarps * u;
+                        if (r < kStat) qsd[r * ndp + c] = x[u];
+                    }
+                }
+            }
+        }
     }
     __syncthreads();
     const int m0 = m_cta + L.warp * 16;
     if (m0 >= N) return;
-    if (m0 + 16 + WB <= N) dkdv_tile<D, WB, true, G>(a, init_s, tap_s, stat_s + L.warp * 16, t.n_sparse, bh, h, m0, L);
-    else dkdv_tile<D, WB, false, G>(a, init_s, tap_s, stat_s + L.warp * 16, t.n_sparse, bh, h, m0, L);
+    const float* qsd_w = qsd + L.warp * 16 * ndp;
+    const int4* qoff = reinterpret_cast<const int4*>(init_s);
+    if (m0 + 16 + WB <= N)
+        dkdv_tile<D, WB, true, G, SE>(a, init_s, tap_s, stat_s + L.warp * 16, t.n_sparse, bh, h, m0, L, qsd_w, qoff, nd, Jp);
+    else
+        dkdv_tile<D, WB, false, G, SE>(a, init_s, tap_s, stat_s + L.warp * 16, t.n_sparse, bh, h, m0, L, qsd_w, qoff, nd, Jp);
 }
 
 template <int D, int WB>
@@ -801,7 +1041,7 @@ cudaError_t fwd_launch_mma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
     if (a.scale_embed) {
         if constexpr (D <= 64) {
             const size_t smem = se_tables_bytes(t.J, D, (WB + 16) / 8, W, 16);
-            if (smem > 48 * 1024) {
+            if (smem > 32 * 1024) {        // static shared memory counts against the 48 KB default as well
                 cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<D, WB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 if (e != cudaSuccess) return e;
             }
@@ -815,34 +1055,58 @@ cudaError_t fwd_launch_mma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
     return cudaGetLastError();
 }
 
-template <int D, int WB>
-cudaError_t bwd_launch_mma(BwdArgs a, const Taps& t, cudaStream_t s, int stages) {
+template <int D, int WB, bool SE>
+cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stages) {
     using T = BwdTune<D>;
-    carve_bwd_scratch(a, kRows, t.J, false);
+    constexpr int NT = (WB + 16) / 8;
+    if (SE) carve_bwd_scratch_mma_se(a, t.J); else carve_bwd_scratch(a, kRows, t.J, false);
     dim3 grid((a.N + kRows - 1) / kRows, a.B * a.H);
     cudaError_t e = cudaSuccess;
     if (stages & DSQG_BWD_STAGE_DQ) {
-        const size_t smem = sizeof(float) * ((size_t)(t.J + 1) * kStagePitch + kWarps * 32);
-        if (smem > 48 * 1024) {
-            e = cudaFuncSetAttribute(bwd_dq_mma_kernel<D, WB, T::dq_group, T::dq_ctas>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (SE) {
+            se_prep_kernel<D><<<1, 1024, 0, s>>>(a.scale_embed, t.J, a.se_pre);
+            if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        }
+        auto kern = bwd_dq_mma_kernel<D, WB, T::dq_group, SE ? T::dq_ctas_se : T::dq_ctas, SE>;
+        const size_t smem = dq_smem_bytes(t.J, D, NT, SE);
+        if (smem > 32 * 1024) {        // static shared memory counts against the 48 KB default as well
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
         }
-        bwd_dq_mma_kernel<D, WB, T::dq_group, T::dq_ctas><<<grid, kWarps * 32, smem, s>>>(a, t);
+        kern<<<grid, kWarps * 32, smem, s>>>(a, t);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        if (SE) {
+            const int groups_bh = (a.tiles_per_bh + kSeGroup - 1) / kSeGroup;
+            dse_group_kernel<<<dim3(groups_bh, a.B * a.H), 256, 0, s>>>(a.dse_tmp, a.dse_part, a.tiles_per_bh, groups_bh, t.J * a.D);
+            if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        }
     }
-    // With both stages in one call the reduction rides on the first CTAs of the dK/dV kernel
-    // (same code, same order of additions as the stand-alone kernel: bitwise equal results).
-    const int n_out = t.J * a.H + a.H;
+    // With both stages in one call the reduction rides on CTAs of the dK/dV kernel (same code,
+    // same order of additions as the stand-alone kernel: bitwise equal results).
+    const int n_out = t.J * a.H + a.H + (SE ? t.J * a.D : 0);
     const bool fuse = (stages & DSQG_BWD_STAGE_DKDV) && (stages & DSQG_BWD_STAGE_REDUCE) &&
                       (long long)grid.x * grid.y >= n_out;
     if (stages & DSQG_BWD_STAGE_DKDV) {
-        bwd_dkdv_mma_kernel<D, WB, T::dkdv_group, T::dkdv_ctas><<<grid, kWarps * 32, 0, s>>>(
-            a, t, fuse ? n_out : 0, fuse ? (int)((long long)grid.x * grid.y / n_out) : 1);
+        auto kern = bwd_dkdv_mma_kernel<D, WB, T::dkdv_group, T::dkdv_ctas, SE>;
+        const size_t smem = dkdv_smem_bytes(t.n_dense, WB, SE);
+        if (smem > 32 * 1024) {        // static shared memory counts against the 48 KB default as well
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+        }
+        kern<<<grid, kWarps * 32, smem, s>>>(a, t, fuse ? n_out : 0, fuse ? (int)((long long)grid.x * grid.y / n_out) : 1);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
     if ((stages & DSQG_BWD_STAGE_REDUCE) && !fuse) e = launch_reduce_params(a, t.J, s);
     return e;
+}
+
+template <int D, int WB>
+cudaError_t bwd_launch_mma(const BwdArgs& a, const Taps& t, cudaStream_t s, int stages) {
+    if (a.scale_embed) {
+        if constexpr (D <= 64) return bwd_launch_mma_se<D, WB, true>(a, t, s, stages);
+        else return cudaErrorInvalidValue;
+    }
+    return bwd_launch_mma_se<D, WB, false>(a, t, s, stages);
 }
 
 int band_width(const Taps& t) {
@@ -861,7 +1125,7 @@ bool mma_fwd_supported(int dtype, int D, const Taps& t, bool has_scale_embed) {
     return mma_shape_supported(dtype, D, t) && (!has_scale_embed || D <= 64);
 }
 bool mma_path_supported(int dtype, int D, const Taps& t, bool has_scale_embed) {
-    return mma_shape_supported(dtype, D, t) && !has_scale_embed;
+    return mma_shape_supported(dtype, D, t) && (!has_scale_embed || D <= 64);
 }
 
 #define DSQG_MMA_DISPATCH(FN, ...)                                             \

@@ -109,7 +109,8 @@ def test_bf16_wide_heads_vs_oracle(shape, path):
         lib.dsqg_set_kernel_path(0)
 
 
-@pytest.mark.parametrize("shape", [(1, 4, 64, 32), (2, 2, 1600, 32), (1, 3, 200, 64), (1, 2, 100, 80)])
+@pytest.mark.parametrize("shape", [(1, 4, 64, 32), (2, 2, 1600, 32), (1, 3, 200, 64), (1, 2, 100, 80),
+                                   (1, 2, 576, 32), (1, 2, 2047, 64), (1, 1, 1, 32), (2, 1, 17, 64)])
 def test_bf16_scale_embed_and_gain_vs_oracle(shape):
     B, H, N, D = shape
     g = torch.Generator().manual_seed(7 + N)
@@ -260,8 +261,9 @@ def test_bitwise_determinism_and_no_unwritten_rows():
         assert torch.equal(x, y)
 
 
+@pytest.mark.parametrize("with_se", [False, True])
 @pytest.mark.parametrize("shape", [(3, 8, 2047, 32), (2, 3, 700, 64), (1, 2, 40, 32)])
-def test_fused_parameter_reduction_equals_staged_backward_bitwise(shape):
+def test_fused_parameter_reduction_equals_staged_backward_bitwise(shape, with_se):
     """Tensor-core path: one dsqg_bwd call lets the first CTAs of the dK/dV kernel finish dpos_bias
     and dhead_gain; running the three stages as separate calls uses the stand-alone reduction
     kernel.  Same additions in the same order: every output is bit-identical, none unwritten."""
@@ -273,25 +275,29 @@ def test_fused_parameter_reduction_equals_staged_backward_bitwise(shape):
     q, k, v, dout = mk(), mk(), mk(), mk()
     pb = (torch.randn(43, H, generator=g) * 0.5).to(dev)
     gain = (torch.rand(H, generator=g) + 0.5).to(dev)
+    se = (torch.randn(43, D, generator=g) * 0.05).to(dev) if with_se else None
+    sep = se.data_ptr() if with_se else None
     off, J = _lib.offsets_array(O.OFFSETS_43)
     stream = torch.cuda.current_stream().cuda_stream
     out = torch.empty_like(q); lse = torch.empty(B, H, N, device=dev)
-    _lib.check(lib.dsqg_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), None, gain.data_ptr(),
+    _lib.check(lib.dsqg_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), sep, gain.data_ptr(),
                             off, J, out.data_ptr(), lse.data_ptr(), B, H, N, D, 0, stream), "fwd")
 
     def run(stage_list):
         nan = float("nan")
         dq, dk, dv = (torch.full_like(q, nan) for _ in range(3))
         dpb = torch.full((J, H), nan, device=dev); dg = torch.full((H,), nan, device=dev)
-        nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, 0)
+        dse = torch.full((J, D), nan, device=dev)
+        nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, int(with_se))
         scratch = torch.full((nbytes // 4,), nan, device=dev)
         for st in stage_list:
-            _lib.check(lib.dsqg_bwd_stages(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), None,
+            _lib.check(lib.dsqg_bwd_stages(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), sep,
                                            gain.data_ptr(), off, J, out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
-                                           dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dpb.data_ptr(), None,
+                                           dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dpb.data_ptr(),
+                                           dse.data_ptr() if with_se else None,
                                            dg.data_ptr(), scratch.data_ptr(), nbytes, B, H, N, D, 0, stream, st), "bwd")
         torch.cuda.synchronize()
-        return dq, dk, dv, dpb, dg
+        return (dq, dk, dv, dpb, dg) + ((dse,) if with_se else ())
 
     fused, staged = run([7]), run([1, 2, 4])
     for x, y in zip(fused, staged):
