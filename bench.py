@@ -122,20 +122,26 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     out = torch.empty_like(q); lse = torch.empty(B, H, N, device=dev)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
     dpb = torch.empty(J, H, device=dev); dg = torch.empty(H, device=dev)
-    nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, 0)
+    se = None
+    if args.scale_embed:
+        se = (torch.randn(J, D, generator=torch.Generator().manual_seed(1234)) * 0.05).to(dev)
+    sep = None if se is None else se.data_ptr()
+    dse = None if se is None else torch.empty(J, D, device=dev)
+    nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, int(se is not None))
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream()
     sp = stream.cuda_stream
     dt = 0 if cfg.dtype == torch.bfloat16 else 1
 
     def fwd():
-        _lib.check(lib.dsqg_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), None, gain.data_ptr(),
+        _lib.check(lib.dsqg_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), sep, gain.data_ptr(),
                                 off, J, out.data_ptr(), lse.data_ptr(), B, H, N, D, dt, sp), "dsqg_fwd")
 
     def bwd(stages):
-        _lib.check(lib.dsqg_bwd_stages(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), None,
+        _lib.check(lib.dsqg_bwd_stages(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), sep,
                                        gain.data_ptr(), off, J, out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
-                                       dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dpb.data_ptr(), None,
+                                       dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dpb.data_ptr(),
+                                       None if dse is None else dse.data_ptr(),
                                        dg.data_ptr(), scratch.data_ptr(), nbytes, B, H, N, D, dt, sp, stages),
                    "dsqg_bwd_stages")
 
@@ -168,12 +174,12 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     # downloads out, dq, dk, dv into pinned host memory; the copies of neighbouring steps overlap
     # the kernels (three streams, two sets of device buffers), all inside the timed region.
     res_host = {nm: torch.empty(q.shape, dtype=q.dtype).pin_memory() for nm in ("out", "dq", "dk", "dv")}
-    pipe = dwarf_b200.DSQGHostPipeline((B, H, N, D), q.dtype, cfg.offsets, dev, depth=2)
+    pipe = dwarf_b200.DSQGHostPipeline((B, H, N, D), q.dtype, cfg.offsets, dev, depth=2, scale_embed=se is not None)
     e2e_steps = max(3, min(args.steps, 20))
 
     def e2e_step():
         pipe.submit(host["q"], host["k"], host["v"], host["dout"], pb, gain,
-                    res_host["out"], res_host["dq"], res_host["dk"], res_host["dv"])
+                    res_host["out"], res_host["dq"], res_host["dk"], res_host["dv"], scale_embed=se)
 
     for _ in range(3):
         e2e_step()
@@ -192,7 +198,7 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     peak, peak_src = measured_peaks()
     # DRAM bytes (read + write) per launch from the ncu capture summarised in
     # profiles/dsqg_mma_kernels_cfg1.md; only known for the workload that was captured.
-    ncu_traffic = {"cfg1": [120.30e6, 197.12e6, 186.98e6]}.get(args.workload, [None] * 3)
+    ncu_traffic = {"cfg1": [120.30e6, 197.12e6, 186.98e6]}.get("" if se is not None else args.workload, [None] * 3)
     names = ["dsqg_fwd", "dsqg_bwd_dq", "dsqg_bwd_dkdv"]
     alg = [4 * T, 6 * T, 6 * T]           # per launch: fwd Q,K,V->O ; dq Q,K,V,O,dO->dQ ; dkdv Q,K,V,dO->dK,dV
     top = max(range(3), key=lambda s: kern_ms[s])
@@ -203,13 +209,13 @@ def run_op_workload(args, cfg, rank, local_rank, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if cfg.dtype == torch.bfloat16 else "f32", "data": "synthetic",
-        "config": {"workload": cfg.name, "tokens_per_step_per_gpu": B * N,
+        "config": {"workload": cfg.name + (" +scale_embed" if se is not None else ""), "tokens_per_step_per_gpu": B * N,
                    "l2": "inputs+outputs per step (>= 400 MB) exceed the 126 MB L2; no flush",
                    "parallelism": f"batch replicated x{world}, no collective"},
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": 4 * T, "d2h_bytes_per_step": 4 * T, "ms_per_step": e2e_ms,
                 "steps": e2e_steps},
-        "gpu_launches": (3 if args.kernel_path in (0, 2) else 4) * args.steps,   # other paths reduce in a 4th kernel
+        "gpu_launches": ((3 if args.kernel_path in (0, 2) else 4) + (2 if se is not None and args.kernel_path in (0, 2) else 0)) * args.steps,   # other paths reduce in a 4th kernel
         "roofline": {"bound": "hbm", "kernel": names[top], "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": ncu_traffic[top], "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": alg[top], "ms_per_launch": kern_ms[top]},
@@ -389,7 +395,7 @@ def run_train_workload(args, rank, local_rank, world):
 
 
 # ----------------------------------------------------------------------------- CPU legs
-def cpu_reference_time(cfg, sample_B, repeats, fwd_bwd=True):
+def cpu_reference_time(cfg, sample_B, repeats, fwd_bwd=True, with_se=False):
     """Times the PyTorch restatement of the reference's DSQG path (oracle/dsqg_oracle.py, a
     line-for-line generalisation of kernels/dsqg_attention_v3.py:543-561) on the host cores.
     This is the one place outside tests/ where oracle/ is executed: as the measured baseline."""
@@ -397,14 +403,17 @@ def cpu_reference_time(cfg, sample_B, repeats, fwd_bwd=True):
     from oracle import dsqg_oracle as O
     torch.set_num_threads(os.cpu_count() or 1)
     x = synth.make_op_inputs(cfg, B=sample_B)
+    se = None
+    if with_se:
+        se = torch.randn(len(cfg.offsets), cfg.D, generator=torch.Generator().manual_seed(1234)) * 0.05
     best = float("inf")
     for _ in range(repeats):
         t0 = time.perf_counter()
         if fwd_bwd:
-            O.dsqg_reference_grads(x["q"], x["k"], x["v"], x["pos_bias"], x["dout"], None, x["head_gain"],
+            O.dsqg_reference_grads(x["q"], x["k"], x["v"], x["pos_bias"], x["dout"], se, x["head_gain"],
                                    cfg.offsets, chunk=1)
         else:
-            O.dsqg_reference_chunked(x["q"], x["k"], x["v"], x["pos_bias"], None, x["head_gain"], cfg.offsets, 1)
+            O.dsqg_reference_chunked(x["q"], x["k"], x["v"], x["pos_bias"], se, x["head_gain"], cfg.offsets, 1)
         best = min(best, time.perf_counter() - t0)
     return sample_B * cfg.N / best, best
 
@@ -418,9 +427,12 @@ def run_reference_arm(args, cfg):
     from oracle import dsqg_oracle as O
     torch.set_num_threads(os.cpu_count() or 1)
     x = synth.make_op_inputs(cfg, B=sample_B)
+    se = None
+    if args.scale_embed:
+        se = torch.randn(len(cfg.offsets), cfg.D, generator=torch.Generator().manual_seed(1234)) * 0.05
 
     def step():
-        O.dsqg_reference_grads(x["q"], x["k"], x["v"], x["pos_bias"], x["dout"], None, x["head_gain"],
+        O.dsqg_reference_grads(x["q"], x["k"], x["v"], x["pos_bias"], x["dout"], se, x["head_gain"],
                                cfg.offsets, chunk=1)
     for _ in range(min(args.warmup, 1)):
         step()
@@ -451,6 +463,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="cfg1", choices=["cfg1", "cfg2", "cfg2_4k", "cfg3", "cfg4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scale-embed", action="store_true",
+                    help="op workloads: add the condU scale_embed term (seeded N(0, 0.05) [J,D]) and its gradient")
     ap.add_argument("--decode-layers", type=int, default=0, help="cfg3: number of layers (default: the 10 of the configuration)")
     ap.add_argument("--kernel-path", type=int, default=0,
                     help="dsqg_set_kernel_path value for A/B runs: 0 automatic (default), 1 generic, 2 tensor-core "
@@ -488,7 +502,7 @@ def main():
         line = run_op_workload(args, cfg, rank, local_rank, world)
         if rank == 0 and world == 1 and not args.no_cpu_baseline:
             sample_B = min(cfg.B, 32)
-            val, secs = cpu_reference_time(cfg, sample_B, repeats=4)
+            val, secs = cpu_reference_time(cfg, sample_B, repeats=4, with_se=args.scale_embed)
             line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": torch.get_num_threads(),
                                     "kind": "port",
                                     "sample": f"{sample_B} of {cfg.B} batch entries ({sample_B * cfg.N} tokens), "

@@ -45,7 +45,7 @@ struct BwdArgs {
     float* dg_part;    // [n_tiles]
     float* dse_part;   // [n_dse_blocks, J, D] (only with scale_embed)
     float* qs_rows;    // [B*H*N, Jp] q.scale_embed[j] + pos_bias[j]/scale per row (tensor-core kernels with scale_embed)
-    void* se_pre;      // scale_embed as split bf16 [2][Jp][D] followed by its dS.SE B fragments (same kernels)
+    void* se_pre;      // tables of se_prep_kernel: split scale_embed, its dS.SE fragments, pos_bias/scale, offsets (same kernels)
     float* dse_tmp;    // [n_tiles, J, D] dscale_embed partial of every 64-row tile (same kernels)
     int n_tiles, tiles_per_bh, n_dse_blocks;
     int B, H, N, D;
@@ -98,9 +98,10 @@ inline size_t bwd_scratch_need(int rows_per_tile, int J, int B, int H, int N, in
 // Tensor-core kernels with scale_embed: 64-row tiles, dscale_embed partials per group of
 // kSeGroup consecutive tiles of a sequence, and the per-row table qs_rows[B*H*N][Jp], Jp = J rounded up to 8.
 constexpr int kSeGroup = 8;
-inline size_t se_pre_bytes(int J, int D) {
+// split scale_embed | dS.SE fragments | pos_bias/scale per head [H][Jp] | dense-window offset table (<= 10 n-tiles)
+inline size_t se_pre_bytes(int J, int D, int H) {
     const size_t Jp = (J + 7) / 8 * 8, JS = (J + 15) / 16 * 16;
-    return 2 * Jp * D * 2 + (JS / 16) * (D / 8) * 32 * 8;
+    return 2 * Jp * D * 2 + (JS / 16) * (D / 8) * 32 * 8 + (size_t)H * Jp * 4 + 10 * 32 * 16;
 }
 inline size_t bwd_scratch_need_mma_se(int J, int B, int H, int N, int D) {
     const size_t tiles_bh = (N + kMinRowsPerBwdTile - 1) / kMinRowsPerBwdTile;
@@ -108,7 +109,7 @@ inline size_t bwd_scratch_need_mma_se(int J, int B, int H, int N, int D) {
     const size_t clusters = (size_t)B * H * ((tiles_bh + kSeGroup - 1) / kSeGroup);
     const size_t Jp = (J + 7) / 8 * 8;
     return round256((size_t)B * H * N * 8) + round256(tiles * J * 4) + round256(tiles * 4) +
-           round256(clusters * J * D * 4) + round256((size_t)B * H * N * Jp * 4) + round256(se_pre_bytes(J, D)) +
+           round256(clusters * J * D * 4) + round256((size_t)B * H * N * Jp * 4) + round256(se_pre_bytes(J, D, H)) +
            round256(tiles * J * D * 4);
 }
 inline void carve_bwd_scratch_mma_se(BwdArgs& a, int J) {
@@ -122,7 +123,7 @@ inline void carve_bwd_scratch_mma_se(BwdArgs& a, int J) {
     a.dg_part = reinterpret_cast<float*>(p);  p += round256((size_t)a.n_tiles * 4);
     a.dse_part = reinterpret_cast<float*>(p); p += round256((size_t)a.n_dse_blocks * J * a.D * 4);
     a.qs_rows = reinterpret_cast<float*>(p);  p += round256((size_t)a.B * a.H * a.N * Jp * 4);
-    a.se_pre = p;                             p += round256(se_pre_bytes(J, a.D));
+    a.se_pre = p;                             p += round256(se_pre_bytes(J, a.D, a.H));
     a.dse_tmp = reinterpret_cast<float*>(p);
 }
 inline void carve_bwd_scratch(BwdArgs& a, int rows_per_tile, int J, bool has_se) {

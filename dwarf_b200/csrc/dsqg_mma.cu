@@ -88,11 +88,13 @@ struct SeTables {
 };
 
 // qs[row][j] = q[row].scale_embed[j] + pbs[j] for the 16 rows held as A fragments qa (rows g) / qb (rows g+8)
-template <int D>
+// GL: the tables (se_hi, se_lo, pbs) are in global memory (read-only path) instead of shared memory
+template <int D, bool GL>
 __device__ __forceinline__ void build_qs_tile(const SeTables& se, const RowFrag<D>& qa, const RowFrag<D>& qb, int g, int tig) {
 #pragma unroll 2
     for (int m = 0; m < se.Jp / 8; ++m) {
-        const float2 pb2 = *reinterpret_cast<const float2*>(se.pbs + 8 * m + 2 * tig);
+        const float2* pbp = reinterpret_cast<const float2*>(se.pbs + 8 * m + 2 * tig);
+        const float2 pb2 = GL ? __ldg(pbp) : *pbp;
         float c[4] = {pb2.x, pb2.y, pb2.x, pb2.y};
         RowFrag<D> sf;
 #pragma unroll
@@ -100,7 +102,7 @@ __device__ __forceinline__ void build_qs_tile(const SeTables& se, const RowFrag<
             const uint4* src = reinterpret_cast<const uint4*>((half ? se.se_lo : se.se_hi) + (8 * m + g) * D + 8 * tig);
 #pragma unroll
             for (int cc = 0; cc < D / 32; ++cc) {
-                const uint4 u = src[4 * cc];
+                const uint4 u = GL ? __ldg(src + 4 * cc) : src[4 * cc];
                 sf.r[4 * cc + 0] = u.x; sf.r[4 * cc + 1] = u.y; sf.r[4 * cc + 2] = u.z; sf.r[4 * cc + 3] = u.w;
             }
             mma_rows(c, qa, qb, sf);
@@ -129,7 +131,7 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
     RowFrag<D> qa, qb;
     load_row(qa, qp + (size_t)row_lo * D, tig, ok_lo);
     load_row(qb, qp + (size_t)row_hi * D, tig, ok_hi);
-    if (SE) build_qs_tile<D>(se, qa, qb, g, tig);
+    if (SE) build_qs_tile<D, false>(se, qa, qb, g, tig);
 
     // ---- dense window: key row of n-tile nt for this thread is kb0 + 8 nt + g = row_lo - WB + 8 nt
     float S[NT][4];
@@ -304,8 +306,7 @@ template <int D> struct FwdTune { static constexpr int warps = 4, group = D == 3
 // smem layout: se_hi [Jp][D] bf16 | se_lo [Jp][D] bf16 | pbs [Jp] f32 | off [NT*32] int4 | qs [warps][16*pitch+4] f32
 template <int D, int WB, int W>
 __device__ __forceinline__ SeTables fill_se_tables(unsigned char* smem, const float* scale_embed, const float* pos_bias,
-                                                   const Taps& t, int H, int h, float scale, int warp, bool transposed,
-                                                   const void* se_pre = nullptr) {
+                                                   const Taps& t, int H, int h, float scale, int warp, bool transposed) {
     constexpr int NT = (WB + 16) / 8;
     const int J = t.J, Jp = (J + 7) / 8 * 8, pitch = Jp + 2;
     __nv_bfloat16* se_hi = reinterpret_cast<__nv_bfloat16*>(smem);
@@ -313,17 +314,6 @@ __device__ __forceinline__ SeTables fill_se_tables(unsigned char* smem, const fl
     float* pbs = reinterpret_cast<float*>(se_lo + Jp * D);
     int4* off = reinterpret_cast<int4*>(pbs + Jp);
     float* qs = reinterpret_cast<float*>(off + NT * 32);
-    if (se_pre) {                                        // already split by se_prep_kernel: copy
-        const uint4* src = static_cast<const uint4*>(se_pre);
-        const int n16 = 2 * Jp * D * 2 / 16;
-        for (int e0 = threadIdx.x; e0 < n16; e0 += 4 * W * 32) {          // four loads in flight per thread
-            uint4 x[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) { const int e = e0 + u * W * 32; x[u] = e < n16 ? __ldg(src + e) : make_uint4(0u, 0u, 0u, 0u); }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) { const int e = e0 + u * W * 32; if (e < n16) reinterpret_cast<uint4*>(se_hi)[e] = x[u]; }
-        }
-    } else
     for (int e = threadIdx.x; e < Jp * D / 2; e += W * 32) {
         const int j = (2 * e) / D;
         float2 x = make_float2(0.f, 0.f);
@@ -442,7 +432,7 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
     load_row(da, dop + (size_t)row_lo * D, tig, ok_lo);
     load_row(db, dop + (size_t)row_hi * D, tig, ok_hi);
     if (SE) {
-        build_qs_tile<D>(se, qa, qb, g, tig);
+        build_qs_tile<D, true>(se, qa, qb, g, tig);
         // the tile goes to global memory for the dK/dV kernel (rows of this warp, Jp floats each)
         float2* dst = reinterpret_cast<float2*>(a.qs_rows + ((size_t)bh * N + g0) * se.Jp);
         const int half = se.Jp / 2;
@@ -489,7 +479,7 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
             const int4 so = soff_s[nt * 32 + L.lane];
             float s[4], dp[4];
             if (SE) {
-                const int4 qo = se.off[nt * 32 + L.lane];
+                const int4 qo = __ldg(se.off + nt * 32 + L.lane);      // table in global memory (se_prep_kernel)
                 s[0] = se.qs[qo.x]; s[1] = se.qs[qo.y]; s[2] = se.qs[qo.z]; s[3] = se.qs[qo.w];
             } else {
                 const float4 ini = init_s[nt * 32 + L.lane];
@@ -621,14 +611,33 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
     return dgrow;
 }
 
-// One block: scale_embed split into bf16 halves [2][Jp][D] and, behind them, its B fragments for
-// dQ += dS.scale_embed, [JS/16][D/8][32] x uint2 in the element order of the dQ accumulators
-// (n-tile jn, column g  <->  d = 32 (jn/4) + 8 (g>>1) + 2 (jn%4) + (g&1)); rows j >= J are zero.
-template <int D>
-__global__ void se_prep_kernel(const float* __restrict__ scale_embed, int J, void* out) {
+// One block, before the dQ kernel with scale_embed.  Writes, back to back:
+//   scale_embed split into bf16 halves [2][Jp][D];
+//   its B fragments for dQ += dS.scale_embed, [JS/16][D/8][32] x uint2, in the element order of the
+//     dQ accumulators (n-tile jn, column g <-> d = 32 (jn/4) + 8 (g>>1) + 2 (jn%4) + (g&1)), rows j >= J zero;
+//   pos_bias[j,h] / scale for every head, [H][Jp];
+//   the offset table of the dense window into a per-warp tile of the given pitch, [NT*32] x int4
+//     (16 * pitch = the dump entry that holds the mask value).
+struct SePre {
+    const __nv_bfloat16* se_hi; const __nv_bfloat16* se_lo; const uint2* seb; const float* pbs; const int4* off;
+};
+__host__ __device__ inline SePre se_pre_layout(const void* base, int J, int D, int H) {
     const int Jp = (J + 7) / 8 * 8, JS = (J + 15) / 16 * 16;
-    __nv_bfloat162* hi = static_cast<__nv_bfloat162*>(out);
-    __nv_bfloat162* lo = hi + Jp * D / 2;
+    SePre p;
+    p.se_hi = static_cast<const __nv_bfloat16*>(base);
+    p.se_lo = p.se_hi + Jp * D;
+    p.seb = reinterpret_cast<const uint2*>(p.se_lo + Jp * D);
+    p.pbs = reinterpret_cast<const float*>(p.seb + (JS / 16) * (D / 8) * 32);
+    p.off = reinterpret_cast<const int4*>(p.pbs + H * Jp);
+    return p;
+}
+template <int D>
+__global__ void se_prep_kernel(const float* __restrict__ scale_embed, const float* __restrict__ pos_bias, float scale,
+                               int J, int H, int d_lo, int n_dense, int WB, void* out) {
+    const int Jp = (J + 7) / 8 * 8, JS = (J + 15) / 16 * 16;
+    const SePre P = se_pre_layout(out, J, D, H);
+    __nv_bfloat162* hi = reinterpret_cast<__nv_bfloat162*>(const_cast<__nv_bfloat16*>(P.se_hi));
+    __nv_bfloat162* lo = reinterpret_cast<__nv_bfloat162*>(const_cast<__nv_bfloat16*>(P.se_lo));
     for (int e = threadIdx.x; e < Jp * D / 2; e += blockDim.x) {
         const int j = (2 * e) / D;
         float2 x = make_float2(0.f, 0.f);
@@ -637,7 +646,7 @@ __global__ void se_prep_kernel(const float* __restrict__ scale_embed, int J, voi
         hi[e] = h2;
         lo[e] = __floats2bfloat162_rn(x.x - __low2float(h2), x.y - __high2float(h2));
     }
-    uint2* seb = reinterpret_cast<uint2*>(lo + Jp * D / 2);
+    uint2* seb = const_cast<uint2*>(P.seb);
     for (int e = threadIdx.x; e < (JS / 16) * (D / 8) * 32; e += blockDim.x) {
         const int ln = e & 31, jn = (e >> 5) % (D / 8), kk = (e >> 5) / (D / 8);
         const int gg = ln >> 2, tt = ln & 3;
@@ -646,6 +655,23 @@ __global__ void se_prep_kernel(const float* __restrict__ scale_embed, int J, voi
         auto sev = [&](int j) { return j < J ? scale_embed[j * D + d] : 0.f; };
         seb[e] = make_uint2(pack_bf16x2(sev(j0), sev(j0 + 1)), pack_bf16x2(sev(j0 + 8), sev(j0 + 9)));
     }
+    float* pbs = const_cast<float*>(P.pbs);
+    const float inv_scale = 1.f / scale;
+    for (int e = threadIdx.x; e < H * Jp; e += blockDim.x) {
+        const int h = e / Jp, j = e - h * Jp;
+        pbs[e] = j < J ? pos_bias[j * H + h] * inv_scale : 0.f;
+    }
+    int4* off = const_cast<int4*>(P.off);
+    const int NT = (WB + 16) / 8, pitch = Jp + 2, d_hi = d_lo + n_dense - 1;
+    for (int e = threadIdx.x; e < NT * 32; e += blockDim.x) {
+        const int nt = e >> 5, gg = (e & 31) >> 2, tt = e & 3;
+        int o[4];
+        for (int r = 0; r < 4; ++r) {
+            const int i = gg + 8 * (r >> 1), delta = WB + i - (8 * nt + 2 * tt + (r & 1));
+            o[r] = (delta >= d_lo && delta <= d_hi) ? i * pitch + (delta - d_lo) : 16 * pitch;
+        }
+        off[e] = make_int4(o[0], o[1], o[2], o[3]);
+    }
 }
 
 inline size_t dq_smem_bytes(int J, int D, int NT, bool se) {
@@ -653,7 +679,7 @@ inline size_t dq_smem_bytes(int J, int D, int NT, bool se) {
     size_t n = sizeof(float) * ((size_t)(JS + 1) * (se ? kStagePitchSe : kStagePitch) + kWarps * 32);
     if (se) {
         n = (n + 15) / 16 * 16;
-        n += se_tables_bytes(J, D, NT, kWarps, 16);
+        n += (size_t)kWarps * (16 * ((J + 7) / 8 * 8 + 2) + 4) * 4;      // one q.scale_embed tile per warp
         n = (n + 15) / 16 * 16;
         n += (size_t)kRows * (2 * D + 16);
     }
@@ -696,13 +722,20 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
         for (int si = threadIdx.x; si < t.n_sparse; si += kWarps * 32)
             tap_s[si] = make_int2(t.sparse[si], __float_as_int(a.pos_bias[(t.n_dense + si) * a.H + h] * kLog2e));
         if (SE) {
+            // tables come from global memory (se_prep_kernel); shared memory only holds the per-warp
+            // q.scale_embed tiles and the CTA's query rows
+            const SePre P = se_pre_layout(a.se_pre, J, D, a.H);
+            const int Jp = (J + 7) / 8 * 8, pitch = Jp + 2;
             unsigned char* p = reinterpret_cast<unsigned char*>(dg_s + kWarps * 32);
             p = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(p) + 15) & ~uintptr_t(15));
-            se = fill_se_tables<D, WB, kWarps>(p, a.scale_embed, a.pos_bias, t, a.H, h, a.scale, L.warp, false, a.se_pre);
-            p += se_tables_bytes(J, D, NT, kWarps, 16);
+            float* qs_w = reinterpret_cast<float*>(p) + L.warp * (16 * pitch + 4);
+            if (L.lane == 0) qs_w[16 * pitch] = kNeg;          // the dump entry: masked
+            se.se_hi = P.se_hi; se.se_lo = P.se_lo; se.pbs = P.pbs + h * Jp; se.off = P.off; se.qs = qs_w;
+            se.Jp = Jp; se.pitch = pitch; se.nd = t.n_dense;
+            p += (size_t)kWarps * (16 * pitch + 4) * 4;
             p = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(p) + 15) & ~uintptr_t(15));
             sb.JS = JS;
-            sb.seb = reinterpret_cast<const uint2*>(static_cast<const unsigned char*>(a.se_pre) + (size_t)2 * ((J + 7) / 8 * 8) * D * 2);
+            sb.seb = P.seb;
             sb.q_s = p;
             // staging rows J .. JS-1 take part in the dS MMAs: zero
             for (int e = threadIdx.x; e < (JS - J) * kRows; e += kWarps * 32)
@@ -1064,7 +1097,7 @@ cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stag
     cudaError_t e = cudaSuccess;
     if (stages & DSQG_BWD_STAGE_DQ) {
         if (SE) {
-            se_prep_kernel<D><<<1, 1024, 0, s>>>(a.scale_embed, t.J, a.se_pre);
+            se_prep_kernel<D><<<1, 1024, 0, s>>>(a.scale_embed, a.pos_bias, a.scale, t.J, a.H, t.d_lo, t.n_dense, WB, a.se_pre);
             if ((e = cudaGetLastError()) != cudaSuccess) return e;
         }
         auto kern = bwd_dq_mma_kernel<D, WB, T::dq_group, SE ? T::dq_ctas_se : T::dq_ctas, SE>;

@@ -27,7 +27,8 @@ class DSQGHostPipeline:
     downloaded into the host tensors given to `submit` when those are not None.
     """
 
-    def __init__(self, shape: Sequence[int], dtype: torch.dtype, offsets: Sequence[int], device, depth: int = 2):
+    def __init__(self, shape: Sequence[int], dtype: torch.dtype, offsets: Sequence[int], device, depth: int = 2,
+                 scale_embed: bool = False):
         if depth < 1:
             raise ValueError("dsqg host pipeline: depth must be >= 1")
         self.lib = _lib.load()
@@ -38,10 +39,11 @@ class DSQGHostPipeline:
         self.dtype = dtype
         self.off, self.J = _lib.offsets_array(offsets)
         self.depth = depth
+        self.with_se = bool(scale_embed)
         B, H, N, D, J = self.B, self.H, self.N, self.D, self.J
         with torch.cuda.device(self.device):
             self.up, self.run, self.down = (torch.cuda.Stream(self.device) for _ in range(3))
-            nbytes = self.lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, 0)
+            nbytes = self.lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, int(self.with_se))
             self.slots = []
             for _ in range(depth):
                 t = lambda: torch.empty(B, H, N, D, dtype=dtype, device=self.device)
@@ -49,6 +51,7 @@ class DSQGHostPipeline:
                     "q": t(), "k": t(), "v": t(), "dout": t(), "out": t(), "dq": t(), "dk": t(), "dv": t(),
                     "lse": torch.empty(B, H, N, device=self.device),
                     "dpb": torch.empty(J, H, device=self.device), "dg": torch.empty(H, device=self.device),
+                    "dse": torch.empty(J, D, device=self.device) if self.with_se else None,
                     "scratch": torch.empty(nbytes, dtype=torch.uint8, device=self.device), "nbytes": nbytes,
                     "uploaded": torch.cuda.Event(), "computed": torch.cuda.Event(), "free": torch.cuda.Event(),
                 })
@@ -62,9 +65,16 @@ class DSQGHostPipeline:
             raise ValueError(f"dsqg host pipeline: {name} must be {(self.B, self.H, self.N, self.D)} {self.dtype}")
 
     def submit(self, q, k, v, dout, pos_bias, head_gain, out, dq, dk, dv,
-               dpos_bias: Optional[torch.Tensor] = None, dhead_gain: Optional[torch.Tensor] = None):
+               dpos_bias: Optional[torch.Tensor] = None, dhead_gain: Optional[torch.Tensor] = None,
+               scale_embed: Optional[torch.Tensor] = None, dscale_embed: Optional[torch.Tensor] = None):
         """q, k, v, dout (inputs) and out, dq, dk, dv (results): pinned host [B,H,N,D];
-        pos_bias [J,H] and head_gain [H] (or None): fp32 DEVICE tensors, read when the step runs."""
+        pos_bias [J,H], head_gain [H] (or None) and scale_embed [J,D] (only for a pipeline built with
+        scale_embed=True): fp32 DEVICE tensors, read when the step runs."""
+        if (scale_embed is not None) != self.with_se:
+            raise ValueError("dsqg host pipeline: scale_embed must be given exactly when the pipeline was built with scale_embed=True")
+        if scale_embed is not None and (tuple(scale_embed.shape) != (self.J, self.D) or scale_embed.dtype != torch.float32
+                                        or not scale_embed.is_cuda):
+            raise ValueError(f"dsqg host pipeline: scale_embed must be a float32 device tensor [{self.J},{self.D}]")
         for name, t in (("q", q), ("k", k), ("v", v), ("dout", dout), ("out", out), ("dq", dq), ("dk", dk), ("dv", dv)):
             self._check_host(name, t)
         if tuple(pos_bias.shape) != (self.J, self.H) or pos_bias.dtype != torch.float32 or not pos_bias.is_cuda:
@@ -84,13 +94,15 @@ class DSQGHostPipeline:
                 self.run.wait_event(s["uploaded"])
                 sp = self.run.cuda_stream
                 hg = None if head_gain is None else head_gain.data_ptr()
+                sep = None if scale_embed is None else scale_embed.data_ptr()
                 _lib.check(lib.dsqg_fwd(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), pos_bias.data_ptr(),
-                                        None, hg, self.off, J, s["out"].data_ptr(), s["lse"].data_ptr(),
+                                        sep, hg, self.off, J, s["out"].data_ptr(), s["lse"].data_ptr(),
                                         B, H, N, D, self._dt, sp), "dsqg_fwd")
                 _lib.check(lib.dsqg_bwd(s["q"].data_ptr(), s["k"].data_ptr(), s["v"].data_ptr(), pos_bias.data_ptr(),
-                                        None, hg, self.off, J, s["out"].data_ptr(), s["lse"].data_ptr(),
+                                        sep, hg, self.off, J, s["out"].data_ptr(), s["lse"].data_ptr(),
                                         s["dout"].data_ptr(), s["dq"].data_ptr(), s["dk"].data_ptr(), s["dv"].data_ptr(),
-                                        s["dpb"].data_ptr(), None, None if head_gain is None else s["dg"].data_ptr(),
+                                        s["dpb"].data_ptr(), None if scale_embed is None else s["dse"].data_ptr(),
+                                        None if head_gain is None else s["dg"].data_ptr(),
                                         s["scratch"].data_ptr(), s["nbytes"], B, H, N, D, self._dt, sp), "dsqg_bwd")
                 s["computed"].record(self.run)
             with torch.cuda.stream(self.down):
@@ -101,6 +113,8 @@ class DSQGHostPipeline:
                     dpos_bias.copy_(s["dpb"], non_blocking=True)
                 if dhead_gain is not None and head_gain is not None:
                     dhead_gain.copy_(s["dg"], non_blocking=True)
+                if dscale_embed is not None and scale_embed is not None:
+                    dscale_embed.copy_(s["dse"], non_blocking=True)
                 s["free"].record(self.down)
 
     def join(self, stream: Optional[torch.cuda.Stream] = None):

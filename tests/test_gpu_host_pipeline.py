@@ -10,31 +10,38 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
+@pytest.mark.parametrize("with_se", [False, True])
 @pytest.mark.parametrize("depth", [1, 2, 3])
-def test_pipeline_steps_equal_the_autograd_operator(depth):
+def test_pipeline_steps_equal_the_autograd_operator(depth, with_se):
     g = torch.Generator().manual_seed(depth)
     B, H, N, D = 2, 4, 300, 32
     offsets = tuple(range(9)) + (16, 48, 128)
     pb = torch.randn(len(offsets), H, generator=g).to(DEV)
     gain = (torch.rand(H, generator=g) + 0.5).to(DEV)
-    pipe = dwarf_b200.DSQGHostPipeline((B, H, N, D), torch.bfloat16, offsets, DEV, depth=depth)
+    se = (torch.randn(len(offsets), D, generator=g) * 0.05).to(DEV) if with_se else None
+    pipe = dwarf_b200.DSQGHostPipeline((B, H, N, D), torch.bfloat16, offsets, DEV, depth=depth, scale_embed=with_se)
     steps = 5
     pin = lambda: torch.empty(B, H, N, D, dtype=torch.bfloat16).pin_memory()
     ins = [[(torch.randn(B, H, N, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory() for _ in range(4)] for _ in range(steps)]
     outs = [[pin() for _ in range(4)] for _ in range(steps)]
     dpb = [torch.empty(len(offsets), H).pin_memory() for _ in range(steps)]
     dg = [torch.empty(H).pin_memory() for _ in range(steps)]
+    dse = [torch.empty(len(offsets), D).pin_memory() for _ in range(steps)]
     for i in range(steps):
-        pipe.submit(*ins[i], pb, gain, *outs[i], dpos_bias=dpb[i], dhead_gain=dg[i])
+        pipe.submit(*ins[i], pb, gain, *outs[i], dpos_bias=dpb[i], dhead_gain=dg[i], scale_embed=se,
+                    dscale_embed=dse[i] if with_se else None)
     pipe.synchronize()
     for i in range(steps):
         q, k, v = (t.to(DEV).requires_grad_(True) for t in ins[i][:3])
         pbp, gp = pb.clone().requires_grad_(True), gain.clone().requires_grad_(True)
-        o = dwarf_b200.dsqg_attention(q, k, v, pbp, gp, None, offsets)
+        sep = se.clone().requires_grad_(True) if with_se else None
+        o = dwarf_b200.dsqg_attention(q, k, v, pbp, gp, sep, offsets)
         o.backward(ins[i][3].to(DEV))
         for got, ref in zip(outs[i], (o.detach(), q.grad, k.grad, v.grad)):
             assert torch.equal(got, ref.cpu())
         assert torch.equal(dpb[i], pbp.grad.cpu()) and torch.equal(dg[i], gp.grad.cpu())
+        if with_se:
+            assert torch.equal(dse[i], sep.grad.cpu())
 
 
 def test_pipeline_rejects_pageable_host_tensors():
