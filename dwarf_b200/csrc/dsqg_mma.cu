@@ -89,8 +89,10 @@ struct SeTables {
 
 // qs[row][j] = q[row].scale_embed[j] + pbs[j] for the 16 rows held as A fragments qa (rows g) / qb (rows g+8)
 // GL: the tables (se_hi, se_lo, pbs) are in global memory (read-only path) instead of shared memory
+// rows_lo / rows_hi (optional): global-memory rows (Jp floats each) that receive a copy of rows g / g+8
 template <int D, bool GL>
-__device__ __forceinline__ void build_qs_tile(const SeTables& se, const RowFrag<D>& qa, const RowFrag<D>& qb, int g, int tig) {
+__device__ __forceinline__ void build_qs_tile(const SeTables& se, const RowFrag<D>& qa, const RowFrag<D>& qb, int g, int tig,
+                                              float* rows_lo = nullptr, float* rows_hi = nullptr) {
 #pragma unroll 2
     for (int m = 0; m < se.Jp / 8; ++m) {
         const float2* pbp = reinterpret_cast<const float2*>(se.pbs + 8 * m + 2 * tig);
@@ -109,6 +111,8 @@ __device__ __forceinline__ void build_qs_tile(const SeTables& se, const RowFrag<
         }
         *reinterpret_cast<float2*>(se.qs + g * se.pitch + 8 * m + 2 * tig) = make_float2(c[0], c[1]);
         *reinterpret_cast<float2*>(se.qs + (g + 8) * se.pitch + 8 * m + 2 * tig) = make_float2(c[2], c[3]);
+        if (rows_lo) *reinterpret_cast<float2*>(rows_lo + 8 * m + 2 * tig) = make_float2(c[0], c[1]);
+        if (rows_hi) *reinterpret_cast<float2*>(rows_hi + 8 * m + 2 * tig) = make_float2(c[2], c[3]);
     }
     __syncwarp();
 }
@@ -432,16 +436,9 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
     load_row(da, dop + (size_t)row_lo * D, tig, ok_lo);
     load_row(db, dop + (size_t)row_hi * D, tig, ok_hi);
     if (SE) {
-        build_qs_tile<D, true>(se, qa, qb, g, tig);
-        // the tile goes to global memory for the dK/dV kernel (rows of this warp, Jp floats each)
-        float2* dst = reinterpret_cast<float2*>(a.qs_rows + ((size_t)bh * N + g0) * se.Jp);
-        const int half = se.Jp / 2;
-#pragma unroll 1
-        for (int r = 0; r < 16; ++r) {
-            if (!INTERIOR && g0 + r >= N) break;
-            for (int c = L.lane; c < half; c += 32)
-                dst[r * half + c] = *reinterpret_cast<const float2*>(se.qs + r * se.pitch + 2 * c);
-        }
+        // the tile also goes to global memory for the dK/dV kernel (rows of this warp, Jp floats each)
+        float* rows = a.qs_rows + ((size_t)bh * N + row_lo) * se.Jp;
+        build_qs_tile<D, true>(se, qa, qb, g, tig, ok_lo ? rows : nullptr, ok_hi ? rows + 8 * se.Jp : nullptr);
         // and the query rows to shared memory for the CTA's dscale_embed partial
         unsigned char* qrow = sb.q_s + (size_t)(L.warp * 16 + g) * (2 * D + 16) + 16 * tig;
 #pragma unroll
@@ -1036,22 +1033,35 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t, const int n_reduce, const int
             stat_s[i] = m_cta + i < N ? rs[m_cta + i] : make_float2(0.f, 0.f);
         if (SE) {
             const float* src = a.qs_rows + ((size_t)bh * N + m_cta) * Jp;
-            // warp w copies rows w, w+4, ...; eight rows per batch so that their loads overlap
-            constexpr int kBatch = 8;
-            for (int c = L.lane; c < ndp; c += 32) {
+            for (int r = threadIdx.x; r < kStat; r += kWarps * 32) qsd[r * ndp + nd] = kNeg;      // the mask column
+            if (nd % 4 == 0) {
+                // 16-byte loads: lane c4 < nd/4 of warp w takes rows w, w+4, ...; eight rows per batch in flight
+                const int per_row = nd / 4;
+                constexpr int kBatch = 8;
+                for (int c4 = L.lane; c4 < per_row; c4 += 32) {
 #pragma unroll 1
-                for (int r0 = L.warp; r0 < kStat; r0 += kWarps * kBatch) {
-                    float x[kBatch];
+                    for (int r0 = L.warp; r0 < kStat; r0 += kWarps * kBatch) {
+                        float4 x[kBatch];
 #pragma unroll
-                    for (int u = 0; u < kBatch; ++u) {
-                        const int r = r0 + kWarps * u;
-                        x[u] = (c < nd && r < kStat && m_cta + r < N) ? __ldg(src + (size_t)r * Jp + c) : (c == nd ? kNeg : 0.f);
-                    }
+                        for (int u = 0; u < kBatch; ++u) {
+                            const int r = r0 + kWarps * u;
+                            x[u] = (r < kStat && m_cta + r < N) ? __ldg(reinterpret_cast<const float4*>(src + (size_t)r * Jp) + c4)
+                                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
 #pragma unroll
-                    for (int u = 0; u < kBatch; ++u) {
-                        const int r = r0 + kWarps * u;
-                        if (r < kStat) qsd[r * ndp + c] = x[u];
+                        for (int u = 0; u < kBatch; ++u) {
+                            const int r = r0 + kWarps * u;
+                            if (r < kStat) {
+                                float* dst = qsd + r * ndp + 4 * c4;
+                                dst[0] = x[u].x; dst[1] = x[u].y; dst[2] = x[u].z; dst[3] = x[u].w;
+                            }
+                        }
                     }
+                }
+            } else {
+                for (int r = L.warp; r < kStat; r += kWarps) {
+                    const bool ok = m_cta + r < N;
+                    for (int c = L.lane; c < nd; c += 32) qsd[r * ndp + c] = ok ? __ldg(src + (size_t)r * Jp + c) : 0.f;
                 }
             }
         }
