@@ -135,13 +135,13 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
     RowFrag<D> qa, qb;
     load_row(qa, qp + (size_t)row_lo * D, tig, ok_lo);
     load_row(qb, qp + (size_t)row_hi * D, tig, ok_hi);
-    if (SE) build_qs_tile<D, false>(se, qa, qb, g, tig);
+    if constexpr (SE) build_qs_tile<D, false>(se, qa, qb, g, tig);
 
     // ---- dense window: key row of n-tile nt for this thread is kb0 + 8 nt + g = row_lo - WB + 8 nt
     float S[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        if (SE) {
+        if constexpr (SE) {
             const int4 qo = se.off[nt * 32 + L.lane];
             S[nt][0] = se.qs[qo.x]; S[nt][1] = se.qs[qo.y]; S[nt][2] = se.qs[qo.z]; S[nt][3] = se.qs[qo.w];
         } else {
@@ -251,7 +251,7 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
             mma_rows_z(s0, qa, qb, kf0[i]);
             mma_rows_z(s1, qa, qb, kf1[i]);
             const float d0 = (g & 1) ? s0[1] : s0[0], d1 = (g & 1) ? s1[3] : s1[2];
-            if (SE) {
+            if constexpr (SE) {
                 x0[i] = (d0 + se.qs[g * se.pitch + se.nd + si + i]) * c2;
                 x1[i] = (d1 + se.qs[(g + 8) * se.pitch + se.nd + si + i]) * c2;
             } else {
@@ -366,7 +366,7 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
     const Lane L;
     const int bh = blockIdx.y, h = bh % a.H, N = a.N;
     SeTables se = {};
-    if (SE) {
+    if constexpr (SE) {
         se = fill_se_tables<D, WB, W>(se_smem, a.scale_embed, a.pos_bias, t, a.H, h, a.scale, L.warp, false);
     } else {
         const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1;
@@ -435,7 +435,7 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
     load_row(qb, qp + (size_t)row_hi * D, tig, ok_hi);
     load_row(da, dop + (size_t)row_lo * D, tig, ok_lo);
     load_row(db, dop + (size_t)row_hi * D, tig, ok_hi);
-    if (SE) {
+    if constexpr (SE) {
         // the tile also goes to global memory for the dK/dV kernel (rows of this warp, Jp floats each)
         float* rows = a.qs_rows + ((size_t)bh * N + row_lo) * se.Jp;
         build_qs_tile<D, true>(se, qa, qb, g, tig, ok_lo ? rows : nullptr, ok_hi ? rows + 8 * se.Jp : nullptr);
@@ -473,15 +473,15 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
             const int nt = 2 * c + hf;
-            const int4 so = soff_s[nt * 32 + L.lane];
-            float s[4], dp[4];
-            if (SE) {
+            float4 ini;
+            if constexpr (SE) {
                 const int4 qo = __ldg(se.off + nt * 32 + L.lane);      // table in global memory (se_prep_kernel)
-                s[0] = se.qs[qo.x]; s[1] = se.qs[qo.y]; s[2] = se.qs[qo.z]; s[3] = se.qs[qo.w];
+                ini = make_float4(se.qs[qo.x], se.qs[qo.y], se.qs[qo.z], se.qs[qo.w]);
             } else {
-                const float4 ini = init_s[nt * 32 + L.lane];
-                s[0] = ini.x; s[1] = ini.y; s[2] = ini.z; s[3] = ini.w;
+                ini = init_s[nt * 32 + L.lane];
             }
+            const int4 so = soff_s[nt * 32 + L.lane];
+            float s[4] = {ini.x, ini.y, ini.z, ini.w}, dp[4];
             RowFrag<D> vf;
             if (INTERIOR) {
                 load_row_at(kf[hf], kl + (8 * nt - WB) * D);
@@ -525,15 +525,14 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
     float* stage_sp = stage_w + nd * SP + g;
     auto finish = [&](int si, float sd0, float sd1, float dp0, float dp1, float pbv, bool v0, bool v1,
                       const RowFrag<D>& kf0, const RowFrag<D>& kf1) {
-        float y0, y1;
-        if (SE) {
-            y0 = (sd0 + se.qs[g * se.pitch + nd + si]) * c2;
-            y1 = (sd1 + se.qs[(g + 8) * se.pitch + nd + si]) * c2;
+        float p0, p1;
+        if constexpr (SE) {
+            p0 = v0 ? ex2((sd0 + se.qs[g * se.pitch + nd + si]) * c2 - ls_lo) : 0.f;
+            p1 = v1 ? ex2((sd1 + se.qs[(g + 8) * se.pitch + nd + si]) * c2 - ls_hi) : 0.f;
         } else {
-            y0 = fmaf(sd0, c2, pbv); y1 = fmaf(sd1, c2, pbv);
+            p0 = v0 ? ex2(fmaf(sd0, c2, pbv) - ls_lo) : 0.f;
+            p1 = v1 ? ex2(fmaf(sd1, c2, pbv) - ls_hi) : 0.f;
         }
-        const float p0 = v0 ? ex2(y0 - ls_lo) : 0.f;
-        const float p1 = v1 ? ex2(y1 - ls_hi) : 0.f;
         dgrow = fmaf(p0, dp0, dgrow); dgrow = fmaf(p1, dp1, dgrow);
         const float x0 = p0 * fmaf(gain, dp0, -delta_lo), x1 = p1 * fmaf(gain, dp1, -delta_hi);
         if (L.owner) { stage_sp[si * SP] = x0; stage_sp[si * SP + 8] = x1; }
@@ -588,7 +587,7 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
     }
     if (L.owner)                                          // taps no row of the tile reaches: zero entries
         for (; si < ns; ++si) { stage_sp[si * SP] = 0.f; stage_sp[si * SP + 8] = 0.f; }
-    if (SE) {
+    if constexpr (SE) {
         // dQ += dS.scale_embed: the warp's ds values are complete in its 16 staging columns
         __syncwarp();
 #pragma unroll 1
@@ -713,12 +712,12 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
                 v[r] = (!SE && inband) ? a.pos_bias[(delta - d_lo) * a.H + h] * inv_scale : kNeg;
                 o[r] = (inband ? delta - d_lo : JS) * SP + i;
             }
-            if (!SE) init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
+            if constexpr (!SE) init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
             soff_s[e] = make_int4(o[0], o[1], o[2], o[3]);
         }
         for (int si = threadIdx.x; si < t.n_sparse; si += kWarps * 32)
             tap_s[si] = make_int2(t.sparse[si], __float_as_int(a.pos_bias[(t.n_dense + si) * a.H + h] * kLog2e));
-        if (SE) {
+        if constexpr (SE) {
             // tables come from global memory (se_prep_kernel); shared memory only holds the per-warp
             // q.scale_embed tiles and the CTA's query rows
             const SePre P = se_pre_layout(a.se_pre, J, D, a.H);
@@ -745,7 +744,7 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
     float dgrow = 0.f;
     if (g0 >= N) {                                      // no rows: this warp's staging columns (and query rows) are zero
         for (int e = L.lane; e < J * 16; e += 32) stage_w[(e >> 4) * SP + (e & 15)] = 0.f;
-        if (SE)
+        if constexpr (SE)
             for (int e = L.lane; e < 16 * (2 * D + 16) / 16; e += 32)
                 reinterpret_cast<uint4*>(sb.q_s + (size_t)L.warp * 16 * (2 * D + 16))[e] = make_uint4(0u, 0u, 0u, 0u);
     } else if (g0 >= WB && g0 + 16 <= N) {
@@ -756,7 +755,7 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
     dg_s[threadIdx.x] = dgrow;
     __syncthreads();
     const int tile = bh * a.tiles_per_bh + blockIdx.x;
-    if (SE) {
+    if constexpr (SE) {
         // CTA partial of dscale_embed = scale * dS^T[JS x 64] . Q[64 x D]; warp w takes n-tiles w, w+4, ...
         constexpr int QP = 2 * D + 16;
         const uint32_t q_base = static_cast<uint32_t>(__cvta_generic_to_shared(sb.q_s));
@@ -858,7 +857,7 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
         for (int hf = 0; hf < 2; ++hf) {
             const int nt = 2 * c + hf;
             float s[4], dp[4];
-            if (SE) {
+            if constexpr (SE) {
                 const int4 qo = qoff[nt * 32 + L.lane];
                 s[0] = qsd_w[qo.x]; s[1] = qsd_w[qo.y]; s[2] = qsd_w[qo.z]; s[3] = qsd_w[qo.w];
             } else {
@@ -926,7 +925,7 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
         for (int i = 0; i < GG; ++i) {
             const int2 tp = tap_s[si + i];
             const ptrdiff_t off = (ptrdiff_t)tp.x * D;
-            if (SE) {
+            if constexpr (SE) {
                 b0[i] = __ldg(qs_r + (size_t)tp.x * Jp + si + i);
                 b1[i] = __ldg(qs_r + (size_t)(tp.x + 8) * Jp + si + i);
             } else {
@@ -959,7 +958,7 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
         } else {
             const bool v0 = row_lo + delta < N, v1 = row_hi + delta < N;
             float b0 = __int_as_float(tap_s[si].y), b1 = b0;
-            if (SE) {
+            if constexpr (SE) {
                 b0 = v0 ? __ldg(qs_r + (size_t)delta * Jp + si) : 0.f;
                 b1 = v1 ? __ldg(qs_r + (size_t)(delta + 8) * Jp + si) : 0.f;
             }
@@ -1023,7 +1022,7 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t, const int n_reduce, const int
                 v[r] = (!SE && inband) ? a.pos_bias[(delta - d_lo) * a.H + h] * inv_scale : kNeg;
                 o[r] = cc * ndp + (inband ? delta - d_lo : nd);       // column nd of every row holds the mask value
             }
-            if (SE) reinterpret_cast<int4*>(init_s)[e] = make_int4(o[0], o[1], o[2], o[3]);
+            if constexpr (SE) reinterpret_cast<int4*>(init_s)[e] = make_int4(o[0], o[1], o[2], o[3]);
             else init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
         }
         for (int si = threadIdx.x; si < t.n_sparse; si += kWarps * 32)
@@ -1031,7 +1030,7 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t, const int n_reduce, const int
         const float2* rs = reinterpret_cast<const float2*>(a.delta) + (size_t)bh * N;
         for (int i = threadIdx.x; i < kStat; i += kWarps * 32)
             stat_s[i] = m_cta + i < N ? rs[m_cta + i] : make_float2(0.f, 0.f);
-        if (SE) {
+        if constexpr (SE) {
             const float* src = a.qs_rows + ((size_t)bh * N + m_cta) * Jp;
             for (int r = threadIdx.x; r < kStat; r += kWarps * 32) qsd[r * ndp + nd] = kNeg;      // the mask column
             if (nd % 4 == 0) {
@@ -1102,11 +1101,11 @@ template <int D, int WB, bool SE>
 cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stages) {
     using T = BwdTune<D>;
     constexpr int NT = (WB + 16) / 8;
-    if (SE) carve_bwd_scratch_mma_se(a, t.J); else carve_bwd_scratch(a, kRows, t.J, false);
+    if constexpr (SE) carve_bwd_scratch_mma_se(a, t.J); else carve_bwd_scratch(a, kRows, t.J, false);
     dim3 grid((a.N + kRows - 1) / kRows, a.B * a.H);
     cudaError_t e = cudaSuccess;
     if (stages & DSQG_BWD_STAGE_DQ) {
-        if (SE) {
+        if constexpr (SE) {
             se_prep_kernel<D><<<1, 1024, 0, s>>>(a.scale_embed, a.pos_bias, a.scale, t.J, a.H, t.d_lo, t.n_dense, WB, a.se_pre);
             if ((e = cudaGetLastError()) != cudaSuccess) return e;
         }
@@ -1118,7 +1117,7 @@ cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stag
         }
         kern<<<grid, kWarps * 32, smem, s>>>(a, t);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
-        if (SE) {
+        if constexpr (SE) {
             const int groups_bh = (a.tiles_per_bh + kSeGroup - 1) / kSeGroup;
             dse_group_kernel<<<dim3(groups_bh, a.B * a.H), 256, 0, s>>>(a.dse_tmp, a.dse_part, a.tiles_per_bh, groups_bh, t.J * a.D);
             if ((e = cudaGetLastError()) != cudaSuccess) return e;
