@@ -95,8 +95,9 @@ int dsqg_fwd(const void* q, const void* k, const void* v,
 
 size_t dsqg_bwd_scratch_bytes(int J, int B, int H, int N, int D, int has_scale_embed) {
     if (J < 1 || J > DSQG_MAX_TAPS || check_shape(B, H, N, D, DSQG_DTYPE_BF16)) return 0;
-    // every kernel family tiles at kMinRowsPerBwdTile rows or coarser; scale_embed partials are
-    // only produced by the generic kernels (512-row tiles)
+    // every kernel family tiles at kMinRowsPerBwdTile rows or coarser; with scale_embed the larger of
+    // the generic kernels' need (512-row partials) and the tensor-core kernels' need (per-row table,
+    // per-tile and per-group partials, prepared tables) is reported
     size_t need = bwd_scratch_need(kMinRowsPerBwdTile, J, B, H, N, D, false);
     const size_t tma = bwd_scratch_need_tma(J, B, H, N);      // persistent kernels: partials per (CTA, sequence, warp)
     if (tma > need) need = tma;

@@ -1,5 +1,7 @@
-// Chooses between the tensor-core kernels (bf16, D in {32,64}) and the generic CUDA-core
-// kernels.  One decision per call, made on the host from the shape alone.
+// Chooses between the tensor-core kernels (bf16; D in {32, 64} with or without scale_embed,
+// D in {96, 128} without) and the generic CUDA-core kernels (everything else: fp32 storage,
+// other head sizes, dense windows wider than the tensor-core kernels are built for).  One
+// decision per call, made on the host from the shape alone.
 #include <atomic>
 
 #include "dsqg_common.cuh"
