@@ -1033,8 +1033,9 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t, const int n_reduce, const int
         if constexpr (SE) {
             const float* src = a.qs_rows + ((size_t)bh * N + m_cta) * Jp;
             for (int r = threadIdx.x; r < kStat; r += kWarps * 32) qsd[r * ndp + nd] = kNeg;      // the mask column
-            if (nd % 4 == 0) {
-                // 16-byte loads: lane c4 < nd/4 of warp w takes rows w, w+4, ...; eight rows per batch in flight
+            {
+                // 16-byte loads for the first nd/4*4 columns: lane c4 < nd/4 of warp w takes rows w, w+4, ...;
+                // eight rows per batch in flight
                 const int per_row = nd / 4;
                 constexpr int kBatch = 8;
                 for (int c4 = L.lane; c4 < per_row; c4 += 32) {
@@ -1057,11 +1058,12 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t, const int n_reduce, const int
                         }
                     }
                 }
-            } else {
-                for (int r = L.warp; r < kStat; r += kWarps) {
-                    const bool ok = m_cta + r < N;
-                    for (int c = L.lane; c < nd; c += 32) qsd[r * ndp + c] = ok ? __ldg(src + (size_t)r * Jp + c) : 0.f;
-                }
+            }
+            // the last nd % 4 columns, one element per thread
+            const int rem = nd & 3, c_first = nd - rem;
+            for (int e = threadIdx.x; e < kStat * rem; e += kWarps * 32) {
+                const int r = e / rem, c = c_first + e - r * rem;
+                qsd[r * ndp + c] = m_cta + r < N ? __ldg(src + (size_t)r * Jp + c) : 0.f;
             }
         }
     }
