@@ -250,8 +250,10 @@ def run_decode_workload(args, rank, local_rank, world):
 
     def step():
         for l in range(L):
+            # from the second layer of a token on, the kernel ahead in the stream is another layer's
+            # step (its own rings), so the overlapped launch is allowed
             dwarf_b200.dsqg_decode_step(q[l], kn[l], vn[l], kr[l], vr[l], head, pb, gain, None, cfg.offsets,
-                                        None, out[l])
+                                        None, out[l], overlap=args.decode_overlap and l > 0)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -318,7 +320,9 @@ def run_decode_workload(args, rank, local_rank, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": cfg.name, "l2": f"ring footprint {2 * L * cfg.S * cfg.H * cfg.R * cfg.D * esz / 1e9:.1f} GB >> L2",
-                   "launch": "one CUDA graph of the 10 per-layer launches per step",
+                   "launch": "one CUDA graph of the 10 per-layer launches per step"
+                             + ("; layers after the first launched with programmatic dependent launch "
+                                "(ring gather overlaps the layer before)" if args.decode_overlap else ""),
                    "parallelism": f"sequences replicated x{world}, no collective"},
         "ms_per_step_eager": eager_ms,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": small,
@@ -465,6 +469,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale-embed", action="store_true",
                     help="op workloads: add the condU scale_embed term (seeded N(0, 0.05) [J,D]) and its gradient")
+    ap.add_argument("--no-decode-overlap", dest="decode_overlap", action="store_false",
+                    help="cfg3: launch every layer as an ordinary kernel (default: layers after the first overlap the one before)")
     ap.add_argument("--decode-layers", type=int, default=0, help="cfg3: number of layers (default: the 10 of the configuration)")
     ap.add_argument("--kernel-path", type=int, default=0,
                     help="dsqg_set_kernel_path value for A/B runs: 0 automatic (default), 1 generic, 2 tensor-core "

@@ -158,11 +158,11 @@ int dsqg_bwd_stages(const void* q, const void* k, const void* v,
     return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
 }
 
-int dsqg_decode(const void* q, const void* k_new, const void* v_new,
-                void* k_ring, void* v_ring, const int32_t* head, const int32_t* fill,
-                const float* pos_bias, const float* scale_embed, const float* head_gain,
-                const int32_t* offsets, int J, int R,
-                void* out, int S, int H, int D, int dtype, void* stream) {
+static int decode_impl(const void* q, const void* k_new, const void* v_new,
+                       void* k_ring, void* v_ring, const int32_t* head, const int32_t* fill,
+                       const float* pos_bias, const float* scale_embed, const float* head_gain,
+                       const int32_t* offsets, int J, int R,
+                       void* out, int S, int H, int D, int dtype, void* stream, bool overlap) {
     if (!q || !k_new || !v_new || !k_ring || !v_ring || !head || !pos_bias || !out) return DSQG_ERR_NULL_POINTER;
     int rc = check_shape(S, H, 1, D, dtype);
     if (rc) return rc;
@@ -179,8 +179,26 @@ int dsqg_decode(const void* q, const void* k_new, const void* v_new,
     a.head = head; a.fill = fill; a.pos_bias = pos_bias; a.scale_embed = scale_embed;
     a.head_gain = head_gain; a.out = out; a.S = S; a.H = H; a.D = D; a.R = R;
     a.scale = 1.0f / sqrtf((float)D);
-    cudaError_t e = launch_decode(a, t, dtype, static_cast<cudaStream_t>(stream));
+    cudaError_t e = launch_decode(a, t, dtype, static_cast<cudaStream_t>(stream), overlap);
     return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
+}
+
+int dsqg_decode(const void* q, const void* k_new, const void* v_new,
+                void* k_ring, void* v_ring, const int32_t* head, const int32_t* fill,
+                const float* pos_bias, const float* scale_embed, const float* head_gain,
+                const int32_t* offsets, int J, int R,
+                void* out, int S, int H, int D, int dtype, void* stream) {
+    return decode_impl(q, k_new, v_new, k_ring, v_ring, head, fill, pos_bias, scale_embed, head_gain,
+                       offsets, J, R, out, S, H, D, dtype, stream, false);
+}
+
+int dsqg_decode_overlapped(const void* q, const void* k_new, const void* v_new,
+                           void* k_ring, void* v_ring, const int32_t* head, const int32_t* fill,
+                           const float* pos_bias, const float* scale_embed, const float* head_gain,
+                           const int32_t* offsets, int J, int R,
+                           void* out, int S, int H, int D, int dtype, void* stream) {
+    return decode_impl(q, k_new, v_new, k_ring, v_ring, head, fill, pos_bias, scale_embed, head_gain,
+                       offsets, J, R, out, S, H, D, dtype, stream, true);
 }
 
 int dsqg_ring_prefill(const void* k, const void* v, void* k_ring, void* v_ring,

@@ -68,7 +68,7 @@ cudaError_t launch_bwd(const BwdArgs& a, const Taps& t, int dtype, cudaStream_t 
 cudaError_t launch_fwd_generic(const FwdArgs& a, const Taps& t, int dtype, cudaStream_t s);
 cudaError_t launch_bwd_generic(const BwdArgs& a, const Taps& t, int dtype, cudaStream_t s, int stages);
 cudaError_t launch_reduce_params(const BwdArgs& a, int J, cudaStream_t s);
-cudaError_t launch_decode(const DecodeArgs& a, const Taps& t, int dtype, cudaStream_t s);
+cudaError_t launch_decode(const DecodeArgs& a, const Taps& t, int dtype, cudaStream_t s, bool overlap);
 cudaError_t launch_ring_prefill(const void* k, const void* v, void* k_ring, void* v_ring, int32_t* head, int32_t* fill,
                                 int S, int H, int N, int D, int R, int dtype, cudaStream_t s);
 

@@ -7,6 +7,7 @@
 // an online-softmax state over the taps it saw, and the groups are merged with shuffles.
 // Pure streaming: 2*J rows of D elements are read per (sequence, head) and nothing is reused.
 #include "dsqg_common.cuh"
+#include <type_traits>
 
 namespace dsqg {
 namespace {
@@ -140,6 +141,167 @@ decode_kernel(const DecodeArgs a, const Taps t) {
     }
 }
 
+// ---- single-pass variant for bf16 rings --------------------------------------------------
+// Every K row of the step is copied asynchronously into shared memory (cp.async, 16 bytes per
+// lane, no register held while the copy is in flight), the first VSM rounds of V rows likewise,
+// and the remaining V rows are loaded into registers.  All 2*J row requests of a (sequence, head)
+// pair are therefore in flight together and the pair costs one memory round trip after head[s],
+// at a register count that keeps every warp of the benchmark shape resident.  Each lane reads
+// back only the 16 bytes it requested itself, so no barrier is needed after the wait.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
+//
+// PDL = true is the overlapped form (programmatic dependent launch): the kernel lets the next
+// kernel of the stream start at once, and itself reads only head, fill and the ring rows of taps
+// with delta > 0 before it waits for the kernels ahead of it; q, k_new, v_new are read and the
+// ring and out are written after that wait.  The ring gather of one layer then overlaps the tail
+// of whatever runs before it.
+template <int TPR, int ROUNDS, int VSM, int CTAS, bool PDL>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, CTAS)
+decode_1pass_kernel(const DecodeArgs a, const Taps t) {
+    if constexpr (PDL) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    using T = __nv_bfloat16;
+    constexpr int GROUPS = 32 / TPR;
+    constexpr int VREG = ROUNDS - VSM;
+    __shared__ uint4 k_sm[kWarpsPerBlock][ROUNDS][32];
+    __shared__ uint4 v_sm[kWarpsPerBlock][VSM > 0 ? VSM : 1][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sh = blockIdx.x * kWarpsPerBlock + warp;
+    if (sh >= a.S * a.H) return;
+    const int s = sh / a.H, h = sh - s * a.H;
+    const int g = lane / TPR, li = lane % TPR;
+    const int d0 = li * 8, D = a.D;
+    const bool active = d0 < D;
+
+    const int head = a.head[s];
+    const int fill = a.fill ? a.fill[s] : a.R;
+    const T* kn = static_cast<const T*>(a.k_new) + (size_t)sh * D;
+    const T* vn = static_cast<const T*>(a.v_new) + (size_t)sh * D;
+    T* kr = static_cast<T*>(a.k_ring) + (size_t)sh * a.R * D;
+    T* vr = static_cast<T*>(a.v_ring) + (size_t)sh * a.R * D;
+
+    // ---- request every row of the step
+    Raw8<T> vraw[VREG > 0 ? VREG : 1];
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int r = 0; r < ROUNDS; ++r) {
+        const int j = r * GROUPS + g;
+        const int delta = j < t.J ? t.delta(j) : 0;
+        int slot = head - delta;
+        if (slot < 0) slot += a.R;
+        const bool on = j < t.J && delta < fill && active;
+        if (PDL && j == 0 && delta == 0) continue;       // the new token itself: after the wait
+        // the tap with delta == 0 reads k_new / v_new, so nothing waits for the ring store below
+        const T* ksrc = delta == 0 ? kn + d0 : kr + (size_t)slot * D + d0;
+        const T* vsrc = delta == 0 ? vn + d0 : vr + (size_t)slot * D + d0;
+        if (on) cp_async16(&k_sm[warp][r][lane], ksrc); else k_sm[warp][r][lane] = zero4;
+        if (r < VSM) {
+            if (on) cp_async16(&v_sm[warp][r][lane], vsrc); else v_sm[warp][r][lane] = zero4;
+        } else {
+            vraw[r - VSM].zero();
+            if (on) vraw[r - VSM].load(vsrc);
+        }
+    }
+    if constexpr (PDL) {
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");
+        if (g == 0 && t.delta(0) == 0) {                 // offsets ascend: only tap 0 can be delta 0
+            const bool on = fill > 0 && active;
+            if (on) cp_async16(&k_sm[warp][0][lane], kn + d0); else k_sm[warp][0][lane] = zero4;
+            if (VSM > 0) {
+                if (on) cp_async16(&v_sm[warp][0][lane], vn + d0); else v_sm[warp][0][lane] = zero4;
+            } else {
+                vraw[0].zero();
+                if (on) vraw[0].load(vn + d0);
+            }
+        }
+    }
+    float qx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (active) load8(static_cast<const T*>(a.q) + (size_t)sh * D + d0, qx);
+    if (g == 0 && active) {          // store the new token in the ring
+        *reinterpret_cast<uint4*>(kr + (size_t)head * D + d0) = *reinterpret_cast<const uint4*>(kn + d0);
+        *reinterpret_cast<uint4*>(vr + (size_t)head * D + d0) = *reinterpret_cast<const uint4*>(vn + d0);
+    }
+    const bool has_se = a.scale_embed != nullptr;
+    cp_async_wait_all();
+
+    // ---- scores and online softmax over this lane group's taps
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float m = -INFINITY, l = 0.f;
+#pragma unroll
+    for (int r = 0; r < ROUNDS; ++r) {
+        const int j = r * GROUPS + g;
+        const bool valid = j < t.J && t.delta(j < t.J ? j : 0) < fill;
+        float kx[8], vx[8];
+        Raw8<T> kk; kk.u = k_sm[warp][r][lane]; kk.get(kx);
+        if (has_se && valid && active) {
+            float se[8];
+            load8(a.scale_embed + (size_t)j * D + d0, se);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) kx[i] += se[i];
+        }
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot = fmaf(qx[i], kx[i], dot);
+        dot = group_sum<TPR>(dot);
+        if (r < VSM) { Raw8<T> vv; vv.u = v_sm[warp][r][lane]; vv.get(vx); }
+        else vraw[r - VSM].get(vx);
+        if (valid) {
+            const float sc = dot * a.scale + a.pos_bias[j * a.H + h];
+            const float mn = fmaxf(m, sc);
+            const float cor = __expf(m - mn), p = __expf(sc - mn);
+            l = l * cor + p;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = acc[i] * cor + p * vx[i];
+            m = mn;
+        }
+    }
+    // ---- merge the GROUPS partial softmax states
+#pragma unroll
+    for (int o = TPR; o < 32; o <<= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+        const float l2 = __shfl_xor_sync(0xffffffffu, l, o);
+        const float mn = fmaxf(m, m2);
+        const float c1 = (m == -INFINITY) ? 0.f : __expf(m - mn);
+        const float c2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
+        l = l * c1 + l2 * c2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float a2 = __shfl_xor_sync(0xffffffffu, acc[i], o);
+            acc[i] = acc[i] * c1 + a2 * c2;
+        }
+        m = mn;
+    }
+    if (g == 0 && active) {
+        const float gain = a.head_gain ? a.head_gain[h] : 1.f;
+        const float inv = l > 0.f ? gain / l : 0.f;
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = acc[i] * inv;
+        store8(static_cast<T*>(a.out) + (size_t)sh * D + d0, o);
+    }
+}
+
+template <int TPR, int ROUNDS, int VSM, int CTAS>
+cudaError_t decode_launch_1pass(const DecodeArgs& a, const Taps& t, cudaStream_t s, bool overlap) {
+    const int pairs = a.S * a.H;
+    const unsigned blocks = (pairs + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    if (!overlap) {
+        decode_1pass_kernel<TPR, ROUNDS, VSM, CTAS, false><<<blocks, kWarpsPerBlock * 32, 0, s>>>(a, t);
+        return cudaGetLastError();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks); cfg.blockDim = dim3(kWarpsPerBlock * 32); cfg.dynamicSmemBytes = 0; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, decode_1pass_kernel<TPR, ROUNDS, VSM, CTAS, true>, a, t);
+}
+
 template <typename T, int TPR, int ROUNDS>
 cudaError_t decode_launch_r(const DecodeArgs& a, const Taps& t, cudaStream_t s) {
     const int pairs = a.S * a.H;
@@ -148,11 +310,18 @@ cudaError_t decode_launch_r(const DecodeArgs& a, const Taps& t, cudaStream_t s) 
 }
 
 template <typename T, int TPR>
-cudaError_t decode_launch(const DecodeArgs& a, const Taps& t, cudaStream_t s) {
+cudaError_t decode_launch(const DecodeArgs& a, const Taps& t, cudaStream_t s, bool overlap) {
     const int rounds = (t.J + 32 / TPR - 1) / (32 / TPR);
-    // Passes of 6 rounds keep the kernel at 96 registers (all warps of the benchmark shape resident
-    // at once); measured slightly faster on B200 than one pass of 12 rounds at 166 registers.
-    (void)rounds;
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        // bf16 rings, up to 12 rounds: single-pass kernel.  K rows plus four rounds of V rows in
+        // shared memory leave 80 registers (6 CTAs per SM); measured 9.95 us per launch on the
+        // benchmark shape against 14.4 us for two register passes, 15.1 us with all of V in
+        // registers (5 CTAs per SM) and 15.7 us with all of V in shared memory (4 CTAs per SM).
+        if (rounds <= 6) return decode_launch_1pass<TPR, 6, 0, 6>(a, t, s, overlap);
+        if (rounds <= 12) return decode_launch_1pass<TPR, 12, 4, 6>(a, t, s, overlap);
+    }
+    // Other cases (fp32 rings, more than 12 rounds): register passes of 6 rounds (96 registers),
+    // launched as an ordinary kernel (the overlapped form is a hint, not a requirement).
     return decode_launch_r<T, TPR, 6>(a, t, s);
 }
 }  // namespace
@@ -160,11 +329,11 @@ cudaError_t decode_launch(const DecodeArgs& a, const Taps& t, cudaStream_t s) {
 #define DSQG_DECODE_TPR(T)                                              \
     do {                                                                \
         const int chunks_ = a.D / 8;                                    \
-        if (chunks_ <= 1) return decode_launch<T, 1>(a, t, s);          \
-        if (chunks_ <= 2) return decode_launch<T, 2>(a, t, s);          \
-        if (chunks_ <= 4) return decode_launch<T, 4>(a, t, s);          \
-        if (chunks_ <= 8) return decode_launch<T, 8>(a, t, s);          \
-        return decode_launch<T, 16>(a, t, s);                           \
+        if (chunks_ <= 1) return decode_launch<T, 1>(a, t, s, overlap);          \
+        if (chunks_ <= 2) return decode_launch<T, 2>(a, t, s, overlap);          \
+        if (chunks_ <= 4) return decode_launch<T, 4>(a, t, s, overlap);          \
+        if (chunks_ <= 8) return decode_launch<T, 8>(a, t, s, overlap);          \
+        return decode_launch<T, 16>(a, t, s, overlap);                           \
     } while (0)
 
 // Ring prefill: copies the last min(N, R) positions of K and V from the training layout
@@ -203,7 +372,7 @@ cudaError_t launch_ring_prefill(const void* k, const void* v, void* k_ring, void
     return cudaGetLastError();
 }
 
-cudaError_t launch_decode(const DecodeArgs& a, const Taps& t, int dtype, cudaStream_t s) {
+cudaError_t launch_decode(const DecodeArgs& a, const Taps& t, int dtype, cudaStream_t s, bool overlap) {
     if (dtype == DSQG_DTYPE_BF16) DSQG_DECODE_TPR(__nv_bfloat16);
     DSQG_DECODE_TPR(float);
 }

@@ -16,12 +16,16 @@ from .ops import OFFSETS_43, _dtype_code, _f32c, _ptr
 
 
 def dsqg_decode_step(q, k_new, v_new, k_ring, v_ring, head, pos_bias, head_gain=None,
-                     scale_embed=None, offsets: Sequence[int] = OFFSETS_43, fill=None, out=None):
+                     scale_embed=None, offsets: Sequence[int] = OFFSETS_43, fill=None, out=None, overlap=False):
     """One decode step for one layer.
 
     q, k_new, v_new [S,H,D]; k_ring, v_ring [S,H,R,D] (updated in place at slot head[s]);
     head int32 [S] on the device; fill int32 [S] (valid tokens incl. the new one) or None
     for a full ring.  Returns out [S,H,D].
+
+    overlap=True launches the kernel so that its ring gather runs while the kernel ahead of it
+    in the stream is still finishing (`dsqg_decode_overlapped`): allowed only when that kernel
+    writes none of this call's head, fill, k_ring, v_ring.
     """
     lib = _lib.load()
     off, J = _lib.offsets_array(offsets)
@@ -42,10 +46,11 @@ def dsqg_decode_step(q, k_new, v_new, k_ring, v_ring, head, pos_bias, head_gain=
         out = torch.empty_like(q)
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream(q.device).cuda_stream
-        _lib.check(lib.dsqg_decode(q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
-                                   k_ring.data_ptr(), v_ring.data_ptr(), head.data_ptr(), _ptr(fill),
-                                   pb.data_ptr(), _ptr(se), _ptr(hg), off, J, R,
-                                   out.data_ptr(), S, H, D, _dtype_code(q), stream), "dsqg_decode")
+        entry = lib.dsqg_decode_overlapped if overlap else lib.dsqg_decode
+        _lib.check(entry(q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+                         k_ring.data_ptr(), v_ring.data_ptr(), head.data_ptr(), _ptr(fill),
+                         pb.data_ptr(), _ptr(se), _ptr(hg), off, J, R,
+                         out.data_ptr(), S, H, D, _dtype_code(q), stream), "dsqg_decode")
     return out
 
 
@@ -80,6 +85,8 @@ class DSQGRingCache:
         self.head = torch.remainder(self.head + 1, self.R).to(torch.int32)
         self.fill = torch.clamp(self.fill + 1, max=self.R).to(torch.int32)
 
-    def step(self, layer, q, k_new, v_new, pos_bias, head_gain=None, scale_embed=None, out=None):
+    def step(self, layer, q, k_new, v_new, pos_bias, head_gain=None, scale_embed=None, out=None, overlap=False):
+        """Decode step of `layer`.  overlap=True is safe from the second layer of a token on (the
+        kernel ahead is then another layer's step or a projection, never `advance`/`prefill`)."""
         return dsqg_decode_step(q, k_new, v_new, self.k[layer], self.v[layer], self.head, pos_bias,
-                                head_gain, scale_embed, self.offsets, self.fill, out)
+                                head_gain, scale_embed, self.offsets, self.fill, out, overlap)

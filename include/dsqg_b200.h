@@ -164,6 +164,24 @@ int dsqg_decode(const void* q, const void* k_new, const void* v_new,
                 const int32_t* offsets, int J, int R,
                 void* out, int S, int H, int D, int dtype, void* stream);
 
+/* dsqg_decode launched so that it overlaps the kernel ahead of it in the stream (programmatic
+ * dependent launch).  Same arguments and results as dsqg_decode.
+ * Replaces: nothing executable (see dsqg_decode).
+ * The kernel starts while the previous kernel of the stream may still be running and, before it
+ * waits for that kernel, reads head, fill and the ring rows of every tap with delta > 0; q, k_new,
+ * v_new are read, and the rings and out written, only after the wait.  The caller therefore
+ * promises that the kernel launched just before this call on the same stream writes none of
+ * head, fill, k_ring, v_ring of THIS call (true for a stack of layers that each own their rings
+ * and share one write head advanced once per token, after some other kernel).  It also lets the
+ * kernel launched after it start early if that kernel was launched in the same way; an ordinary
+ * kernel after it waits as usual.  bf16 rings with at most 12 taps per lane group (J <= 48 at
+ * D = 64, J <= 96 at D = 32) take this form; other cases run exactly as dsqg_decode. */
+int dsqg_decode_overlapped(const void* q, const void* k_new, const void* v_new,
+                           void* k_ring, void* v_ring, const int32_t* head, const int32_t* fill,
+                           const float* pos_bias, const float* scale_embed, const float* head_gain,
+                           const int32_t* offsets, int J, int R,
+                           void* out, int S, int H, int D, int dtype, void* stream);
+
 /* Fills the decode rings from a training-layout prefix.
  * Replaces: nothing executable (the reference has no cache; its generate() re-runs the whole
  *   prefix, DWARF train/train_2048_condU.py:463-487).

@@ -128,3 +128,42 @@ def test_benchmark_shape_runs_and_matches_on_a_sample():
                                              x["head"][sl], x["pos_bias"], x["head_gain"], cfg.offsets)
     assert_bf16_close(out[sl].float().cpu(), ref, "out")
     assert torch.equal(kr[sl].float().cpu(), kref)
+
+
+@pytest.mark.parametrize("D,J", [(64, 43), (32, 43), (64, 45), (128, 43)])
+def test_overlapped_launch_equals_plain_launch_over_a_stack_of_layers(D, J):
+    """dsqg_decode_overlapped over several layers back to back (each layer its own rings, one shared
+    write head), eagerly and replayed from a CUDA graph, gives bit-identical outputs and rings."""
+    g = torch.Generator().manual_seed(100 + D + J)
+    offsets = O.OFFSETS_43 if J == 43 else tuple(O.OFFSETS_43) + (2048, 3072)
+    L, S, H, R = 4, 24, 4, max(offsets) + 1
+    to = lambda t: t.to(torch.bfloat16).to(DEV)
+    kr0, vr0 = to(torch.randn(L, S, H, R, D, generator=g)), to(torch.randn(L, S, H, R, D, generator=g))
+    q, kn, vn = (to(torch.randn(L, S, H, D, generator=g)) for _ in range(3))
+    head = torch.randint(0, R, (S,), generator=g, dtype=torch.int32).to(DEV)
+    fill = torch.randint(1, R + 1, (S,), generator=g, dtype=torch.int32).to(DEV)
+    pb = synth.log_linear_pos_bias(offsets, H).to(DEV)
+
+    def run(overlap, kr, vr, out):
+        for l in range(L):
+            dwarf_b200.dsqg_decode_step(q[l], kn[l], vn[l], kr[l], vr[l], head, pb, None, None, offsets,
+                                        fill, out[l], overlap=overlap)
+
+    kr_a, vr_a, out_a = kr0.clone(), vr0.clone(), torch.empty_like(q)
+    run(False, kr_a, vr_a, out_a)
+    kr_b, vr_b, out_b = kr0.clone(), vr0.clone(), torch.full_like(q, float("nan"))
+    run(True, kr_b, vr_b, out_b)
+    torch.cuda.synchronize()
+    assert torch.equal(out_a, out_b) and torch.equal(kr_a, kr_b) and torch.equal(vr_a, vr_b)
+
+    kr_c, vr_c, out_c = kr0.clone(), vr0.clone(), torch.full_like(q, float("nan"))
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            run(True, kr_c, vr_c, out_c)
+    torch.cuda.current_stream().wait_stream(side)
+    kr_c.copy_(kr0); vr_c.copy_(vr0)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out_a, out_c) and torch.equal(kr_a, kr_c) and torch.equal(vr_a, vr_c)
