@@ -320,7 +320,7 @@ def run_decode_workload(args, rank, local_rank, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": cfg.name, "l2": f"ring footprint {2 * L * cfg.S * cfg.H * cfg.R * cfg.D * esz / 1e9:.1f} GB >> L2",
-                   "launch": "one CUDA graph of the 10 per-layer launches per step"
+                   "launch": f"one CUDA graph of the {L} per-layer launches per step"
                              + ("; layers after the first launched with programmatic dependent launch "
                                 "(ring gather overlaps the layer before)" if args.decode_overlap else ""),
                    "parallelism": f"sequences replicated x{world}, no collective"},
@@ -329,8 +329,9 @@ def run_decode_workload(args, rank, local_rank, world):
                 "d2h_bytes_per_step": small // 3, "ms_per_step": e2e_ms, "steps": e2e_steps},
         "gpu_launches": L * args.steps,
         "roofline": {"bound": "hbm", "kernel": "dsqg_decode", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
-                     "algorithmic_bytes_per_launch": layer_bytes, "ms_per_launch": ms / L},
+                     # DRAM read+write of one launch from the committed ncu capture of this shape
+                     "frac": achieved / peak, "traffic": 34.27e6 if cfg.name.startswith("cfg3") else None,
+                     "peak_source": peak_src, "algorithmic_bytes_per_launch": layer_bytes, "ms_per_launch": ms / L},
         "clocks": clocks,
     }
 
