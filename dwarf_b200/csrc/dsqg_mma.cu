@@ -261,19 +261,26 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
         }
         fold(GC, x0, x1, vf0, vf1);
     };
+    // A tile that reaches past row N-1 may pair its missing rows with key rows that do not exist
+    // either (past the end of the sequence, for the last (b,h) past the end of the tensor).  Their
+    // scores land in lanes that own no diagonal entry and are meant to contribute exp(x - 1e30) = 0;
+    // a NaN or Inf bit pattern there would make that NaN, so such a tile takes the predicated path,
+    // which reads zeros for those rows.
+    const bool past_end = !INTERIOR && g0 + 16 > N;
     int si = 0;
-    for (; si + kTapGroup <= ns && g0 >= tap_s[si + kTapGroup - 1].x; si += kTapGroup)
-        full_taps(std::integral_constant<int, kTapGroup>(), si);
+    if (!past_end)
+        for (; si + kTapGroup <= ns && g0 >= tap_s[si + kTapGroup - 1].x; si += kTapGroup)
+            full_taps(std::integral_constant<int, kTapGroup>(), si);
 #pragma unroll 1
     for (; si < ns; ++si) {
         const int delta = tap_s[si].x;
         if (g0 + 15 < delta) break;                       // taps ascend: no row of the tile reaches back that far
-        if (g0 >= delta) {
+        if (g0 >= delta && !past_end) {
             full_taps(std::integral_constant<int, 1>(), si);
-        } else {                                          // some key rows lie before the sequence start
+        } else {                                          // some key rows lie outside the sequence
             const float pbv = __int_as_float(tap_s[si].y);
             const int kr0 = row_lo - delta, kr1 = row_hi - delta;
-            const bool v0 = kr0 >= 0, v1 = kr1 >= 0;
+            const bool v0 = kr0 >= 0 && kr0 < N, v1 = kr1 >= 0 && kr1 < N;
             const ptrdiff_t off = (ptrdiff_t)delta * D + 8 * tig;
             RowFrag<D> kf0, kf1, vf0[1], vf1[1];
             load_row(kf0, kl - off, tig, v0);
@@ -561,17 +568,20 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
                    (g & 1) ? e1[3] : e1[2], pbv[i], true, true, kf0[i], kf1[i]);
         }
     };
+    // as in the forward: a tile that reaches past row N-1 reads no key row past the end
+    const bool past_end = !INTERIOR && g0 + 16 > N;
     int si = 0;
-    for (; si + G <= ns && g0 >= tap_s[si + G - 1].x; si += G) full_taps(std::integral_constant<int, G>(), si);
+    if (!past_end)
+        for (; si + G <= ns && g0 >= tap_s[si + G - 1].x; si += G) full_taps(std::integral_constant<int, G>(), si);
 #pragma unroll 1
     for (; si < ns; ++si) {
         const int delta = tap_s[si].x;
         if (g0 + 15 < delta) break;
-        if (g0 >= delta) {
+        if (g0 >= delta && !past_end) {
             full_taps(std::integral_constant<int, 1>(), si);
         } else {
             const float pbv = __int_as_float(tap_s[si].y);
-            const bool v0 = row_lo >= delta, v1 = row_hi >= delta;
+            const bool v0 = row_lo >= delta && row_lo - delta < N, v1 = row_hi >= delta && row_hi - delta < N;
             const ptrdiff_t off = (ptrdiff_t)delta * D + 8 * tig;
             RowFrag<D> kf0, kf1, vf0, vf1;
             load_row(kf0, kl - off, tig, v0);

@@ -74,11 +74,18 @@ class _DSQGAttentionBase(nn.Module):
             self.if_gain = nn.Parameter(torch.ones(num_heads))
         self.dropout = nn.Dropout(dropout)
 
-    def forward(self, x, kv_inject=None):
+    def _project_heads(self, x):
+        """x [B,N,D] -> q, k, v [B,H,N,HD] contiguous."""
         B, N, D = x.shape
         H, HD = self.num_heads, self.head_dim
-        q, k, v = (t.view(B, N, H, HD).permute(0, 2, 1, 3).contiguous()
-                   for t in self.qkv_proj(x).split(D, dim=-1))
+        return tuple(t.view(B, N, H, HD).permute(0, 2, 1, 3).contiguous()
+                     for t in self.qkv_proj(x).split(D, dim=-1))
+
+    def attend(self, x, kv_inject=None):
+        """The layer's output together with the k, v [B,H,N,HD] bf16 the op saw (what a decode
+        cache has to be filled with)."""
+        B, N, D = x.shape
+        q, k, v = self._project_heads(x)
         if kv_inject is not None:          # Huygens K/V injection, train_2048_condU.py:178-181
             k = k + kv_inject[0]
             v = v + kv_inject[1]
@@ -89,7 +96,23 @@ class _DSQGAttentionBase(nn.Module):
                              getattr(self, "scale_embed", None), self._offsets)
         out = out if orig == torch.bfloat16 else out.to(orig)
         flat = out.permute(0, 2, 1, 3).reshape(B, N, D)
-        return self.dropout(self.out_proj(flat * torch.sigmoid(self.gate_proj(x))))
+        return self.dropout(self.out_proj(flat * torch.sigmoid(self.gate_proj(x)))), k, v
+
+    def forward(self, x, kv_inject=None):
+        return self.attend(x, kv_inject)[0]
+
+    def decode(self, x, cache, layer, overlap=False):
+        """One new token per sequence: x [S,D] -> [S,D], reading the previous tokens' k, v from
+        ring `layer` of `cache` (a DSQGRingCache whose `advance()` ran for this token) and storing
+        this token's there.  The reference has no such path: its generate() re-runs the whole
+        prefix (train/train_2048_condU.py:463-487)."""
+        S, D = x.shape
+        H, HD = self.num_heads, self.head_dim
+        q, k, v = (t.reshape(S, H, HD).to(cache.k.dtype).contiguous() for t in self.qkv_proj(x).split(D, dim=-1))
+        out = cache.step(layer, q, k, v, self.pos_bias, getattr(self, "if_gain", None),
+                         getattr(self, "scale_embed", None), overlap=overlap)
+        flat = out.reshape(S, D).to(x.dtype)
+        return self.out_proj(flat * torch.sigmoid(self.gate_proj(x)))
 
     def attn_summary(self):
         with torch.no_grad():

@@ -14,18 +14,29 @@ PARAM_REL_TOL_BF16 = 2e-2  # dpos_bias / dscale_embed / dhead_gain in the bf16 p
 FP32_REL_TOL = 1e-5        # ||x-ref||_inf / ||ref||_inf for the fp32 instantiation
 
 
+def _inside_poison(t, dev, dtype, poison):
+    """A device copy of t that sits in the middle of a larger buffer filled with `poison`."""
+    pad = 8192
+    buf = torch.full((t.numel() + 2 * pad,), poison, dtype=dtype, device=dev)
+    view = buf[pad:pad + t.numel()].view(t.shape)
+    view.copy_(t)
+    return view.detach()
+
+
 def cuda_fwd_bwd(q, k, v, pos_bias, dout=None, scale_embed=None, head_gain=None, offsets=None,
-                 dtype=torch.bfloat16):
-    """Run forward (+ backward when dout is given) on cuda:0.  Inputs are CPU tensors."""
+                 dtype=torch.bfloat16, poison=None):
+    """Run forward (+ backward when dout is given) on cuda:0.  Inputs are CPU tensors.
+    poison: value the memory before and after q, k, v and dout is filled with."""
     dev = torch.device("cuda", 0)
-    qd, kd, vd = (t.to(dev, dtype).requires_grad_(dout is not None) for t in (q, k, v))
+    put = (lambda t: t.to(dev, dtype)) if poison is None else (lambda t: _inside_poison(t, dev, dtype, poison))
+    qd, kd, vd = (put(t).requires_grad_(dout is not None) for t in (q, k, v))
     pb = pos_bias.to(dev).float().requires_grad_(dout is not None)
     se = None if scale_embed is None else scale_embed.to(dev).float().requires_grad_(dout is not None)
     hg = None if head_gain is None else head_gain.to(dev).float().requires_grad_(dout is not None)
     out = dwarf_b200.dsqg_attention(qd, kd, vd, pb, hg, se, offsets)
     res = {"out": out.detach().float().cpu()}
     if dout is not None:
-        out.backward(dout.to(dev, dtype))
+        out.backward(put(dout))
         res.update(dq=qd.grad.float().cpu(), dk=kd.grad.float().cpu(), dv=vd.grad.float().cpu(),
                    dpb=pb.grad.cpu())
         if se is not None: res["dse"] = se.grad.cpu()

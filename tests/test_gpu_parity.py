@@ -85,6 +85,32 @@ def test_bf16_forward_backward_vs_oracle(shape, offsets, kernel_path):
     assert_param_grad_close(r["dgain"], ref["dgain"], "dgain", PARAM_REL_TOL_BF16)
 
 
+@pytest.mark.parametrize("poison", [float("nan"), float("inf"), -3.0e38])
+@pytest.mark.parametrize("shape", [(3, 2, 9, 32), (3, 2, 33, 32), (2, 2, 70, 32), (2, 3, 45, 64), (1, 2, 2047, 32), (1, 2, 41, 96)])
+@pytest.mark.parametrize("with_se", [False, True])
+def test_memory_around_the_tensors_is_never_used(shape, poison, with_se, kernel_path):
+    """q, k, v and dout sit inside buffers of NaN / Inf / huge values: a tile that reaches past row
+    N-1 of the last (b,h) must not let what lies behind the tensor into any result.  The offset
+    set has small sparse taps (5, 6 after a dense run 0..3), which pair the missing rows of such a
+    tile with key rows past the end inside the same 8-row group as existing ones."""
+    B, H, N, D = shape
+    offsets = (0, 1, 2, 3, 5, 6, 64, 150)
+    g = torch.Generator().manual_seed(7 + N + D)
+    q, k, v = (bf16_valued(B, H, N, D, scale=0.5, gen=g) for _ in range(3))
+    dout = bf16_valued(B, H, N, D, gen=g)
+    pb = torch.randn(len(offsets), H, generator=g) * 0.5
+    gain = torch.rand(H, generator=g) * 0.4 + 0.8
+    se = torch.randn(len(offsets), D, generator=g) * 0.05 if with_se else None
+    ref = oracle_fwd_bwd(q, k, v, pb, dout, se, gain, offsets)
+    r = cuda_fwd_bwd(q, k, v, pb, dout, se, gain, offsets, torch.bfloat16, poison=poison)
+    for nm in ("out", "dq", "dk", "dv"):
+        assert_bf16_close(r[nm], ref[nm], nm)
+    assert_param_grad_close(r["dpb"], ref["dpb"], "dpb", PARAM_REL_TOL_BF16)
+    assert_param_grad_close(r["dgain"], ref["dgain"], "dgain", PARAM_REL_TOL_BF16)
+    if with_se:
+        assert_param_grad_close(r["dse"], ref["dse"], "dse", PARAM_REL_TOL_BF16)
+
+
 @pytest.mark.parametrize("shape", [(1, 2, 333, 96), (2, 2, 1700, 128), (1, 3, 40, 128)])
 @pytest.mark.parametrize("path", ["auto", "generic"])
 def test_bf16_wide_heads_vs_oracle(shape, path):
