@@ -43,6 +43,13 @@ static int check_shape(int B, int H, int N, int D, int dtype) {
     return DSQG_OK;
 }
 
+// Forward and backward launch one grid row per (batch, head) pair: B*H is bounded by the grid's y extent.
+static int check_op_shape(int B, int H, int N, int D, int dtype) {
+    const int rc = check_shape(B, H, N, D, dtype);
+    if (rc) return rc;
+    return (long long)B * H > 65535 ? DSQG_ERR_BAD_SHAPE : DSQG_OK;
+}
+
 }  // namespace dsqg
 
 using namespace dsqg;
@@ -53,7 +60,7 @@ const char* dsqg_status_str(int status) {
     switch (status) {
         case DSQG_OK: return "ok";
         case DSQG_ERR_NULL_POINTER: return "a required pointer is NULL";
-        case DSQG_ERR_BAD_SHAPE: return "shape out of range (need B,H,N >= 1; D a multiple of 8 in [8,128]; 1 <= J <= 128)";
+        case DSQG_ERR_BAD_SHAPE: return "shape out of range (need B,H,N >= 1; B*H <= 65535 for forward/backward; D a multiple of 8 in [8,128]; 1 <= J <= 128)";
         case DSQG_ERR_BAD_OFFSETS: return "offsets must be non-negative and strictly ascending (and < R for decode)";
         case DSQG_ERR_BAD_DTYPE: return "dtype must be DSQG_DTYPE_BF16 (0) or DSQG_DTYPE_F32 (1)";
         case DSQG_ERR_MISALIGNED: return "tensor pointers must be 16-byte aligned";
@@ -76,7 +83,7 @@ int dsqg_fwd(const void* q, const void* k, const void* v,
              const int32_t* offsets, int J, void* out, float* lse,
              int B, int H, int N, int D, int dtype, void* stream) {
     if (!q || !k || !v || !pos_bias || !out || !lse) return DSQG_ERR_NULL_POINTER;
-    int rc = check_shape(B, H, N, D, dtype);
+    int rc = check_op_shape(B, H, N, D, dtype);
     if (rc) return rc;
     Taps t;
     rc = build_taps(offsets, J, &t);
@@ -94,7 +101,7 @@ int dsqg_fwd(const void* q, const void* k, const void* v,
 }
 
 size_t dsqg_bwd_scratch_bytes(int J, int B, int H, int N, int D, int has_scale_embed) {
-    if (J < 1 || J > DSQG_MAX_TAPS || check_shape(B, H, N, D, DSQG_DTYPE_BF16)) return 0;
+    if (J < 1 || J > DSQG_MAX_TAPS || check_op_shape(B, H, N, D, DSQG_DTYPE_BF16)) return 0;
     // every kernel family tiles at kMinRowsPerBwdTile rows or coarser; with scale_embed the larger of
     // the generic kernels' need (512-row partials) and the tensor-core kernels' need (per-row table,
     // per-tile and per-group partials, prepared tables) is reported
@@ -133,7 +140,7 @@ int dsqg_bwd_stages(const void* q, const void* k, const void* v,
         return DSQG_ERR_NULL_POINTER;
     if (scale_embed && !dscale_embed) return DSQG_ERR_NULL_POINTER;
     if (head_gain && !dhead_gain) return DSQG_ERR_NULL_POINTER;
-    int rc = check_shape(B, H, N, D, dtype);
+    int rc = check_op_shape(B, H, N, D, dtype);
     if (rc) return rc;
     Taps t;
     rc = build_taps(offsets, J, &t);

@@ -37,7 +37,7 @@ extern "C" {
 typedef enum {
     DSQG_OK = 0,
     DSQG_ERR_NULL_POINTER = -1,   /* a required pointer is NULL */
-    DSQG_ERR_BAD_SHAPE = -2,      /* B,H,N,D,J,R,S out of the supported range */
+    DSQG_ERR_BAD_SHAPE = -2,      /* B,H,N,D,J,R,S out of the supported range (B*H <= 65535 for fwd/bwd) */
     DSQG_ERR_BAD_OFFSETS = -3,    /* offsets not strictly ascending / negative */
     DSQG_ERR_BAD_DTYPE = -4,      /* dtype is neither DSQG_DTYPE_BF16 nor DSQG_DTYPE_F32 */
     DSQG_ERR_MISALIGNED = -5,     /* a tensor pointer is not 16-byte aligned */

@@ -24,9 +24,11 @@ def _inside_poison(t, dev, dtype, poison):
 
 
 def cuda_fwd_bwd(q, k, v, pos_bias, dout=None, scale_embed=None, head_gain=None, offsets=None,
-                 dtype=torch.bfloat16, poison=None):
+                 dtype=torch.bfloat16, poison=float("nan")):
     """Run forward (+ backward when dout is given) on cuda:0.  Inputs are CPU tensors.
-    poison: value the memory before and after q, k, v and dout is filled with."""
+    poison: value the memory before and after q, k, v and dout is filled with (NaN by default, so
+    every parity test also checks that nothing outside the tensors reaches a result); None puts
+    the tensors in ordinary allocations."""
     dev = torch.device("cuda", 0)
     put = (lambda t: t.to(dev, dtype)) if poison is None else (lambda t: _inside_poison(t, dev, dtype, poison))
     qd, kd, vd = (put(t).requires_grad_(dout is not None) for t in (q, k, v))

@@ -60,6 +60,7 @@ def test_fwd_argument_errors_are_statuses(lib):
     assert call_fwd(lib, offsets=None) == -1
     assert call_fwd(lib, D=33) == -2 and call_fwd(lib, D=0) == -2 and call_fwd(lib, D=136) == -2
     assert call_fwd(lib, N=0) == -2 and call_fwd(lib, B=-1) == -2
+    assert call_fwd(lib, B=32768, H=2) == -2          # one grid row per (batch, head): B*H <= 65535
     assert call_fwd(lib, offsets=(0, 2, 2)) == -3 and call_fwd(lib, offsets=(-1, 0)) == -3
     assert call_fwd(lib, offsets=(3, 1)) == -3
     assert call_fwd(lib, offsets=tuple(range(129))) == -2
