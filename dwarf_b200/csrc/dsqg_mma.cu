@@ -762,7 +762,9 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
     } else {
         dgrow = dq_tile<D, WB, false, G, SE>(a, init_s, soff_s, tap_s, stage_w, t.n_dense, t.n_sparse, bh, h, g0, L, se, sb);
     }
-    dg_s[threadIdx.x] = dgrow;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dgrow += __shfl_xor_sync(0xffffffffu, dgrow, o);
+    if (L.lane == 0) dg_s[L.warp] = dgrow;
     __syncthreads();
     const int tile = bh * a.tiles_per_bh + blockIdx.x;
     if constexpr (SE) {
@@ -793,17 +795,23 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
             }
         }
     }
-    if (threadIdx.x < J) {
+    // Column sums of the staging tile: two threads per tap (32 rows each, four independent partial
+    // sums, fixed order), so the CTA's tail is a few dozen dependent additions instead of kRows.
+    static_assert(kRows == 64 && kWarps == 4, "the column sums below split 64 rows over thread pairs");
+    for (int j0 = 0; j0 < J; j0 += kWarps * 16) {
+        const int j = j0 + (threadIdx.x >> 1), half = threadIdx.x & 1;
         float s = 0.f;
-        const float* row = stage + threadIdx.x * SP;
-#pragma unroll 8
-        for (int r = 0; r < kRows; ++r) s += row[r];
-        a.dpb_part[(size_t)tile * J + threadIdx.x] = s;
-    } else if (threadIdx.x == kWarps * 32 - 1) {
-        float s = 0.f;
-        for (int r = 0; r < kWarps * 32; ++r) s += dg_s[r];
-        a.dg_part[tile] = s;
+        if (j < J) {
+            const float* row = stage + j * SP + 32 * half;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+            for (int r = 0; r < 32; r += 4) { s0 += row[r]; s1 += row[r + 1]; s2 += row[r + 2]; s3 += row[r + 3]; }
+            s = (s0 + s1) + (s2 + s3);
+        }
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        if (j < J && half == 0) a.dpb_part[(size_t)tile * J + j] = s;
     }
+    if (threadIdx.x == 0) a.dg_part[tile] = (dg_s[0] + dg_s[1]) + (dg_s[2] + dg_s[3]);
 }
 
 // dscale_embed partials: one block per group of kSeGroup consecutive 64-row tiles of a sequence adds
