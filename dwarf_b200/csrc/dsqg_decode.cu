@@ -12,7 +12,7 @@
 namespace dsqg {
 namespace {
 
-constexpr int kWarpsPerBlock = 4;
+constexpr int kWarpsPerBlock = 4;     // 2 warps per CTA measured within 1 % of this
 
 // Raw 8-element slices as loaded from memory; conversion happens after every load of the step
 // has been issued, so one (sequence, head) pair costs a single memory round trip.
@@ -36,6 +36,68 @@ template <> struct Raw8<float> {
     }
 };
 
+// Online-softmax state of one lane group over the taps it has seen: running maximum m, sum l and
+// the 8 output elements this lane owns.
+struct TapState {
+    float m = -INFINITY, l = 0.f;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+};
+
+// Folds tap j (key slice kx, value slice vx of this lane) into the state.  All lanes of the warp
+// must call it (the dot product is summed over the lane group with shuffles); `valid` says
+// whether the tap exists for this sequence.
+template <int TPR>
+__device__ __forceinline__ void fold_tap(TapState& st, const DecodeArgs& a, int j, int h, int d0, bool valid, bool active,
+                                         const float (&qx)[8], float (&kx)[8], const float (&vx)[8]) {
+    if (a.scale_embed != nullptr && valid && active) {
+        float se[8];
+        load8(a.scale_embed + (size_t)j * a.D + d0, se);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) kx[i] += se[i];
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dot = fmaf(qx[i], kx[i], dot);
+    dot = group_sum<TPR>(dot);
+    if (valid) {
+        const float sc = dot * a.scale + a.pos_bias[j * a.H + h];
+        const float mn = fmaxf(st.m, sc);
+        const float cor = __expf(st.m - mn), p = __expf(sc - mn);
+        st.l = st.l * cor + p;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) st.acc[i] = st.acc[i] * cor + p * vx[i];
+        st.m = mn;
+    }
+}
+
+// Merges the 32/TPR lane-group states of the warp and stores gain * acc / l from lane group 0.
+template <typename T, int TPR>
+__device__ __forceinline__ void merge_and_store(TapState& st, const DecodeArgs& a, int sh, int h, int d0, bool writer) {
+#pragma unroll
+    for (int o = TPR; o < 32; o <<= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, st.m, o);
+        const float l2 = __shfl_xor_sync(0xffffffffu, st.l, o);
+        const float mn = fmaxf(st.m, m2);
+        const float c1 = (st.m == -INFINITY) ? 0.f : __expf(st.m - mn);
+        const float c2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
+        st.l = st.l * c1 + l2 * c2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float a2 = __shfl_xor_sync(0xffffffffu, st.acc[i], o);
+            st.acc[i] = st.acc[i] * c1 + a2 * c2;
+        }
+        st.m = mn;
+    }
+    if (writer) {
+        const float gain = a.head_gain ? a.head_gain[h] : 1.f;
+        const float inv = st.l > 0.f ? gain / st.l : 0.f;
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = st.acc[i] * inv;
+        store8(static_cast<T*>(a.out) + (size_t)sh * a.D + d0, o);
+    }
+}
+
 // All K and V rows of up to ROUNDS taps per lane group are requested before any is used
 // (2*ROUNDS independent 16/32-byte loads per lane): one memory round trip per pass.
 template <typename T, int TPR, int ROUNDS>
@@ -57,7 +119,6 @@ decode_kernel(const DecodeArgs a, const Taps t) {
     const T* vn = static_cast<const T*>(a.v_new) + (size_t)sh * D;
     T* kr = static_cast<T*>(a.k_ring) + (size_t)sh * a.R * D;
     T* vr = static_cast<T*>(a.v_ring) + (size_t)sh * a.R * D;
-    const bool has_se = a.scale_embed != nullptr;
 
     float qx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (active) load8(q + d0, qx);
@@ -66,8 +127,7 @@ decode_kernel(const DecodeArgs a, const Taps t) {
         load8(kn + d0, t8); store8(kr + (size_t)head * D + d0, t8);
         load8(vn + d0, t8); store8(vr + (size_t)head * D + d0, t8);
     }
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    float m = -INFINITY, l = 0.f;
+    TapState st;
     const int rounds = (t.J + GROUPS - 1) / GROUPS;
 #pragma unroll 1
     for (int r0 = 0; r0 < rounds; r0 += ROUNDS) {         // one pass for the usual tap counts
@@ -94,51 +154,10 @@ decode_kernel(const DecodeArgs a, const Taps t) {
             const bool valid = j < t.J && t.delta(j < t.J ? j : 0) < fill;
             float kx[8], vx[8];
             kraw[r].get(kx); vraw[r].get(vx);
-            if (has_se && valid && active) {
-                float se[8];
-                load8(a.scale_embed + (size_t)j * D + d0, se);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) kx[i] += se[i];
-            }
-            float dot = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) dot = fmaf(qx[i], kx[i], dot);
-            dot = group_sum<TPR>(dot);
-            if (valid) {
-                const float sc = dot * a.scale + a.pos_bias[j * a.H + h];
-                const float mn = fmaxf(m, sc);
-                const float cor = __expf(m - mn), p = __expf(sc - mn);
-                l = l * cor + p;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[i] = acc[i] * cor + p * vx[i];
-                m = mn;
-            }
+            fold_tap<TPR>(st, a, j, h, d0, valid, active, qx, kx, vx);
         }
     }
-    // ---- merge the GROUPS partial softmax states
-#pragma unroll
-    for (int o = TPR; o < 32; o <<= 1) {
-        const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
-        const float l2 = __shfl_xor_sync(0xffffffffu, l, o);
-        const float mn = fmaxf(m, m2);
-        const float c1 = (m == -INFINITY) ? 0.f : __expf(m - mn);
-        const float c2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
-        l = l * c1 + l2 * c2;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float a2 = __shfl_xor_sync(0xffffffffu, acc[i], o);
-            acc[i] = acc[i] * c1 + a2 * c2;
-        }
-        m = mn;
-    }
-    if (g == 0 && active) {
-        const float gain = a.head_gain ? a.head_gain[h] : 1.f;
-        const float inv = l > 0.f ? gain / l : 0.f;
-        float o[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = acc[i] * inv;
-        store8(static_cast<T*>(a.out) + (size_t)sh * D + d0, o);
-    }
+    merge_and_store<T, TPR>(st, a, sh, h, d0, g == 0 && active);
 }
 
 // ---- single-pass variant for bf16 rings --------------------------------------------------
@@ -225,64 +244,21 @@ decode_1pass_kernel(const DecodeArgs a, const Taps t) {
         *reinterpret_cast<uint4*>(kr + (size_t)head * D + d0) = *reinterpret_cast<const uint4*>(kn + d0);
         *reinterpret_cast<uint4*>(vr + (size_t)head * D + d0) = *reinterpret_cast<const uint4*>(vn + d0);
     }
-    const bool has_se = a.scale_embed != nullptr;
     cp_async_wait_all();
 
     // ---- scores and online softmax over this lane group's taps
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    float m = -INFINITY, l = 0.f;
+    TapState st;
 #pragma unroll
     for (int r = 0; r < ROUNDS; ++r) {
         const int j = r * GROUPS + g;
         const bool valid = j < t.J && t.delta(j < t.J ? j : 0) < fill;
         float kx[8], vx[8];
         Raw8<T> kk; kk.u = k_sm[warp][r][lane]; kk.get(kx);
-        if (has_se && valid && active) {
-            float se[8];
-            load8(a.scale_embed + (size_t)j * D + d0, se);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) kx[i] += se[i];
-        }
-        float dot = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) dot = fmaf(qx[i], kx[i], dot);
-        dot = group_sum<TPR>(dot);
         if (r < VSM) { Raw8<T> vv; vv.u = v_sm[warp][r][lane]; vv.get(vx); }
         else vraw[r - VSM].get(vx);
-        if (valid) {
-            const float sc = dot * a.scale + a.pos_bias[j * a.H + h];
-            const float mn = fmaxf(m, sc);
-            const float cor = __expf(m - mn), p = __expf(sc - mn);
-            l = l * cor + p;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = acc[i] * cor + p * vx[i];
-            m = mn;
-        }
+        fold_tap<TPR>(st, a, j, h, d0, valid, active, qx, kx, vx);
     }
-    // ---- merge the GROUPS partial softmax states
-#pragma unroll
-    for (int o = TPR; o < 32; o <<= 1) {
-        const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
-        const float l2 = __shfl_xor_sync(0xffffffffu, l, o);
-        const float mn = fmaxf(m, m2);
-        const float c1 = (m == -INFINITY) ? 0.f : __expf(m - mn);
-        const float c2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
-        l = l * c1 + l2 * c2;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float a2 = __shfl_xor_sync(0xffffffffu, acc[i], o);
-            acc[i] = acc[i] * c1 + a2 * c2;
-        }
-        m = mn;
-    }
-    if (g == 0 && active) {
-        const float gain = a.head_gain ? a.head_gain[h] : 1.f;
-        const float inv = l > 0.f ? gain / l : 0.f;
-        float o[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = acc[i] * inv;
-        store8(static_cast<T*>(a.out) + (size_t)sh * D + d0, o);
-    }
+    merge_and_store<T, TPR>(st, a, sh, h, d0, g == 0 && active);
 }
 
 template <int TPR, int ROUNDS, int VSM, int CTAS>
@@ -317,8 +293,8 @@ cudaError_t decode_launch(const DecodeArgs& a, const Taps& t, cudaStream_t s, bo
         // shared memory leave 80 registers (6 CTAs per SM); measured 9.95 us per launch on the
         // benchmark shape against 14.4 us for two register passes, 15.1 us with all of V in
         // registers (5 CTAs per SM) and 15.7 us with all of V in shared memory (4 CTAs per SM).
-        if (rounds <= 6) return decode_launch_1pass<TPR, 6, 0, 6>(a, t, s, overlap);
-        if (rounds <= 12) return decode_launch_1pass<TPR, 12, 4, 6>(a, t, s, overlap);
+        if (rounds <= 6) return decode_launch_1pass<TPR, 6, 0, 24 / kWarpsPerBlock>(a, t, s, overlap);
+        if (rounds <= 12) return decode_launch_1pass<TPR, 12, 4, 24 / kWarpsPerBlock>(a, t, s, overlap);
     }
     // Other cases (fp32 rings, more than 12 rounds): register passes of 6 rounds (96 registers),
     // launched as an ordinary kernel (the overlapped form is a hint, not a requirement).

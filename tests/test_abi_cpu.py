@@ -92,13 +92,14 @@ def test_bwd_scratch_and_argument_errors(lib):
 def test_decode_argument_errors(lib):
     off, J = _off((0, 1, 2, 5))
 
-    def call(R=6, head=_fake(8), S=2, D=64, kr=_fake(4)):
-        return lib.dsqg_decode(_fake(1), _fake(2), _fake(3), kr, _fake(5), head, None,
-                               _fake(6), None, None, off, J, R, _fake(7), S, 2, D, 0, None)
-    assert call(R=5) == -3                  # max offset must be < R
-    assert call(head=None) == -1
-    assert call(D=12) == -2 and call(S=0) == -2
-    assert call(kr=_fake(4) + 8) == -5
+    for entry in (lib.dsqg_decode, lib.dsqg_decode_overlapped):      # same checks, no launch
+        def call(R=6, head=_fake(8), S=2, D=64, kr=_fake(4)):
+            return entry(_fake(1), _fake(2), _fake(3), kr, _fake(5), head, None,
+                         _fake(6), None, None, off, J, R, _fake(7), S, 2, D, 0, None)
+        assert call(R=5) == -3                  # max offset must be < R
+        assert call(head=None) == -1
+        assert call(D=12) == -2 and call(S=0) == -2
+        assert call(kr=_fake(4) + 8) == -5
 
 
 def test_ring_prefill_argument_errors(lib):
