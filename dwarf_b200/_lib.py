@@ -29,6 +29,12 @@ _SIGNATURES = {
     "dsqg_bwd_scratch_bytes": (c_size_t, [c_int] * 6),
     "dsqg_bwd": (c_int, [c_void_p] * 3 + [c_void_p] * 3 + [POINTER(c_int32), c_int] + [c_void_p] * 3
                  + [c_void_p] * 3 + [c_void_p] * 3 + [c_void_p, c_size_t] + [c_int] * 5 + [c_void_p]),
+    "dsqg_tensor_core_path": (c_int, [c_int, c_int, POINTER(c_int32), c_int, c_int]),
+    "dsqg_fwd_scaled": (c_int, [c_void_p] * 3 + [c_void_p] * 3 + [POINTER(c_int32), c_int] + [c_void_p] * 2
+                        + [c_int] * 5 + [c_void_p, c_float]),
+    "dsqg_bwd_scaled": (c_int, [c_void_p] * 3 + [c_void_p] * 3 + [POINTER(c_int32), c_int] + [c_void_p] * 3
+                        + [c_void_p] * 3 + [c_void_p] * 3 + [c_void_p, c_size_t] + [c_int] * 5
+                        + [c_void_p, c_float]),
     "dsqg_bwd_stages": (c_int, [c_void_p] * 3 + [c_void_p] * 3 + [POINTER(c_int32), c_int] + [c_void_p] * 3
                         + [c_void_p] * 3 + [c_void_p] * 3 + [c_void_p, c_size_t] + [c_int] * 5
                         + [c_void_p, c_int]),

@@ -78,10 +78,17 @@ const char* dsqg_last_cuda_error(void) { return g_cuda_err; }
 
 int dsqg_version(void) { return 100; }
 
-int dsqg_fwd(const void* q, const void* k, const void* v,
-             const float* pos_bias, const float* scale_embed, const float* head_gain,
-             const int32_t* offsets, int J, void* out, float* lse,
-             int B, int H, int N, int D, int dtype, void* stream) {
+int dsqg_tensor_core_path(int dtype, int D, const int32_t* offsets, int J, int has_scale_embed) {
+    Taps t;
+    if (check_shape(1, 1, 1, D, dtype) || build_taps(offsets, J, &t)) return 0;
+    return mma_fwd_supported(dtype, D, t, has_scale_embed != 0) && mma_path_supported(dtype, D, t, has_scale_embed != 0) ? 1 : 0;
+}
+
+// scale <= 0 selects the operator's own 1/sqrt(D)
+static int fwd_impl(const void* q, const void* k, const void* v,
+                    const float* pos_bias, const float* scale_embed, const float* head_gain,
+                    const int32_t* offsets, int J, void* out, float* lse,
+                    int B, int H, int N, int D, int dtype, void* stream, float scale) {
     if (!q || !k || !v || !pos_bias || !out || !lse) return DSQG_ERR_NULL_POINTER;
     int rc = check_op_shape(B, H, N, D, dtype);
     if (rc) return rc;
@@ -95,9 +102,24 @@ int dsqg_fwd(const void* q, const void* k, const void* v,
     a.q = q; a.k = k; a.v = v; a.pos_bias = pos_bias; a.scale_embed = scale_embed;
     a.head_gain = head_gain; a.out = out; a.lse = lse;
     a.B = B; a.H = H; a.N = N; a.D = D;
-    a.scale = 1.0f / sqrtf((float)D);
+    a.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
     cudaError_t e = launch_fwd(a, t, dtype, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
+}
+
+int dsqg_fwd(const void* q, const void* k, const void* v,
+             const float* pos_bias, const float* scale_embed, const float* head_gain,
+             const int32_t* offsets, int J, void* out, float* lse,
+             int B, int H, int N, int D, int dtype, void* stream) {
+    return fwd_impl(q, k, v, pos_bias, scale_embed, head_gain, offsets, J, out, lse, B, H, N, D, dtype, stream, 0.f);
+}
+
+int dsqg_fwd_scaled(const void* q, const void* k, const void* v,
+                    const float* pos_bias, const float* scale_embed, const float* head_gain,
+                    const int32_t* offsets, int J, void* out, float* lse,
+                    int B, int H, int N, int D, int dtype, void* stream, float scale) {
+    if (!(scale > 0.f) || !(scale < 3.0e38f)) return DSQG_ERR_UNSUPPORTED;
+    return fwd_impl(q, k, v, pos_bias, scale_embed, head_gain, offsets, J, out, lse, B, H, N, D, dtype, stream, scale);
 }
 
 size_t dsqg_bwd_scratch_bytes(int J, int B, int H, int N, int D, int has_scale_embed) {
@@ -127,6 +149,15 @@ int dsqg_bwd(const void* q, const void* k, const void* v,
                            B, H, N, D, dtype, stream, DSQG_BWD_STAGE_ALL);
 }
 
+static int bwd_impl(const void* q, const void* k, const void* v,
+                    const float* pos_bias, const float* scale_embed, const float* head_gain,
+                    const int32_t* offsets, int J,
+                    const void* out, const float* lse, const void* dout,
+                    void* dq, void* dk, void* dv,
+                    float* dpos_bias, float* dscale_embed, float* dhead_gain,
+                    void* scratch, size_t scratch_bytes,
+                    int B, int H, int N, int D, int dtype, void* stream, int stages, float scale);
+
 int dsqg_bwd_stages(const void* q, const void* k, const void* v,
                     const float* pos_bias, const float* scale_embed, const float* head_gain,
                     const int32_t* offsets, int J,
@@ -135,6 +166,32 @@ int dsqg_bwd_stages(const void* q, const void* k, const void* v,
                     float* dpos_bias, float* dscale_embed, float* dhead_gain,
                     void* scratch, size_t scratch_bytes,
                     int B, int H, int N, int D, int dtype, void* stream, int stages) {
+    return bwd_impl(q, k, v, pos_bias, scale_embed, head_gain, offsets, J, out, lse, dout, dq, dk, dv,
+                    dpos_bias, dscale_embed, dhead_gain, scratch, scratch_bytes, B, H, N, D, dtype, stream, stages, 0.f);
+}
+
+int dsqg_bwd_scaled(const void* q, const void* k, const void* v,
+                    const float* pos_bias, const float* scale_embed, const float* head_gain,
+                    const int32_t* offsets, int J,
+                    const void* out, const float* lse, const void* dout,
+                    void* dq, void* dk, void* dv,
+                    float* dpos_bias, float* dscale_embed, float* dhead_gain,
+                    void* scratch, size_t scratch_bytes,
+                    int B, int H, int N, int D, int dtype, void* stream, float scale) {
+    if (!(scale > 0.f) || !(scale < 3.0e38f)) return DSQG_ERR_UNSUPPORTED;
+    return bwd_impl(q, k, v, pos_bias, scale_embed, head_gain, offsets, J, out, lse, dout, dq, dk, dv,
+                    dpos_bias, dscale_embed, dhead_gain, scratch, scratch_bytes, B, H, N, D, dtype, stream,
+                    DSQG_BWD_STAGE_ALL, scale);
+}
+
+static int bwd_impl(const void* q, const void* k, const void* v,
+                    const float* pos_bias, const float* scale_embed, const float* head_gain,
+                    const int32_t* offsets, int J,
+                    const void* out, const float* lse, const void* dout,
+                    void* dq, void* dk, void* dv,
+                    float* dpos_bias, float* dscale_embed, float* dhead_gain,
+                    void* scratch, size_t scratch_bytes,
+                    int B, int H, int N, int D, int dtype, void* stream, int stages, float scale) {
     if (stages < 1 || stages > DSQG_BWD_STAGE_ALL) return DSQG_ERR_UNSUPPORTED;
     if (!q || !k || !v || !pos_bias || !out || !lse || !dout || !dq || !dk || !dv || !dpos_bias || !scratch)
         return DSQG_ERR_NULL_POINTER;
@@ -160,7 +217,7 @@ int dsqg_bwd_stages(const void* q, const void* k, const void* v,
     a.delta = a.dpb_part = a.dg_part = a.dse_part = nullptr;
     a.n_tiles = a.tiles_per_bh = a.n_dse_blocks = 0;
     a.B = B; a.H = H; a.N = N; a.D = D;
-    a.scale = 1.0f / sqrtf((float)D);
+    a.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
     cudaError_t e = launch_bwd(a, t, dtype, static_cast<cudaStream_t>(stream), stages);
     return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
 }

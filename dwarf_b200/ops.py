@@ -11,6 +11,7 @@ from __future__ import annotations
 from typing import Optional, Sequence
 
 import torch
+import torch.nn.functional as F
 
 from . import _lib
 
@@ -52,6 +53,22 @@ def _check_inputs(q, k, v, pos_bias, head_gain, scale_embed, J):
         raise ValueError(f"dsqg: head_gain must be [{H}], got {tuple(head_gain.shape)}")
 
 
+def _padded_head_dim(q, off, J, has_scale_embed):
+    """Head dimension the kernels are called with.  The bf16 tensor-core kernels exist for
+    D in {32, 64, 96, 128}; another bf16 head dimension (80 in the reference's 85M condM model,
+    train/train_2048_85m_condM.py:67-69; 48) is zero-padded up to the next of those when the
+    tensor-core kernels take the padded problem, with the scale 1/sqrt(D) of the true width passed
+    explicitly: several times faster than the CUDA-core kernels on the odd width.  The reference
+    pads to a power of two inside its kernels (kernels/dsqg_attention_v2.py:344).  fp32 tensors
+    are never padded."""
+    D = q.shape[-1]
+    if q.dtype != torch.bfloat16 or D % 32 == 0 or D > 128 or D % 8 != 0:
+        return D
+    Dp = (D + 31) // 32 * 32
+    lib = _lib.load()
+    return Dp if lib.dsqg_tensor_core_path(_lib.DSQG_DTYPE_BF16, Dp, off, J, int(has_scale_embed)) else D
+
+
 def _f32c(t):
     return None if t is None else t.detach().to(torch.float32).contiguous()
 
@@ -68,45 +85,56 @@ class DSQGFunction(torch.autograd.Function):
         lib = _lib.load()
         off, J = _lib.offsets_array(offsets)
         _check_inputs(q, k, v, pos_bias, head_gain, scale_embed, J)
-        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         pb, hg, se = _f32c(pos_bias), _f32c(head_gain), _f32c(scale_embed)
         B, H, N, D = q.shape
+        Dp = _padded_head_dim(q, off, J, scale_embed is not None)
+        if Dp != D:                              # zero columns change no score and give zero outputs
+            q, k, v = (F.pad(t, (0, Dp - D)) for t in (q, k, v))
+            se = None if se is None else F.pad(se, (0, Dp - D))
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         out = torch.empty_like(q)
         lse = torch.empty(B, H, N, device=q.device, dtype=torch.float32)
         with torch.cuda.device(q.device):
             stream = torch.cuda.current_stream(q.device).cuda_stream
-            _lib.check(lib.dsqg_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), _ptr(se),
-                                    _ptr(hg), off, J, out.data_ptr(), lse.data_ptr(),
-                                    B, H, N, D, _dtype_code(q), stream), "dsqg_fwd")
+            _lib.check(lib.dsqg_fwd_scaled(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), _ptr(se),
+                                           _ptr(hg), off, J, out.data_ptr(), lse.data_ptr(),
+                                           B, H, N, Dp, _dtype_code(q), stream, D ** -0.5), "dsqg_fwd")
         ctx.save_for_backward(q, k, v, pb, hg, se, out, lse)
         ctx.offsets = tuple(offsets)
+        ctx.head_dim = D
         ctx.param_dtypes = (pos_bias.dtype, None if head_gain is None else head_gain.dtype,
                             None if scale_embed is None else scale_embed.dtype)
-        return out
+        return out if Dp == D else out[..., :D].contiguous()
 
     @staticmethod
     def backward(ctx, dout):
         lib = _lib.load()
         q, k, v, pb, hg, se, out, lse = ctx.saved_tensors
         off, J = _lib.offsets_array(ctx.offsets)
-        B, H, N, D = q.shape
-        dout = dout.contiguous()                      # kernels/dsqg_attention_v3.py:394
+        B, H, N, Dp = q.shape
+        D = ctx.head_dim
         if dout.dtype != q.dtype:
             dout = dout.to(q.dtype)
+        if Dp != D:
+            dout = F.pad(dout, (0, Dp - D))
+        dout = dout.contiguous()                      # kernels/dsqg_attention_v3.py:394
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dpb = torch.empty_like(pb)
         dse = None if se is None else torch.empty_like(se)
         dhg = None if hg is None else torch.empty_like(hg)
-        nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, int(se is not None))
+        nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, Dp, int(se is not None))
         scratch = torch.empty(nbytes, device=q.device, dtype=torch.uint8)
         with torch.cuda.device(q.device):
             stream = torch.cuda.current_stream(q.device).cuda_stream
-            _lib.check(lib.dsqg_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), _ptr(se),
-                                    _ptr(hg), off, J, out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
-                                    dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                    dpb.data_ptr(), _ptr(dse), _ptr(dhg),
-                                    scratch.data_ptr(), nbytes, B, H, N, D, _dtype_code(q), stream),
-                       "dsqg_bwd")
+            _lib.check(lib.dsqg_bwd_scaled(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), _ptr(se),
+                                           _ptr(hg), off, J, out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
+                                           dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                           dpb.data_ptr(), _ptr(dse), _ptr(dhg),
+                                           scratch.data_ptr(), nbytes, B, H, N, Dp, _dtype_code(q), stream,
+                                           D ** -0.5), "dsqg_bwd")
+        if Dp != D:
+            dq, dk, dv = (t[..., :D].contiguous() for t in (dq, dk, dv))
+            dse = None if dse is None else dse[:, :D].contiguous()
         pb_dt, hg_dt, se_dt = ctx.param_dtypes
         return (dq, dk, dv, dpb.to(pb_dt),
                 None if dhg is None else dhg.to(hg_dt),

@@ -149,6 +149,33 @@ int dsqg_bwd_stages(const void* q, const void* k, const void* v,
                     void* scratch, size_t scratch_bytes,
                     int B, int H, int N, int D, int dtype, void* stream, int stages);
 
+/* 1 if dsqg_fwd and dsqg_bwd run the tensor-core kernels for this dtype, head dimension, offset
+ * set and use of scale_embed, 0 if they run the CUDA-core kernels (or the arguments are invalid).
+ * Replaces: nothing (the reference has one kernel family); a host uses it to decide whether
+ * zero-padding the head dimension (dsqg_fwd_scaled) pays.  No launch, no device access. */
+int dsqg_tensor_core_path(int dtype, int D, const int32_t* offsets, int J, int has_scale_embed);
+
+/* dsqg_fwd / dsqg_bwd with the score scale given by the caller instead of 1/sqrt(D):
+ *     s_j = scale * q[n].(k[n-delta_j] [+ scale_embed[j]]) + pos_bias[j,h].
+ * Replaces: the power-of-two padding of the head dimension inside the reference's kernels
+ *   (BLOCK_HD = next_power_of_2(HD) with masked lanes, kernels/dsqg_attention_v2.py:344): a host
+ *   that zero-pads q, k, v (and scale_embed, dout) from HD = 80 to 96 columns calls these with
+ *   D = 96 and scale = 1/sqrt(80), gets the tensor-core kernels, and drops the padded columns of
+ *   the results (they are exactly zero).  scale must be positive and finite
+ *   (DSQG_ERR_UNSUPPORTED otherwise).  Everything else as dsqg_fwd / dsqg_bwd. */
+int dsqg_fwd_scaled(const void* q, const void* k, const void* v,
+                    const float* pos_bias, const float* scale_embed, const float* head_gain,
+                    const int32_t* offsets, int J, void* out, float* lse,
+                    int B, int H, int N, int D, int dtype, void* stream, float scale);
+int dsqg_bwd_scaled(const void* q, const void* k, const void* v,
+                    const float* pos_bias, const float* scale_embed, const float* head_gain,
+                    const int32_t* offsets, int J,
+                    const void* out, const float* lse, const void* dout,
+                    void* dq, void* dk, void* dv,
+                    float* dpos_bias, float* dscale_embed, float* dhead_gain,
+                    void* scratch, size_t scratch_bytes,
+                    int B, int H, int N, int D, int dtype, void* stream, float scale);
+
 /* Single-token decode over a circular K/V ring buffer.
  * Replaces: nothing executable -- the reference only describes the O(1) cache in prose
  *   (DWARF README.md:175-179; generate() in train/train_2048_condU.py:463-487 re-runs the

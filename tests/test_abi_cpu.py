@@ -122,3 +122,24 @@ def test_kernel_path_knob(lib):
     assert lib.dsqg_set_kernel_path(1) == 0 and lib.dsqg_set_kernel_path(0) == 0
     assert lib.dsqg_set_kernel_path(2) == 0 and lib.dsqg_set_kernel_path(3) == 0 and lib.dsqg_set_kernel_path(0) == 0
     assert lib.dsqg_set_kernel_path(5) == -8
+
+
+def test_tensor_core_path_query_and_scaled_entry_checks(lib):
+    j43 = tuple(range(32)) + (48, 64, 96, 128, 192, 256, 384, 512, 768, 1024, 1536)
+    j44 = tuple(range(33)) + j43[32:]
+    q = lambda dtype, D, offs, se: lib.dsqg_tensor_core_path(dtype, D, *_off(offs), se)
+    assert q(0, 32, j43, 0) == 1 and q(0, 64, j44, 1) == 1 and q(0, 96, j43, 0) == 1 and q(0, 128, j43, 0) == 1
+    assert q(0, 80, j43, 0) == 0 and q(0, 48, j43, 0) == 0          # odd widths: CUDA-core kernels unless padded
+    d41 = tuple(range(41)) + (128, 384, 1536)
+    assert q(0, 96, j44, 0) == 1 and q(0, 64, d41, 0) == 1
+    assert q(0, 96, j43, 1) == 0 and q(0, 96, d41, 0) == 0          # wide heads: dense window up to 32, no scale_embed
+    assert q(1, 32, j43, 0) == 0                                    # fp32 storage
+    assert q(0, 32, (3, 1), 0) == 0 and q(0, 33, j43, 0) == 0       # invalid arguments
+    off, J = _off((0, 1, 2, 8))
+    fwd = lambda scale: lib.dsqg_fwd_scaled(_fake(1), _fake(2), _fake(3), _fake(4), None, None, off, J,
+                                            _fake(5), _fake(6), 1, 2, 16, 32, 0, None, scale)
+    assert fwd(0.0) == -8 and fwd(-1.0) == -8 and fwd(float("inf")) == -8 and fwd(float("nan")) == -8
+    bwd = lambda scale: lib.dsqg_bwd_scaled(_fake(1), _fake(2), _fake(3), _fake(4), None, None, off, J,
+                                            _fake(5), _fake(6), _fake(7), _fake(10), _fake(11), _fake(12),
+                                            _fake(13), None, None, _fake(20), 1 << 20, 1, 1, 16, 32, 0, None, scale)
+    assert bwd(0.0) == -8 and bwd(float("nan")) == -8

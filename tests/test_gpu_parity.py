@@ -111,6 +111,34 @@ def test_memory_around_the_tensors_is_never_used(shape, poison, with_se, kernel_
         assert_param_grad_close(r["dse"], ref["dse"], "dse", PARAM_REL_TOL_BF16)
 
 
+@pytest.mark.parametrize("shape", [(2, 3, 700, 80), (1, 2, 300, 48), (1, 2, 90, 80), (1, 1, 2047, 80)])
+@pytest.mark.parametrize("offsets", [O.OFFSETS_43, O.OFFSETS_44, tuple(range(41)) + (128, 384, 1536)],
+                         ids=["J43", "J44", "d41"])
+def test_bf16_odd_head_widths_run_zero_padded_on_the_tensor_core_kernels(shape, offsets):
+    """HD = 80 (the reference's 85M condM model) and 48: the operator pads the head dimension with
+    zero columns to 96 / 64 when the tensor-core kernels take the padded problem and passes the
+    true 1/sqrt(HD); results and gradients have the caller's width and match the oracle."""
+    B, H, N, D = shape
+    lib = _lib.load()
+    off, J = _lib.offsets_array(offsets)
+    padded = (D + 31) // 32 * 32
+    assert lib.dsqg_tensor_core_path(0, D, off, J, 0) == 0
+    takes_padded = lib.dsqg_tensor_core_path(0, padded, off, J, 0) == 1
+    assert takes_padded == (padded == 64 or offsets[32] != 32 or offsets[33] != 33)   # wide heads: dense window up to 32
+    g = torch.Generator().manual_seed(5 + N + D)
+    q, k, v = (bf16_valued(B, H, N, D, scale=0.5, gen=g) for _ in range(3))
+    dout = bf16_valued(B, H, N, D, gen=g)
+    pb = synth.log_linear_pos_bias(offsets, H) + torch.randn(len(offsets), H, generator=g) * 0.05
+    gain = torch.rand(H, generator=g) * 0.4 + 0.8
+    ref = oracle_fwd_bwd(q, k, v, pb, dout, None, gain, offsets)
+    r = cuda_fwd_bwd(q, k, v, pb, dout, None, gain, offsets, torch.bfloat16)
+    for nm in ("out", "dq", "dk", "dv"):
+        assert r[nm].shape == (B, H, N, D)
+        assert_bf16_close(r[nm], ref[nm], nm)
+    assert_param_grad_close(r["dpb"], ref["dpb"], "dpb", PARAM_REL_TOL_BF16)
+    assert_param_grad_close(r["dgain"], ref["dgain"], "dgain", PARAM_REL_TOL_BF16)
+
+
 @pytest.mark.parametrize("shape", [(1, 2, 333, 96), (2, 2, 1700, 128), (1, 3, 40, 128)])
 @pytest.mark.parametrize("path", ["auto", "generic"])
 def test_bf16_wide_heads_vs_oracle(shape, path):
