@@ -113,7 +113,17 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     lib = _lib.load()
-    x = synth.make_op_inputs(cfg)                       # CPU, seeded; every rank runs a full batch
+    x = synth.make_op_inputs(cfg)                       # CPU, seeded
+    strong = args.scaling == "strong" and world > 1
+    global_B = cfg.B
+    if strong:                                          # fixed problem: this rank's slice of the batch
+        import dataclasses
+        b0, b1 = ddist.shard_range(cfg.B, rank, world)
+        if b1 <= b0:
+            raise SystemExit(f"--scaling strong: batch {cfg.B} has no entry for rank {rank} of {world}")
+        for nm in ("q", "k", "v", "dout"):
+            x[nm] = x[nm][b0:b1].contiguous()
+        cfg = dataclasses.replace(cfg, B=b1 - b0)
     host = {nm: x[nm].pin_memory() for nm in ("q", "k", "v", "dout")}
     q, k, v, dout = (host[nm].to(dev, non_blocking=True) for nm in ("q", "k", "v", "dout"))
     pb = x["pos_bias"].to(dev); gain = x["head_gain"].to(dev)
@@ -153,20 +163,27 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     for _ in range(args.warmup):
         fwd(); bwd(1); bwd(6)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    # A step touches 12 T bytes; when that does not clearly exceed the 126 MB L2 (small per-GPU
+    # batches, e.g. --scaling strong at 8 GPUs) a 256 MB buffer is overwritten between steps and
+    # the step time is the sum of the kernels' event intervals instead of the whole span.
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if 12 * op_bytes(cfg) < (256 << 20) else None
     ddist.barrier(); torch.cuda.synchronize()
     t_wall = time.perf_counter()
     for i in range(args.steps):
+        if flush_buf is not None:
+            flush_buf.fill_(i & 0xff)
         ev[i][0].record(stream); fwd()
         ev[i][1].record(stream); bwd(1)
         ev[i][2].record(stream); bwd(6)       # dK/dV kernel; its first CTAs also reduce dpos_bias / dhead_gain
         ev[i][3].record(stream)
     torch.cuda.synchronize(); ddist.barrier()
     wall_ms = (time.perf_counter() - t_wall) * 1e3
-    total_ms = ev[0][0].elapsed_time(ev[-1][3])
+    total_ms = ev[0][0].elapsed_time(ev[-1][3]) if flush_buf is None else \
+        sum(ev[i][0].elapsed_time(ev[i][3]) for i in range(args.steps))
     kern_ms = [sum(ev[i][s].elapsed_time(ev[i][s + 1]) for i in range(args.steps)) / args.steps for s in range(3)]
     total_ms = ddist.max_over_ranks(total_ms, dev if world > 1 else "cpu")
     ms_per_step = total_ms / args.steps
-    tokens_per_step = B * N * world
+    tokens_per_step = global_B * N if strong else B * N * world       # what all ranks processed
     value = tokens_per_step / (ms_per_step * 1e-3)
 
     # ---- end to end: pinned host buffers in, pinned host buffers out ----------------------
@@ -198,7 +215,7 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     peak, peak_src = measured_peaks()
     # DRAM bytes (read + write) per launch from the ncu capture summarised in
     # profiles/dsqg_mma_kernels_cfg1.md; only known for the workload that was captured.
-    ncu_traffic = {"cfg1": [120.30e6, 197.12e6, 186.98e6]}.get("" if se is not None else args.workload, [None] * 3)
+    ncu_traffic = {"cfg1": [120.30e6, 197.12e6, 186.98e6]}.get("" if se is not None or strong else args.workload, [None] * 3)
     names = ["dsqg_fwd", "dsqg_bwd_dq", "dsqg_bwd_dkdv"]
     alg = [4 * T, 6 * T, 6 * T]           # per launch: fwd Q,K,V->O ; dq Q,K,V,O,dO->dQ ; dkdv Q,K,V,dO->dK,dV
     top = max(range(3), key=lambda s: kern_ms[s])
@@ -207,11 +224,13 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     line = {
         "metric": "DSQG fwd+bwd tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
         "dtype": "bf16" if cfg.dtype == torch.bfloat16 else "f32", "data": "synthetic",
         "config": {"workload": cfg.name + (" +scale_embed" if se is not None else ""), "tokens_per_step_per_gpu": B * N,
-                   "l2": "inputs+outputs per step (>= 400 MB) exceed the 126 MB L2; no flush",
-                   "parallelism": f"batch replicated x{world}, no collective"},
+                   "l2": (f"inputs+outputs per step ({12 * T / 1e6:.0f} MB) exceed the 126 MB L2; no flush" if flush_buf is None
+                          else f"inputs+outputs per step are {12 * T / 1e6:.0f} MB: L2 flushed by a 256 MB write between steps"),
+                   "parallelism": (f"batch of {global_B} split over {world} GPUs, no collective" if strong
+                                   else f"batch replicated x{world}, no collective")},
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": 4 * T, "d2h_bytes_per_step": 4 * T, "ms_per_step": e2e_ms,
                 "steps": e2e_steps},
@@ -470,6 +489,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale-embed", action="store_true",
                     help="op workloads: add the condU scale_embed term (seeded N(0, 0.05) [J,D]) and its gradient")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                    help="op workloads at N > 1: weak = every GPU runs the configuration's batch (default); "
+                         "strong = the configuration's batch is split over the GPUs")
     ap.add_argument("--no-decode-overlap", dest="decode_overlap", action="store_false",
                     help="cfg3: launch every layer as an ordinary kernel (default: layers after the first overlap the one before)")
     ap.add_argument("--decode-layers", type=int, default=0, help="cfg3: number of layers (default: the 10 of the configuration)")
