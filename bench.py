@@ -113,6 +113,9 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     lib = _lib.load()
+    if args.batch > 0:                                  # a smaller case of the same workload (e.g. for an ncu capture)
+        import dataclasses
+        cfg = dataclasses.replace(cfg, B=args.batch, name=cfg.name.replace(f"B{cfg.B} ", f"B{args.batch} "))
     x = synth.make_op_inputs(cfg)                       # CPU, seeded
     strong = args.scaling == "strong" and world > 1
     global_B = cfg.B
@@ -215,7 +218,7 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     peak, peak_src = measured_peaks()
     # DRAM bytes (read + write) per launch from the ncu capture summarised in
     # profiles/dsqg_mma_kernels_cfg1.md; only known for the workload that was captured.
-    ncu_traffic = {"cfg1": [120.30e6, 197.12e6, 186.98e6]}.get("" if se is not None or strong else args.workload, [None] * 3)
+    ncu_traffic = {"cfg1": [120.30e6, 197.12e6, 186.98e6]}.get("" if se is not None or strong or args.batch > 0 else args.workload, [None] * 3)
     names = ["dsqg_fwd", "dsqg_bwd_dq", "dsqg_bwd_dkdv"]
     alg = [4 * T, 6 * T, 6 * T]           # per launch: fwd Q,K,V->O ; dq Q,K,V,O,dO->dQ ; dkdv Q,K,V,dO->dK,dV
     top = max(range(3), key=lambda s: kern_ms[s])
@@ -489,6 +492,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale-embed", action="store_true",
                     help="op workloads: add the condU scale_embed term (seeded N(0, 0.05) [J,D]) and its gradient")
+    ap.add_argument("--batch", type=int, default=0, help="op workloads: batch size instead of the configuration's")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="op workloads at N > 1: weak = every GPU runs the configuration's batch (default); "
                          "strong = the configuration's batch is split over the GPUs")
