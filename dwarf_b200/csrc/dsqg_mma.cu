@@ -264,18 +264,19 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
     // A tile that reaches past row N-1 may pair its missing rows with key rows that do not exist
     // either (past the end of the sequence, for the last (b,h) past the end of the tensor).  Their
     // scores land in lanes that own no diagonal entry and are meant to contribute exp(x - 1e30) = 0;
-    // a NaN or Inf bit pattern there would make that NaN, so such a tile takes the predicated path,
+    // a NaN or Inf bit pattern there would make that NaN, so boundary tiles take the predicated path,
     // which reads zeros for those rows.
-    const bool past_end = !INTERIOR && g0 + 16 > N;
+    // Only interior tiles load taps unpredicated (boundary tiles are the first WB rows, which the
+    // usual tap sets do not reach from, and the last partial tile).
     int si = 0;
-    if (!past_end)
+    if constexpr (INTERIOR)
         for (; si + kTapGroup <= ns && g0 >= tap_s[si + kTapGroup - 1].x; si += kTapGroup)
             full_taps(std::integral_constant<int, kTapGroup>(), si);
 #pragma unroll 1
     for (; si < ns; ++si) {
         const int delta = tap_s[si].x;
         if (g0 + 15 < delta) break;                       // taps ascend: no row of the tile reaches back that far
-        if (g0 >= delta && !past_end) {
+        if (INTERIOR && g0 >= delta) {
             full_taps(std::integral_constant<int, 1>(), si);
         } else {                                          // some key rows lie outside the sequence
             const float pbv = __int_as_float(tap_s[si].y);
@@ -568,16 +569,15 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
                    (g & 1) ? e1[3] : e1[2], pbv[i], true, true, kf0[i], kf1[i]);
         }
     };
-    // as in the forward: a tile that reaches past row N-1 reads no key row past the end
-    const bool past_end = !INTERIOR && g0 + 16 > N;
+    // as in the forward: only interior tiles load taps unpredicated, so no key row past the end is read
     int si = 0;
-    if (!past_end)
+    if constexpr (INTERIOR)
         for (; si + G <= ns && g0 >= tap_s[si + G - 1].x; si += G) full_taps(std::integral_constant<int, G>(), si);
 #pragma unroll 1
     for (; si < ns; ++si) {
         const int delta = tap_s[si].x;
         if (g0 + 15 < delta) break;
-        if (g0 >= delta && !past_end) {
+        if (INTERIOR && g0 >= delta) {
             full_taps(std::integral_constant<int, 1>(), si);
         } else {
             const float pbv = __int_as_float(tap_s[si].y);
