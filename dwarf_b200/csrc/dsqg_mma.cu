@@ -406,7 +406,7 @@ template <int D> struct BwdTune {
     static constexpr int dq_ctas_se = D == 32 ? 4 : 3;      // with scale_embed: more shared memory and registers per CTA
     static constexpr int dkdv_group = D == 32 ? 2 : 1, dkdv_ctas = D == 32 ? 4 : (D == 64 ? 3 : 2);
 };
-constexpr int kStagePitch = kRows + 3;      // 67: 2-way bank conflicts on the scattered writes, none on the column sums
+constexpr int kStagePitch = kRows + 4;      // 68: no bank conflicts on the scattered writes; the column sums rotate their start
 constexpr int kStagePitchSe = kRows + 4;    // 68 with scale_embed: rows are read back as 8-byte pairs by the dS MMAs
 template <bool SE> struct StagePitch { static constexpr int v = SE ? kStagePitchSe : kStagePitch; };
 
@@ -802,10 +802,16 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
         const int j = j0 + (threadIdx.x >> 1), half = threadIdx.x & 1;
         float s = 0.f;
         if (j < J) {
+            // pitch 68 puts rows j and j+8 (and the two halves) in the same banks: start each of the
+            // four at a different column so that a warp's 32 reads fall into 32 banks
             const float* row = stage + j * SP + 32 * half;
+            const int rot = ((j >> 3) & 1) + 2 * half;
             float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-            for (int r = 0; r < 32; r += 4) { s0 += row[r]; s1 += row[r + 1]; s2 += row[r + 2]; s3 += row[r + 3]; }
+            for (int r = 0; r < 32; r += 4) {
+                s0 += row[(r + rot) & 31]; s1 += row[(r + 1 + rot) & 31];
+                s2 += row[(r + 2 + rot) & 31]; s3 += row[(r + 3 + rot) & 31];
+            }
             s = (s0 + s1) + (s2 + s3);
         }
         s += __shfl_xor_sync(0xffffffffu, s, 1);
