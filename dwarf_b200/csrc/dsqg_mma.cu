@@ -472,6 +472,7 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
         if (ok_hi) rs[row_hi] = make_float2(l2_hi, delta_hi);
     }
     float dQ[D / 8][4];
+    const int stage_base = (WB + 15 + g - 2 * tig) * SP + g;      // plain kernel: see the dense loop
 
     // ---- dense window
 #pragma unroll
@@ -488,7 +489,18 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
             } else {
                 ini = init_s[nt * 32 + L.lane];
             }
-            const int4 so = soff_s[nt * 32 + L.lane];
+            int so_r[4];
+            if constexpr (SE) {
+                const int4 so = soff_s[nt * 32 + L.lane];
+                so_r[0] = so.x; so_r[1] = so.y; so_r[2] = so.z; so_r[3] = so.w;
+            } else {
+                // plain kernel: staging row = delta + 15 for every delta a tile element can have
+                // (-15 .. WB+15), so the address is a per-lane base plus a compile-time constant and
+                // entries outside the dense window (exactly zero) land in rows nobody sums
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    so_r[r] = stage_base + (8 * (r >> 1) - 8 * nt - (r & 1)) * SP + 8 * (r >> 1);
+            }
             float s[4] = {ini.x, ini.y, ini.z, ini.w}, dp[4];
             RowFrag<D> vf;
             if (INTERIOR) {
@@ -507,7 +519,6 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
                 for (int r = 0; r < 4; ++r)
                     if (kb0 + 8 * nt + 2 * tig + (r & 1) < 0) s[r] = kNeg;
             }
-            const int so_r[4] = {so.x, so.y, so.z, so.w};
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 const float p = ex2(fmaf(s[r], c2, r < 2 ? -l2_lo : -l2_hi));
@@ -530,7 +541,7 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
     }
     // ---- sparse taps
     const float ls_lo = L.owner ? l2_lo : 1.0e30f, ls_hi = L.owner ? l2_hi : 1.0e30f;   // p == 0 on lanes without a diagonal entry
-    float* stage_sp = stage_w + nd * SP + g;
+    float* stage_sp = stage_w + (SE ? nd : WB + 31) * SP + g;     // plain kernel: after the WB+31 delta rows
     auto finish = [&](int si, float sd0, float sd1, float dp0, float dp1, float pbv, bool v0, bool v1,
                       const RowFrag<D>& kf0, const RowFrag<D>& kf1) {
         float p0, p1;
@@ -680,9 +691,11 @@ __global__ void se_prep_kernel(const float* __restrict__ scale_embed, const floa
     }
 }
 
-inline size_t dq_smem_bytes(int J, int D, int NT, bool se) {
-    const int JS = se ? (J + 15) / 16 * 16 : J;
-    size_t n = sizeof(float) * ((size_t)(JS + 1) * (se ? kStagePitchSe : kStagePitch) + kWarps * 32);
+inline size_t dq_smem_bytes(int J, int n_sparse, int D, int NT, bool se) {
+    // staging rows: with scale_embed one per tap (rounded up to the MMA shape) plus a dump row;
+    // plain kernel one per delta a tile element can have (8 NT + 15 = WB + 31) plus the sparse taps
+    const int rows = se ? (J + 15) / 16 * 16 + 1 : 8 * NT + 15 + n_sparse;
+    size_t n = sizeof(float) * ((size_t)rows * (se ? kStagePitchSe : kStagePitch) + kWarps * 32);
     if (se) {
         n = (n + 15) / 16 * 16;
         n += (size_t)kWarps * (16 * ((J + 7) / 8 * 8 + 2) + 4) * 4;      // one q.scale_embed tile per warp
@@ -699,12 +712,13 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
     constexpr int SP = StagePitch<SE>::v;
     extern __shared__ __align__(16) float stage[];     // [JS + 1][SP] ds values, then [128] dgain terms, then the scale_embed extras
     __shared__ float4 init_s[SE ? 1 : NT * 32];
-    __shared__ int4 soff_s[NT * 32];
+    __shared__ int4 soff_s[SE ? NT * 32 : 1];          // staging offsets per lane (scale_embed variant only)
     __shared__ int2 tap_s[DSQG_MAX_TAPS];
     const Lane L;
     const int bh = blockIdx.y, h = bh % a.H, N = a.N, J = t.J;
-    const int JS = SE ? (J + 15) / 16 * 16 : J;         // staging rows (row JS is the dump for out-of-band entries)
-    float* dg_s = stage + (JS + 1) * SP;
+    const int JS = SE ? (J + 15) / 16 * 16 : J;         // scale_embed: staging rows (row JS is the dump for out-of-band entries)
+    constexpr int kDeltaRows = WB + 31;                 // plain kernel: one staging row per delta -15 .. WB+15
+    float* dg_s = stage + (SE ? JS + 1 : kDeltaRows + t.n_sparse) * SP;
     SeTables se = {};
     SeBwd sb = {};
     {
@@ -723,7 +737,7 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
                 o[r] = (inband ? delta - d_lo : JS) * SP + i;
             }
             if constexpr (!SE) init_s[e] = make_float4(v[0], v[1], v[2], v[3]);
-            soff_s[e] = make_int4(o[0], o[1], o[2], o[3]);
+            if constexpr (SE) soff_s[e] = make_int4(o[0], o[1], o[2], o[3]);
         }
         for (int si = threadIdx.x; si < t.n_sparse; si += kWarps * 32)
             tap_s[si] = make_int2(t.sparse[si], __float_as_int(a.pos_bias[(t.n_dense + si) * a.H + h] * kLog2e));
@@ -753,7 +767,14 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
     float* stage_w = stage + L.warp * 16;
     float dgrow = 0.f;
     if (g0 >= N) {                                      // no rows: this warp's staging columns (and query rows) are zero
-        for (int e = L.lane; e < J * 16; e += 32) stage_w[(e >> 4) * SP + (e & 15)] = 0.f;
+        if constexpr (SE) {
+            for (int e = L.lane; e < J * 16; e += 32) stage_w[(e >> 4) * SP + (e & 15)] = 0.f;
+        } else {                                        // the rows the column sums read: in-band deltas, then the sparse taps
+            for (int e = L.lane; e < J * 16; e += 32) {
+                const int j = e >> 4;
+                stage_w[(j < t.n_dense ? t.d_lo + j + 15 : kDeltaRows + j - t.n_dense) * SP + (e & 15)] = 0.f;
+            }
+        }
         if constexpr (SE)
             for (int e = L.lane; e < 16 * (2 * D + 16) / 16; e += 32)
                 reinterpret_cast<uint4*>(sb.q_s + (size_t)L.warp * 16 * (2 * D + 16))[e] = make_uint4(0u, 0u, 0u, 0u);
@@ -804,8 +825,9 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
         if (j < J) {
             // pitch 68 puts rows j and j+8 (and the two halves) in the same banks: start each of the
             // four at a different column so that a warp's 32 reads fall into 32 banks
-            const float* row = stage + j * SP + 32 * half;
-            const int rot = ((j >> 3) & 1) + 2 * half;
+            const int jr = SE ? j : (j < t.n_dense ? t.d_lo + j + 15 : kDeltaRows + j - t.n_dense);   // staging row of tap j
+            const float* row = stage + jr * SP + 32 * half;
+            const int rot = ((jr >> 3) & 1) + 2 * half;
             float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
             for (int r = 0; r < 32; r += 4) {
@@ -1136,7 +1158,7 @@ cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stag
             if ((e = cudaGetLastError()) != cudaSuccess) return e;
         }
         auto kern = bwd_dq_mma_kernel<D, WB, T::dq_group, SE ? T::dq_ctas_se : T::dq_ctas, SE>;
-        const size_t smem = dq_smem_bytes(t.J, D, NT, SE);
+        const size_t smem = dq_smem_bytes(t.J, t.n_sparse, D, NT, SE);
         if (smem > 32 * 1024) {        // static shared memory counts against the 48 KB default as well
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
