@@ -151,7 +151,9 @@ class CondMLM(nn.Module):
         for i, blk in enumerate(self.blocks):
             h = blk.norm1(x)
             if i in state["ring_of"]:
-                x = x + blk.attn.decode(h, cache, state["ring_of"][i])
+                # the kernel ahead of the step is this layer's projection, never a writer of the rings
+                # or the write head, so the overlapped launch is allowed
+                x = x + blk.attn.decode(h, cache, state["ring_of"][i], overlap=True)
             else:
                 x = x + blk.attn.decode(h, *state["full"][i], t)
             x = x + blk.ffn(blk.norm2(x))
