@@ -217,7 +217,7 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     T = op_bytes(cfg)
     peak, peak_src = measured_peaks()
     # DRAM bytes (read + write) per launch from the ncu capture summarised in
-    # profiles/dsqg_mma_kernels_cfg1.md and ..._cfg2.md; only known for the workloads that were captured.
+    # profiles/ (cfg1 and cfg2); only known for the workloads that were captured.
     ncu_traffic = {"cfg1": [120.38e6, 197.38e6, 185.12e6], "cfg2": [187.5e6, 296.6e6, 284.3e6]}.get("" if se is not None or strong or args.batch > 0 else args.workload, [None] * 3)
     names = ["dsqg_fwd", "dsqg_bwd_dq", "dsqg_bwd_dkdv"]
     alg = [4 * T, 6 * T, 6 * T]           # per launch: fwd Q,K,V->O ; dq Q,K,V,O,dO->dQ ; dkdv Q,K,V,dO->dK,dV
