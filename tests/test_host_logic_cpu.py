@@ -102,3 +102,20 @@ def test_two_rank_gloo_sharding_and_timing_reduction():
     assert [p.exitcode for p in procs] == [0, 0]
     assert res[0][1:3] == (0, 16) and res[1][1:3] == (16, 32)
     assert all(r[3] == 11.0 and r[4] == 32.0 for r in res)
+
+
+def test_odd_head_widths_are_padded_only_when_the_tensor_core_kernels_take_them():
+    """Host-side choice of the head dimension the kernels are called with (no device access)."""
+    from dwarf_b200 import _lib, ops
+    off43, J43 = _lib.offsets_array(ops.OFFSETS_43)
+    wide = tuple(range(41)) + (128, 384, 1536)
+    offw, Jw = _lib.offsets_array(wide)
+    q = lambda D, dt=torch.bfloat16: torch.zeros(1, 1, 4, D, dtype=dt)
+    assert ops._padded_head_dim(q(80), off43, J43, False) == 96
+    assert ops._padded_head_dim(q(48), off43, J43, False) == 64
+    assert ops._padded_head_dim(q(48), off43, J43, True) == 64       # scale_embed runs on the 64-wide kernels
+    assert ops._padded_head_dim(q(80), off43, J43, True) == 80       # but not on the 96-wide ones
+    assert ops._padded_head_dim(q(80), offw, Jw, False) == 80        # dense window wider than 32
+    assert ops._padded_head_dim(q(80, torch.float32), off43, J43, False) == 80
+    for D in (32, 64, 96, 128):
+        assert ops._padded_head_dim(q(D), off43, J43, False) == D
