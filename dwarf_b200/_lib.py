@@ -24,6 +24,7 @@ _SIGNATURES = {
     "dsqg_version": (c_int, []),
     "dsqg_set_kernel_path": (c_int, [c_int]),
     "dsqg_device_error": (c_int, [c_int]),
+    "dsqg_test_wait_timeout": (c_int, [ctypes.c_longlong, c_void_p]),
     "dsqg_fwd": (c_int, [c_void_p] * 3 + [c_void_p] * 3 + [POINTER(c_int32), c_int] + [c_void_p] * 2
                  + [c_int] * 5 + [c_void_p]),
     "dsqg_bwd_scratch_bytes": (c_size_t, [c_int] * 6),

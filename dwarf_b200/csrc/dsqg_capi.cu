@@ -1,6 +1,7 @@
 // C ABI of libdsqg_b200.so: argument validation on the host, then dispatch to the
 // sm_100a kernels.  Declarations and the reference interfaces they replace are in
-// include/dsqg_b200.h.  Nothing here allocates, throws, or keeps state between calls.
+// include/dsqg_b200.h.  Nothing here allocates or throws; the little state the library keeps
+// between calls (kernel-path knob, error word, built-in scratch) lives in other files.
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -128,8 +129,6 @@ size_t dsqg_bwd_scratch_bytes(int J, int B, int H, int N, int D, int has_scale_e
     // the generic kernels' need (512-row partials) and the tensor-core kernels' need (per-row table,
     // per-tile and per-group partials, prepared tables) is reported
     size_t need = bwd_scratch_need(kMinRowsPerBwdTile, J, B, H, N, D, false);
-    const size_t tma = bwd_scratch_need_tma(J, B, H, N);      // persistent kernels: partials per (CTA, sequence, warp)
-    if (tma > need) need = tma;
     if (!has_scale_embed) return need;
     need += bwd_scratch_need(512, J, B, H, N, D, true);
     const size_t mma_se = bwd_scratch_need_mma_se(J, B, H, N, D);

@@ -76,13 +76,11 @@ cudaError_t launch_fwd_mma(const FwdArgs& a, const Taps& t, cudaStream_t s);
 cudaError_t launch_bwd_mma(const BwdArgs& a, const Taps& t, cudaStream_t s, int stages);
 bool mma_path_supported(int dtype, int D, const Taps& t, bool has_scale_embed);   // backward
 bool mma_fwd_supported(int dtype, int D, const Taps& t, bool has_scale_embed);
-cudaError_t launch_fwd_tma(const FwdArgs& a, const Taps& t, cudaStream_t s);
-bool tma_fwd_supported(int dtype, int D, int N, const Taps& t, bool has_scale_embed);
-cudaError_t read_device_error_fwd_tma(int* value, bool reset);
-cudaError_t launch_bwd_tma(const BwdArgs& a, const Taps& t, cudaStream_t s, int stages);
-bool tma_bwd_supported(int dtype, int D, int N, const Taps& t, bool has_scale_embed);
-size_t bwd_scratch_need_tma(int J, int B, int H, int N);
-cudaError_t read_device_error_bwd_tma(int* value, bool reset);
+// forward with TMA-staged V (dsqg_staged.cu)
+bool staged_supported(int dtype, int D, const Taps& t, bool has_scale_embed);
+cudaError_t launch_fwd_staged(const FwdArgs& a, const Taps& t, cudaStream_t s);
+cudaError_t read_stage_error(int* value, bool reset);
+cudaError_t launch_wait_timeout(long long limit_cycles, int site, cudaStream_t s);
 
 // Backward scratch layout: row statistics (8 bytes per row) | dpos_bias partials | dhead_gain partials | dscale_embed
 // partials, each block rounded up to 256 bytes.  A "tile" is the set of rows whose partial

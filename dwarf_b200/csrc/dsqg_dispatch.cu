@@ -8,22 +8,20 @@
 
 namespace dsqg {
 
-// 0 = automatic, 1 = always the generic kernels, 2 = tensor-core kernels (same as automatic
-// where they apply), 3 = persistent TMA variants wherever they exist.  The TMA variants are not
-// chosen automatically: on B200 they measure 10-50 % slower than the plain tensor-core kernels,
-// which need fewer registers and keep 20-24 warps resident per SM instead of 9-16.
+// 0 = automatic, 1 = always the generic kernels, 2 = the tensor-core kernels (what the automatic
+// choice uses where they apply), 3 = the forward with TMA-staged V wherever it applies
+// (dsqg_staged.cu; not chosen automatically: it measures slower on B200).
 static std::atomic<int> g_path{0};
 
 cudaError_t launch_fwd(const FwdArgs& a, const Taps& t, int dtype, cudaStream_t s) {
     const int path = g_path.load();
-    if (path == 3 && tma_fwd_supported(dtype, a.D, a.N, t, a.scale_embed != nullptr)) return launch_fwd_tma(a, t, s);
+    if (path == 3 && staged_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_staged(a, t, s);
     if (path != 1 && mma_fwd_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_mma(a, t, s);
     return launch_fwd_generic(a, t, dtype, s);
 }
 
 cudaError_t launch_bwd(const BwdArgs& a, const Taps& t, int dtype, cudaStream_t s, int stages) {
     const int path = g_path.load();
-    if (path == 3 && tma_bwd_supported(dtype, a.D, a.N, t, a.scale_embed != nullptr)) return launch_bwd_tma(a, t, s, stages);
     if (path != 1 && mma_path_supported(dtype, a.D, t, a.scale_embed != nullptr))
         return launch_bwd_mma(a, t, s, stages);
     return launch_bwd_generic(a, t, dtype, s, stages);
@@ -39,8 +37,11 @@ extern "C" int dsqg_set_kernel_path(int path) {
 
 extern "C" int dsqg_device_error(int reset) {
     int v = 0;
-    int w = 0;
-    if (dsqg::read_device_error_fwd_tma(&v, reset != 0) != cudaSuccess) return -1;
-    if (dsqg::read_device_error_bwd_tma(&w, reset != 0) != cudaSuccess) return -1;
-    return v ? v : w;
+    if (dsqg::read_stage_error(&v, reset != 0) != cudaSuccess) return -1;
+    return v;
+}
+
+extern "C" int dsqg_test_wait_timeout(long long limit_cycles, void* stream) {
+    if (limit_cycles < 1 || limit_cycles > 2000000000LL) return DSQG_ERR_UNSUPPORTED;
+    return dsqg::launch_wait_timeout(limit_cycles, 0x7e57, static_cast<cudaStream_t>(stream)) == cudaSuccess ? DSQG_OK : DSQG_ERR_CUDA;
 }

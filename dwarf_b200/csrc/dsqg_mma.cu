@@ -17,6 +17,7 @@
 // produces dscale_embed partials per 64-row tile (dS^T.Q, MMA; dse_group_kernel adds groups of
 // eight tiles) and leaves the per-row tile in global memory for the dK/dV kernel.
 #include "dsqg_mma.cuh"
+#include <mutex>
 #include <type_traits>
 
 namespace dsqg {
@@ -1124,6 +1125,23 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t, const int n_reduce, const int
         dkdv_tile<D, WB, false, G, SE>(a, init_s, tap_s, stat_s + L.warp * 16, t.n_sparse, bh, h, m0, L, qsd_w, qoff, nd, Jp);
 }
 
+// Raises a kernel's dynamic shared-memory limit to what this launch needs.  The attribute is set
+// once per kernel and device for the largest size seen so far (`seen` is that kernel's record),
+// not on every launch.
+template <typename K>
+cudaError_t ensure_dynamic_smem(K kernel, size_t bytes, int (&seen)[64]) {
+    if (bytes <= 32 * 1024) return cudaSuccess;        // static shared memory counts against the 48 KB default as well
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && seen[dev] >= (int)bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < 64) seen[dev] = (int)bytes;
+    return e;
+}
+
 template <int D, int WB>
 cudaError_t fwd_launch_mma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
     constexpr int W = FwdTune<D>::warps, rows = 16 * W;
@@ -1131,10 +1149,9 @@ cudaError_t fwd_launch_mma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
     if (a.scale_embed) {
         if constexpr (D <= 64) {
             const size_t smem = se_tables_bytes(t.J, D, (WB + 16) / 8, W, 16);
-            if (smem > 32 * 1024) {        // static shared memory counts against the 48 KB default as well
-                cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<D, WB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                if (e != cudaSuccess) return e;
-            }
+            static int seen[64] = {0};
+            cudaError_t e = ensure_dynamic_smem(fwd_mma_kernel<D, WB, true>, smem, seen);
+            if (e != cudaSuccess) return e;
             fwd_mma_kernel<D, WB, true><<<grid, W * 32, smem, s>>>(a, t);
         } else {
             return cudaErrorInvalidValue;
@@ -1159,10 +1176,8 @@ cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stag
         }
         auto kern = bwd_dq_mma_kernel<D, WB, T::dq_group, SE ? T::dq_ctas_se : T::dq_ctas, SE>;
         const size_t smem = dq_smem_bytes(t.J, t.n_sparse, D, NT, SE);
-        if (smem > 32 * 1024) {        // static shared memory counts against the 48 KB default as well
-            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return e;
-        }
+        static int seen[64] = {0};
+        if ((e = ensure_dynamic_smem(kern, smem, seen)) != cudaSuccess) return e;
         kern<<<grid, kWarps * 32, smem, s>>>(a, t);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
         if constexpr (SE) {
@@ -1179,10 +1194,8 @@ cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stag
     if (stages & DSQG_BWD_STAGE_DKDV) {
         auto kern = bwd_dkdv_mma_kernel<D, WB, T::dkdv_group, T::dkdv_ctas, SE>;
         const size_t smem = dkdv_smem_bytes(t.n_dense, WB, SE);
-        if (smem > 32 * 1024) {        // static shared memory counts against the 48 KB default as well
-            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return e;
-        }
+        static int seen[64] = {0};
+        if ((e = ensure_dynamic_smem(kern, smem, seen)) != cudaSuccess) return e;
         kern<<<grid, kWarps * 32, smem, s>>>(a, t, fuse ? n_out : 0, fuse ? (int)((long long)grid.x * grid.y / n_out) : 1);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }

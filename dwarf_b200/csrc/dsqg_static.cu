@@ -21,7 +21,10 @@ constexpr int kMaxDevices = 64;
 std::mutex g_setup_mutex;
 void* g_scratch_addr[kMaxDevices] = {nullptr};   // per device, filled on that device's first call
 
-// Address of the current device's copy of the array (looked up once per device).
+// Address of the current device's copy of the array (looked up once per device and kept for
+// the life of the process: the entry point assumes the device's primary context and that the
+// caller never calls cudaDeviceReset; a host that binds another context of the same device, or
+// resets it, would be handed a stale address).
 cudaError_t static_scratch(void** ptr) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

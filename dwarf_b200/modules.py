@@ -52,7 +52,7 @@ class _DSQGAttentionBase(nn.Module):
     """qkv projection -> DSQG op -> sigmoid gate -> output projection."""
 
     def __init__(self, embedding_dim, num_heads, seq_len=2048, offsets=None, dropout=0.1,
-                 gate_bias=2.0, with_scale_embed=False, with_if_gain=False):
+                 gate_bias=2.0, with_scale_embed=False, with_if_gain=False, offsets_in_state_dict=True):
         super().__init__()
         if embedding_dim % num_heads:
             raise ValueError("embedding_dim must be divisible by num_heads")
@@ -60,7 +60,9 @@ class _DSQGAttentionBase(nn.Module):
         self.head_dim = embedding_dim // num_heads
         self.seq_len = seq_len
         offsets = list(ALL_OFFSETS if offsets is None else offsets)
-        self.register_buffer("offsets", torch.tensor(offsets, dtype=torch.long))
+        # the kernel-file modules of the reference keep `offsets` in their state dict
+        # (kernels/dsqg_attention_v2.py:448, kernels/dsqg_attention_v3.py:488); its condU script module does not
+        self.register_buffer("offsets", torch.tensor(offsets, dtype=torch.long), persistent=offsets_in_state_dict)
         self._offsets = tuple(offsets)
         self.n_offsets = len(offsets)
         self.qkv_proj = nn.Linear(embedding_dim, 3 * embedding_dim, bias=True)
@@ -148,8 +150,10 @@ class DSQGAttentionV3(_DSQGAttentionBase):
 
 
 class DSQGAttentionQW(_DSQGAttentionBase):
-    """condU attention with the per-head IF gain; the gain multiply runs inside the kernel."""
+    """condU attention with the per-head IF gain; the gain multiply runs inside the kernel.
+    As in the reference script (train/train_2048_condU.py:139-166) the state dict holds no
+    `offsets` entry, so its checkpoints load with strict=True."""
 
     def __init__(self, embedding_dim, num_heads, seq_len=2048, dropout=0.1, offsets=None):
         super().__init__(embedding_dim, num_heads, seq_len, offsets, dropout, gate_bias=0.0,
-                         with_scale_embed=True, with_if_gain=True)
+                         with_scale_embed=True, with_if_gain=True, offsets_in_state_dict=False)

@@ -16,8 +16,11 @@
  *   - offsets: HOST pointer to J int32 values, strictly ascending, >= 0.  The leading run
  *     of consecutive integers is treated as the dense window, the rest as sparse taps.
  *   - stream: a cudaStream_t passed as void* (NULL = legacy default stream).
- *   - The caller owns every buffer; the library allocates nothing and keeps no state
- *     between calls.  The caller makes the device current (cudaSetDevice) before calling.
+ *   - The caller owns every buffer; the library allocates nothing.  The only state it keeps
+ *     between calls is named where it is declared: the kernel-path knob
+ *     (dsqg_set_kernel_path), the device error word (dsqg_device_error), the built-in scratch
+ *     of dsqg_bwd_static with its per-device address cache, and per-kernel "attribute set"
+ *     flags.  The caller makes the device current (cudaSetDevice) before calling.
  *   - Every function returns DSQG_OK (0) or a negative dsqg_status; nothing throws, traps
  *     or aborts.  Argument errors are detected on the host before any launch.
  *   - D must be a multiple of 8, 8 <= D <= 128; J <= DSQG_MAX_TAPS.
@@ -60,16 +63,22 @@ int dsqg_version(void);
 
 /* Testing knob with no counterpart in the reference: 0 = choose kernels automatically
  * (default), 1 = always use the generic CUDA-core kernels, 2 = the tensor-core kernels (what the
- * automatic choice uses where they apply), 3 = the persistent TMA-fed variants wherever one
- * exists (not chosen automatically: they measure slower on B200).  Process-wide. */
+ * automatic choice uses where they apply), 3 = the forward with TMA-staged V wherever it applies
+ * (not chosen automatically: it measures slower on B200).  Process-wide state. */
 int dsqg_set_kernel_path(int path);
 
 /* Device-side error word of the current device (no counterpart in the reference).  The
- * persistent kernels bound every wait on a shared-memory barrier; a wait that runs out
- * records (kernel id << 8 | wait site) here and the kernel returns with unspecified output
- * instead of hanging.  0 = no error, -1 = the word could not be read.  Synchronises the
- * device.  reset != 0 clears the word after reading. */
+ * kernels that wait on shared-memory barriers for the copy engine (kernel path 3) bound every
+ * such wait; a wait that runs out records its site id here and the kernel returns with
+ * unspecified output instead of hanging.  0 = no error, -1 = the word could not be read.
+ * Synchronises the device.  reset != 0 clears the word after reading. */
 int dsqg_device_error(int reset);
+
+/* Test hook for the bounded wait (no counterpart in the reference): launches one thread that
+ * waits, for at most limit_cycles SM cycles (1 .. 2e9), on a barrier nothing signals.  The wait
+ * gives up, dsqg_device_error() then reports site 0x7e57, and the kernel returns: nothing is
+ * in flight, nothing hangs or faults. */
+int dsqg_test_wait_timeout(long long limit_cycles, void* stream);
 
 /* Forward.
  * Replaces: _DSQGFn.forward / _DSQGFnV3.forward + the _fwd/_fwd_v3 kernels
@@ -118,6 +127,8 @@ int dsqg_bwd(const void* q, const void* k, const void* v,
  *     DSQG_ERR_STATIC_SCRATCH_EXCEEDED before anything is launched.
  *   - The first call on each device looks up that device's copy of the array (the device must
  *     be current, as for every entry point); make that first call outside any stream capture.
+ *     The address is kept until the process exits: use the device's primary context (what the
+ *     CUDA runtime gives you) and do not call cudaDeviceReset while the library is loaded.
  *   - All calls on a device share the one array and it keeps whatever the last call left; the
  *     kernels overwrite every word they later read, so nothing has to be cleared.  Two calls
  *     that may run on the GPU at the same time (different streams) race on it: serialise them. */

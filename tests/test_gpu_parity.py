@@ -56,9 +56,9 @@ REF_SHAPES = [(1, 8, 64, 32), (2, 8, 512, 32), (2, 8, 2047, 32), (1, 4, 2047, 80
 
 @pytest.fixture(params=["auto", "generic", "mma", "tma"])
 def kernel_path(request):
-    """Runs a test with the automatic kernel choice (persistent TMA / tensor-core kernels where
-    they apply), with the generic CUDA-core kernels forced, with the plain tensor-core
-    kernels (no TMA variants), and with every persistent TMA variant (forward and backward)."""
+    """Runs a test with the automatic kernel choice, with the generic CUDA-core kernels forced, with
+    the tensor-core kernels, and with the forward that stages V through the copy engine (its
+    bounded waits must not have given up)."""
     lib = _lib.load()
     lib.dsqg_set_kernel_path({"auto": 0, "generic": 1, "mma": 2, "tma": 3}[request.param])
     yield request.param
@@ -413,27 +413,122 @@ def test_gpu_argument_errors_raise_with_status():
 
 
 # ------------------------------------------------------------------ full benchmark sizes
+# Tensors that meet the benchmark's plain bound (|x - ref| <= 2e-2, no term relative to the value) on the
+# whole batch.  dv at cfg1 is the one exception: its largest values are near 4.5, where one bf16 rounding
+# step of the stored result is 0.031, and its largest error is 0.0215; it keeps the bound that adds the
+# rounding of the stored value (2e-2 + 2^-8 |ref|).
+PLAIN_2E2 = {"cfg1": ("out", "dq", "dk"), "cfg2": ("out", "dq", "dk", "dv"), "cfg2_4k": ("out", "dq", "dk", "dv")}
+
+
 @pytest.mark.parametrize("cfg_name", ["cfg1", "cfg2", "cfg2_4k"])
-def test_full_size_configs_vs_c_oracle_on_batch_slices(cfg_name):
-    """Full benchmark shape on the GPU; the CPU oracle checks the first and last batch
-    entries (every (b,h) problem is independent, so a slice is a complete check of the rows
-    it covers), plus size-independent properties on everything."""
+def test_full_size_configs_vs_c_oracle_whole_batch(cfg_name, record_property):
+    """Full benchmark shape on the GPU against the (threaded, double-accumulating) C oracle on every
+    batch entry: out, dq, dk, dv element-wise, dpos_bias and dhead_gain (sums over all B*N rows of a
+    head) to 1 % of their largest entry.  The largest absolute error of every tensor is printed and
+    recorded."""
     cfg = synth.OP_CONFIGS[cfg_name]
     x = synth.make_op_inputs(cfg)
     r = cuda_fwd_bwd(x["q"], x["k"], x["v"], x["pos_bias"], x["dout"], None, x["head_gain"],
                      cfg.offsets, cfg.dtype)
+    f = lambda t: t.float()
+    ref = oracle_fwd_bwd(f(x["q"]), f(x["k"]), f(x["v"]), x["pos_bias"], f(x["dout"]), None,
+                         x["head_gain"], cfg.offsets)
+    for nm in ("out", "dq", "dk", "dv", "dpb", "dgain"):
+        err = (r[nm].double() - ref[nm].double()).abs().max().item()
+        record_property(f"{cfg_name}_{nm}_max_abs_err", err)
+        print(f"{cfg_name} {nm}: max abs err {err:.4g} (|ref| max {ref[nm].abs().max().item():.4g})")
     for nm in ("out", "dq", "dk", "dv"):
         assert torch.isfinite(r[nm]).all()
-    for b in (0, cfg.B - 1):
-        sl = slice(b, b + 1)
-        f = lambda t: t[sl].float()
-        ref = oracle_fwd_bwd(f(x["q"]), f(x["k"]), f(x["v"]), x["pos_bias"], f(x["dout"]), None,
-                             x["head_gain"], cfg.offsets)
-        for nm in ("out", "dq", "dk", "dv"):
-            assert_bf16_close(r[nm][sl], ref[nm], f"{nm}[b={b}]")
+        if nm in PLAIN_2E2[cfg_name]:
+            err = (r[nm].double() - ref[nm].double()).abs().max().item()
+            assert err <= BF16_ABS_TOL, f"{nm}: max abs err {err:.4g} > {BF16_ABS_TOL}"
+        else:
+            assert_bf16_close(r[nm], ref[nm], nm)
+    assert_param_grad_close(r["dpb"], ref["dpb"], "dpb", 1e-2, abs_floor=0.0)
+    assert_param_grad_close(r["dgain"], ref["dgain"], "dgain", 1e-3, abs_floor=0.0)
     # row 0 of every (b,h) attends only to itself: out[0] = gain * v[0]
     want = x["v"][:, :, 0].float() * x["head_gain"].view(1, cfg.H, 1)
     assert (r["out"][:, :, 0] - want).abs().max().item() <= BF16_ABS_TOL
-    # sum_j dpos_bias[j,h] ~ 0: softmax gradients sum to zero over the taps of every row
-    # (up to the bf16 rounding of the saved output that enters delta = sum_d dout*out)
-    assert (r["dpb"].sum(0).abs() <= 1e-2 * r["dpb"].abs().sum(0) + 1.0).all()
+
+
+# ------------------------------------------------------------------ gather index and causal mask, read directly
+@pytest.mark.parametrize("offsets", [O.OFFSETS_43, O.OFFSETS_44, O.OFFSETS_45], ids=["J43", "J44", "J45"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("coding", ["mod", "div"])
+def test_gather_index_and_mask_are_exact(offsets, dtype, coding):
+    """q = 0 and pos_bias = 0 make every valid tap of a row weigh 1/count.  With V rows one-hot in
+    `n mod 128` (first pass) and in `n div 128` (second pass; D = 128) the output row n is a histogram of
+    the value rows the kernel gathered: it must be non-zero exactly at the codes of the rows n - delta_j
+    with n - delta_j >= 0 (the gather index and mask of kernels/dsqg_attention_v2.py:491,495), exactly zero
+    elsewhere, and multiplicity / count where it is non-zero."""
+    B, H, N, D = 1, 2, 1800, 128
+    n = torch.arange(N)
+    code = (n % 128) if coding == "mod" else (n // 128)
+    v = torch.zeros(B, H, N, D)
+    v[:, :, n, code] = 1.0
+    q = torch.zeros(B, H, N, D)
+    k = (torch.randn(B, H, N, D, generator=torch.Generator().manual_seed(1)) * 0.5).bfloat16().float()   # irrelevant: q = 0
+    pb = torch.zeros(len(offsets), H)
+    r = cuda_fwd_bwd(q, k, v, pb, None, None, None, offsets, dtype)["out"]
+    off = torch.tensor(offsets)
+    src = n[:, None] - off[None, :]                          # [N, J] gathered row index
+    valid = src >= 0
+    hist = torch.zeros(N, D)
+    rows = n[:, None].expand_as(src)[valid]
+    hist.index_put_((rows, code[src[valid]]), torch.ones(int(valid.sum())), accumulate=True)
+    count = valid.sum(1).float()
+    want = hist / count[:, None]
+    for h in range(H):
+        got = r[0, h]
+        assert torch.equal(got != 0, hist != 0), "the set of gathered rows differs from {n - delta_j >= 0}"
+        tol = 1e-6 if dtype == torch.float32 else 2.0 ** -7          # one rounding step of the stored bf16 value
+        assert ((got - want).abs() <= tol * want).all()
+
+
+def test_module_kv_inject_matches_oracle():
+    """K/V injection hook of the condU attention (train/train_2048_condU.py:178-181): k += k_delta,
+    v += v_delta before the op.  Module output and the gradients that reach the injected tensors
+    against the same module math evaluated with the oracle."""
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(3)
+    E, Hh, N = 64, 2, 90
+    m = dwarf_b200.DSQGAttentionQW(E, Hh, dropout=0.0, offsets=O.OFFSETS_43).eval()
+    with torch.no_grad():
+        m.scale_embed.normal_(0, 0.05); m.if_gain.uniform_(0.8, 1.2)
+    x = torch.randn(1, N, E)
+    kd = (torch.randn(1, Hh, N, E // Hh) * 0.3).requires_grad_(True)
+    vd = (torch.randn(1, Hh, N, E // Hh) * 0.3).requires_grad_(True)
+    # oracle side: same projections, injection, bf16 rounding of q, k, v as the module does
+    qkv = m.qkv_proj(x)
+    q, k, v = (t.view(1, N, Hh, E // Hh).permute(0, 2, 1, 3) for t in qkv.split(E, -1))
+    rnd = lambda t: t + (t.bfloat16().float() - t).detach()          # value rounding, identity gradient
+    o = O.dsqg_reference(rnd(q), rnd(k + kd), rnd(v + vd), m.pos_bias, m.scale_embed, m.if_gain, O.OFFSETS_43)
+    ref = m.out_proj(o.permute(0, 2, 1, 3).reshape(1, N, E) * torch.sigmoid(m.gate_proj(x)))
+    ref.sum().backward()
+    ref_gk, ref_gv = kd.grad.clone(), vd.grad.clone()
+    md = m.to(dev)
+    kd2 = kd.detach().to(dev).requires_grad_(True)
+    vd2 = vd.detach().to(dev).requires_grad_(True)
+    got = md(x.to(dev), kv_inject=(kd2, vd2))
+    got.sum().backward()
+    assert (got.detach().cpu() - ref.detach()).abs().max().item() < 2e-2
+    assert (kd2.grad.cpu() - ref_gk).abs().max().item() < 2e-2
+    assert (vd2.grad.cpu() - ref_gv).abs().max().item() < 2e-2
+    without = md(x.to(dev))
+    assert (without - got).abs().max().item() > 1e-3             # the injection is not a no-op
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A wait on a barrier nothing signals runs out after its cycle limit: the kernel returns, the
+    error word names the wait site, reading with reset clears it, and the context stays usable."""
+    lib = _lib.load()
+    assert lib.dsqg_device_error(1) >= 0
+    assert lib.dsqg_device_error(0) == 0
+    _lib.check(lib.dsqg_test_wait_timeout(20000, torch.cuda.current_stream().cuda_stream), "wait")
+    torch.cuda.synchronize()
+    assert lib.dsqg_device_error(0) == 0x7e57
+    assert lib.dsqg_device_error(1) == 0x7e57
+    assert lib.dsqg_device_error(0) == 0
+    assert lib.dsqg_test_wait_timeout(0, None) == -8
+    q = torch.zeros(1, 2, 16, 32, device="cuda:0", dtype=torch.bfloat16)
+    assert torch.isfinite(dwarf_b200.dsqg_attention(q, q, q, torch.zeros(44, 2, device="cuda:0")).float()).all()

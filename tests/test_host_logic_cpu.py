@@ -39,6 +39,25 @@ def test_module_surface_matches_reference_names():
     assert tuple(m43.pos_bias.shape) == (43, 2)
 
 
+def test_reference_shaped_state_dicts_load_strictly():
+    """Key sets of the reference's modules: kernels/dsqg_attention_v2.py:434-456 (N_Fused),
+    kernels/dsqg_attention_v3.py:463-500 (V3), train/train_2048_condU.py:139-166 (QW: no `offsets`)."""
+    E, H, J = 64, 2, 44
+    lin = lambda name, o, i: {f"{name}.weight": torch.zeros(o, i), f"{name}.bias": torch.zeros(o)}
+    common = {**lin("qkv_proj", 3 * E, E), **lin("out_proj", E, E), **lin("gate_proj", E, E),
+              "pos_bias": torch.zeros(J, H)}
+    offs = {"offsets": torch.tensor(dwarf_b200.ALL_OFFSETS, dtype=torch.long)}
+    se = {"scale_embed": torch.zeros(J, E // H)}
+    cases = [(dwarf_b200.DSQGAttentionN_Fused, {**common, **offs}),
+             (dwarf_b200.DSQGAttentionV3, {**common, **offs, **se}),
+             (dwarf_b200.DSQGAttentionQW, {**common, **se, "if_gain": torch.ones(H)})]
+    for cls, sd in cases:
+        m = cls(E, H)
+        assert set(m.state_dict()) == set(sd), cls.__name__
+        m.load_state_dict(sd, strict=True)
+        assert m.offsets.tolist() == list(dwarf_b200.ALL_OFFSETS)
+
+
 def test_compat_shims_export_reference_names():
     sys.path.insert(0, os.path.join(ROOT, "dwarf_b200", "compat"))
     try:
