@@ -106,86 +106,168 @@ def op_bytes(cfg):
     return cfg.B * cfg.H * cfg.N * cfg.D * esz          # T: one [B,H,N,D] tensor
 
 
+class OpProblem:
+    """Device-resident tensors of one op workload and direct C-ABI calls on them."""
+
+    def __init__(self, cfg, dev, x, scale_embed=False):
+        import dwarf_b200  # noqa: F401  (loads the library)
+        from dwarf_b200 import _lib
+        self.lib, self._lib = _lib.load(), _lib
+        self.cfg, self.dev = cfg, dev
+        self.host = {nm: x[nm].pin_memory() for nm in ("q", "k", "v", "dout")}
+        self.q, self.k, self.v, self.dout = (self.host[nm].to(dev, non_blocking=True) for nm in ("q", "k", "v", "dout"))
+        self.pb = x["pos_bias"].to(dev); self.gain = x["head_gain"].to(dev)
+        B, H, N, D = cfg.B, cfg.H, cfg.N, cfg.D
+        self.off, self.J = _lib.offsets_array(cfg.offsets)
+        J = self.J
+        self.out = torch.empty_like(self.q); self.lse = torch.empty(B, H, N, device=dev)
+        self.dq, self.dk, self.dv = (torch.empty_like(self.q) for _ in range(3))
+        self.dpb = torch.empty(J, H, device=dev); self.dg = torch.empty(H, device=dev)
+        self.se = (torch.randn(J, D, generator=torch.Generator().manual_seed(1234)) * 0.05).to(dev) if scale_embed else None
+        self.dse = None if self.se is None else torch.empty(J, D, device=dev)
+        self.nbytes = self.lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, int(self.se is not None))
+        self.scratch = torch.empty(self.nbytes, dtype=torch.uint8, device=dev)
+        self.stream = torch.cuda.current_stream()
+        self.dt = 0 if cfg.dtype == torch.bfloat16 else 1
+
+    def fwd(self):
+        c = self.cfg
+        self._lib.check(self.lib.dsqg_fwd(self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.pb.data_ptr(),
+                                          None if self.se is None else self.se.data_ptr(), self.gain.data_ptr(),
+                                          self.off, self.J, self.out.data_ptr(), self.lse.data_ptr(),
+                                          c.B, c.H, c.N, c.D, self.dt, self.stream.cuda_stream), "dsqg_fwd")
+
+    def bwd(self, stages):
+        c = self.cfg
+        self._lib.check(self.lib.dsqg_bwd_stages(
+            self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.pb.data_ptr(),
+            None if self.se is None else self.se.data_ptr(), self.gain.data_ptr(), self.off, self.J,
+            self.out.data_ptr(), self.lse.data_ptr(), self.dout.data_ptr(), self.dq.data_ptr(), self.dk.data_ptr(),
+            self.dv.data_ptr(), self.dpb.data_ptr(), None if self.dse is None else self.dse.data_ptr(),
+            self.dg.data_ptr(), self.scratch.data_ptr(), self.nbytes, c.B, c.H, c.N, c.D, self.dt,
+            self.stream.cuda_stream, stages), "dsqg_bwd_stages")
+
+    def timed(self, steps, warmup, world):
+        """W warm-up steps, then exactly `steps` timed steps (CUDA events on the launching stream around
+        every kernel, barrier + synchronize on both sides).  Returns (ms per step, MAX over ranks; this
+        rank's ms per kernel; wall ms; whether L2 was flushed between steps)."""
+        from dwarf_b200 import dist as ddist
+        for _ in range(warmup):
+            self.fwd(); self.bwd(1); self.bwd(6)
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
+        # A step touches 12 T bytes; when that does not clearly exceed the 126 MB L2 (small per-GPU
+        # batches, e.g. --scaling strong at 8 GPUs) a 256 MB buffer is overwritten between steps and
+        # the step time is the sum of the kernels' event intervals instead of the whole span.
+        flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=self.dev) if 12 * op_bytes(self.cfg) < (256 << 20) else None
+        stream = self.stream
+        ddist.barrier(); torch.cuda.synchronize()
+        t_wall = time.perf_counter()
+        for i in range(steps):
+            if flush_buf is not None:
+                flush_buf.fill_(i & 0xff)
+            ev[i][0].record(stream); self.fwd()
+            ev[i][1].record(stream); self.bwd(1)
+            ev[i][2].record(stream); self.bwd(6)       # dK/dV kernel; its first CTAs also reduce dpos_bias / dhead_gain
+            ev[i][3].record(stream)
+        torch.cuda.synchronize(); ddist.barrier()
+        wall_ms = (time.perf_counter() - t_wall) * 1e3
+        total_ms = ev[0][0].elapsed_time(ev[-1][3]) if flush_buf is None else \
+            sum(ev[i][0].elapsed_time(ev[i][3]) for i in range(steps))
+        kern_ms = [sum(ev[i][s].elapsed_time(ev[i][s + 1]) for i in range(steps)) / steps for s in range(3)]
+        total_ms = ddist.max_over_ranks(total_ms, self.dev if world > 1 else "cpu")
+        return total_ms / steps, kern_ms, wall_ms, flush_buf is not None
+
+
+def profiled_traffic(workload):
+    """DRAM bytes (read + write) per launch of the three default kernels, from the table in
+    profiles/dram_traffic.md (ncu captures of the named kernel instantiations).  {} when the
+    workload was not captured."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.md")
+    res = {}
+    if not os.path.exists(path):
+        return res
+    with open(path) as f:
+        for line in f:
+            cells = [c.strip() for c in line.strip().strip("|").split("|")]
+            if len(cells) >= 4 and cells[0] == workload:
+                try:
+                    res[cells[1]] = {"kernel": cells[2], "bytes": float(cells[3]) * 1e6}
+                except ValueError:
+                    pass
+    return res
+
+
+def small_op_line(cfg, dev, world, steps, warmup, x=None):
+    """ms/step, tokens/s and roofline fraction of one more op workload (device-resident, fewer steps)."""
+    from dwarf_b200 import synth
+    prob = OpProblem(cfg, dev, synth.make_op_inputs(cfg) if x is None else x)
+    ms, kern_ms, _, flushed = prob.timed(steps, warmup, world)
+    peak, _ = measured_peaks()
+    T = op_bytes(cfg)
+    del prob
+    torch.cuda.empty_cache()
+    return {"workload": cfg.name, "ms_per_step": ms, "tokens_per_s": cfg.B * cfg.N * world / (ms * 1e-3), "steps": steps,
+            "kernels_ms": {"dsqg_fwd": kern_ms[0], "dsqg_bwd_dq": kern_ms[1], "dsqg_bwd_dkdv": kern_ms[2]},
+            "frac": 12 * T / (ms * 1e-3) / 1e9 / peak, "l2_flushed": flushed}
+
+
+def api_line(cfg, dev, world, steps, warmup, x):
+    """fwd+bwd through the operator a reference script calls (dsqg_attention -> DSQGFunction, the
+    replacement of kernels/dsqg_attention_v3.py:445-456): device-resident tensors, result tensors
+    and scratch allocated by the autograd Function on every call."""
+    import dwarf_b200
+    from dwarf_b200 import dist as ddist
+    q, k, v = (x[nm].to(dev).requires_grad_(True) for nm in ("q", "k", "v"))
+    dout = x["dout"].to(dev)
+    pb = x["pos_bias"].to(dev).requires_grad_(True); gain = x["head_gain"].to(dev).requires_grad_(True)
+
+    def step():
+        out = dwarf_b200.dsqg_attention(q, k, v, pb, gain, None, cfg.offsets)
+        out.backward(dout)
+        q.grad = k.grad = v.grad = pb.grad = gain.grad = None
+    for _ in range(warmup):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream = torch.cuda.current_stream()
+    ddist.barrier(); torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize(); ddist.barrier()
+    ms = ddist.max_over_ranks(e0.elapsed_time(e1), dev if world > 1 else "cpu") / steps
+    peak, _ = measured_peaks()
+    return {"entry": "dwarf_b200.dsqg_attention (autograd Function over the C ABI)", "workload": cfg.name,
+            "ms_per_step": ms, "tokens_per_s": cfg.B * cfg.N * world / (ms * 1e-3), "steps": steps,
+            "frac": 12 * op_bytes(cfg) / (ms * 1e-3) / 1e9 / peak}
+
+
 def run_op_workload(args, cfg, rank, local_rank, world):
     import dwarf_b200
     from dwarf_b200 import _lib, dist as ddist, synth
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    lib = _lib.load()
     if args.batch > 0:                                  # a smaller case of the same workload (e.g. for an ncu capture)
         import dataclasses
         cfg = dataclasses.replace(cfg, B=args.batch, name=cfg.name.replace(f"B{cfg.B} ", f"B{args.batch} "))
     x = synth.make_op_inputs(cfg)                       # CPU, seeded
+    x_full, cfg_full = x, cfg
     strong = args.scaling == "strong" and world > 1
     global_B = cfg.B
     if strong:                                          # fixed problem: this rank's slice of the batch
-        import dataclasses
-        b0, b1 = ddist.shard_range(cfg.B, rank, world)
-        if b1 <= b0:
-            raise SystemExit(f"--scaling strong: batch {cfg.B} has no entry for rank {rank} of {world}")
-        for nm in ("q", "k", "v", "dout"):
-            x[nm] = x[nm][b0:b1].contiguous()
-        cfg = dataclasses.replace(cfg, B=b1 - b0)
-    host = {nm: x[nm].pin_memory() for nm in ("q", "k", "v", "dout")}
-    q, k, v, dout = (host[nm].to(dev, non_blocking=True) for nm in ("q", "k", "v", "dout"))
-    pb = x["pos_bias"].to(dev); gain = x["head_gain"].to(dev)
+        x, cfg = shard_inputs(x, cfg, rank, world)
+    prob = OpProblem(cfg, dev, x, args.scale_embed)
+    host, q, pb, gain, se = prob.host, prob.q, prob.pb, prob.gain, prob.se
     B, H, N, D = cfg.B, cfg.H, cfg.N, cfg.D
-    off, J = _lib.offsets_array(cfg.offsets)
-    out = torch.empty_like(q); lse = torch.empty(B, H, N, device=dev)
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
-    dpb = torch.empty(J, H, device=dev); dg = torch.empty(H, device=dev)
-    se = None
-    if args.scale_embed:
-        se = (torch.randn(J, D, generator=torch.Generator().manual_seed(1234)) * 0.05).to(dev)
-    sep = None if se is None else se.data_ptr()
-    dse = None if se is None else torch.empty(J, D, device=dev)
-    nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, int(se is not None))
-    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-    stream = torch.cuda.current_stream()
-    sp = stream.cuda_stream
-    dt = 0 if cfg.dtype == torch.bfloat16 else 1
-
-    def fwd():
-        _lib.check(lib.dsqg_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), sep, gain.data_ptr(),
-                                off, J, out.data_ptr(), lse.data_ptr(), B, H, N, D, dt, sp), "dsqg_fwd")
-
-    def bwd(stages):
-        _lib.check(lib.dsqg_bwd_stages(q.data_ptr(), k.data_ptr(), v.data_ptr(), pb.data_ptr(), sep,
-                                       gain.data_ptr(), off, J, out.data_ptr(), lse.data_ptr(), dout.data_ptr(),
-                                       dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dpb.data_ptr(),
-                                       None if dse is None else dse.data_ptr(),
-                                       dg.data_ptr(), scratch.data_ptr(), nbytes, B, H, N, D, dt, sp, stages),
-                   "dsqg_bwd_stages")
+    stream = prob.stream
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
 
     # ---- device-resident timing: W warm-up steps, then exactly K timed steps -------------
-    for _ in range(args.warmup):
-        fwd(); bwd(1); bwd(6)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
-    # A step touches 12 T bytes; when that does not clearly exceed the 126 MB L2 (small per-GPU
-    # batches, e.g. --scaling strong at 8 GPUs) a 256 MB buffer is overwritten between steps and
-    # the step time is the sum of the kernels' event intervals instead of the whole span.
-    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if 12 * op_bytes(cfg) < (256 << 20) else None
-    ddist.barrier(); torch.cuda.synchronize()
-    t_wall = time.perf_counter()
-    for i in range(args.steps):
-        if flush_buf is not None:
-            flush_buf.fill_(i & 0xff)
-        ev[i][0].record(stream); fwd()
-        ev[i][1].record(stream); bwd(1)
-        ev[i][2].record(stream); bwd(6)       # dK/dV kernel; its first CTAs also reduce dpos_bias / dhead_gain
-        ev[i][3].record(stream)
-    torch.cuda.synchronize(); ddist.barrier()
-    wall_ms = (time.perf_counter() - t_wall) * 1e3
-    total_ms = ev[0][0].elapsed_time(ev[-1][3]) if flush_buf is None else \
-        sum(ev[i][0].elapsed_time(ev[i][3]) for i in range(args.steps))
-    kern_ms = [sum(ev[i][s].elapsed_time(ev[i][s + 1]) for i in range(args.steps)) / args.steps for s in range(3)]
-    total_ms = ddist.max_over_ranks(total_ms, dev if world > 1 else "cpu")
-    ms_per_step = total_ms / args.steps
+    ms_per_step, kern_ms, wall_ms, flushed = prob.timed(args.steps, args.warmup, world)
     tokens_per_step = global_B * N if strong else B * N * world       # what all ranks processed
     value = tokens_per_step / (ms_per_step * 1e-3)
 
@@ -216,10 +298,13 @@ def run_op_workload(args, cfg, rank, local_rank, world):
 
     T = op_bytes(cfg)
     peak, peak_src = measured_peaks()
-    # DRAM bytes (read + write) per launch from the ncu capture summarised in
-    # profiles/ (cfg1 and cfg2); only known for the workloads that were captured.
-    ncu_traffic = {"cfg1": [120.38e6, 197.38e6, 185.12e6], "cfg2": [187.5e6, 296.6e6, 284.3e6]}.get("" if se is not None or strong or args.batch > 0 else args.workload, [None] * 3)
+    # DRAM bytes (read + write) per launch from the ncu captures listed in profiles/dram_traffic.md,
+    # reported together with the kernel instantiation they were taken on; only known for the
+    # workloads that were captured (full batch, automatic kernel choice, no scale_embed).
     names = ["dsqg_fwd", "dsqg_bwd_dq", "dsqg_bwd_dkdv"]
+    prof = profiled_traffic("" if se is not None or strong or args.batch > 0 or args.kernel_path else args.workload)
+    ncu_traffic = [prof.get(nm, {}).get("bytes") for nm in names]
+    ncu_kernel = [prof.get(nm, {}).get("kernel") for nm in names]
     alg = [4 * T, 6 * T, 6 * T]           # per launch: fwd Q,K,V->O ; dq Q,K,V,O,dO->dQ ; dkdv Q,K,V,dO->dK,dV
     top = max(range(3), key=lambda s: kern_ms[s])
     achieved = alg[top] / (kern_ms[top] * 1e-3) / 1e9
@@ -230,7 +315,7 @@ def run_op_workload(args, cfg, rank, local_rank, world):
         "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
         "dtype": "bf16" if cfg.dtype == torch.bfloat16 else "f32", "data": "synthetic",
         "config": {"workload": cfg.name + (" +scale_embed" if se is not None else ""), "tokens_per_step_per_gpu": B * N,
-                   "l2": (f"inputs+outputs per step ({12 * T / 1e6:.0f} MB) exceed the 126 MB L2; no flush" if flush_buf is None
+                   "l2": (f"inputs+outputs per step ({12 * T / 1e6:.0f} MB) exceed the 126 MB L2; no flush" if not flushed
                           else f"inputs+outputs per step are {12 * T / 1e6:.0f} MB: L2 flushed by a 256 MB write between steps"),
                    "parallelism": (f"batch of {global_B} split over {world} GPUs, no collective" if strong
                                    else f"batch replicated x{world}, no collective")},
@@ -239,19 +324,62 @@ def run_op_workload(args, cfg, rank, local_rank, world):
                 "steps": e2e_steps},
         "gpu_launches": ((3 if args.kernel_path in (0, 2) else 4) + (2 if se is not None and args.kernel_path in (0, 2) else 0)) * args.steps,   # other paths reduce in a 4th kernel
         "roofline": {"bound": "hbm", "kernel": names[top], "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": ncu_traffic[top], "peak_source": peak_src,
+                     "frac": achieved / peak, "traffic": ncu_traffic[top], "traffic_from": (
+                         None if ncu_traffic[top] is None else f"profiles/dram_traffic.md, ncu capture of {ncu_kernel[top]}"),
+                     "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": alg[top], "ms_per_launch": kern_ms[top]},
         "step_roofline": {"algorithmic_bytes_per_step": 12 * T, "achieved": step_achieved,
                           "frac": step_achieved / peak, "unit": "GB/s"},
         "kernels": [{"name": names[s], "ms": kern_ms[s], "algorithmic_bytes": alg[s], "traffic": ncu_traffic[s],
-                     "gbs": alg[s] / (kern_ms[s] * 1e-3) / 1e9} for s in range(3)],
+                     "profiled_kernel": ncu_kernel[s], "gbs": alg[s] / (kern_ms[s] * 1e-3) / 1e9} for s in range(3)],
         "wall_ms_timed_region": wall_ms,
         "clocks": clocks,
     }
+    del prob, pipe, res_host
+    torch.cuda.empty_cache()
+    if args.extras and not strong and args.batch <= 0 and se is None:
+        # The rest of the metric in the same record: the operator API on the same workload, the other
+        # op configurations, the decode step, and (N > 1) the same batch split over the ranks.
+        xs = min(args.steps, 50)
+        sampler2 = ClockSampler(local_rank)
+        if rank == 0:
+            sampler2.start()
+        line["api"] = api_line(cfg, dev, world, xs, 5, x)
+        if world > 1:
+            xs_, cfg_s = shard_inputs(x_full, cfg_full, rank, world)
+            sl = small_op_line(cfg_s, dev, world, xs, 5, xs_)
+            sl["tokens_per_s"] = cfg_full.B * cfg_full.N / (sl["ms_per_step"] * 1e-3)
+            sl["workload"] = f"{cfg_full.name}: batch of {cfg_full.B} split over {world} GPUs, no collective"
+            sl["speedup_vs_one_rank_of_the_weak_run"] = ms_per_step / sl["ms_per_step"]
+            line["strong"] = sl
+        for other in ("cfg2", "cfg2_4k"):
+            if other != args.workload:
+                line[other] = small_op_line(synth.OP_CONFIGS[other], dev, world, min(args.steps, 30), 5)
+        dargs = argparse.Namespace(**vars(args))
+        dargs.steps, dargs.warmup, dargs.decode_layers = min(args.steps, 100), 5, 0
+        d = run_decode_workload(dargs, rank, local_rank, world, sample_clocks=False, device_rings=True)
+        line["decode"] = {"workload": d["config"]["workload"], "tokens_per_s": d["value"], "ms_per_step": d["ms_per_step"],
+                          "ms_per_step_eager": d["ms_per_step_eager"], "ring_gbs": d["roofline"]["achieved"],
+                          "frac": d["roofline"]["frac"], "steps": dargs.steps, "launch": d["config"]["launch"]}
+        if rank == 0:
+            line["extras_clocks"] = sampler2.stop()      # clocks while api / strong / cfg2 / cfg2_4k / decode ran
     return line
 
 
-def run_decode_workload(args, rank, local_rank, world):
+def shard_inputs(x, cfg, rank, world):
+    """This rank's contiguous slice of the batch (strong scaling: the configuration's batch split over the ranks)."""
+    import dataclasses
+    from dwarf_b200 import dist as ddist
+    b0, b1 = ddist.shard_range(cfg.B, rank, world)
+    if b1 <= b0:
+        raise SystemExit(f"strong scaling: batch {cfg.B} has no entry for rank {rank} of {world}")
+    y = dict(x)
+    for nm in ("q", "k", "v", "dout"):
+        y[nm] = x[nm][b0:b1].contiguous()
+    return y, dataclasses.replace(cfg, B=b1 - b0)
+
+
+def run_decode_workload(args, rank, local_rank, world, sample_clocks=True, device_rings=False):
     import dwarf_b200
     from dwarf_b200 import dist as ddist, synth
 
@@ -261,7 +389,9 @@ def run_decode_workload(args, rank, local_rank, world):
         cfg.name = cfg.name.replace("L10", f"L{cfg.layers}")
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    x = synth.make_decode_inputs(cfg, device="cpu")
+    # device_rings: the 12 GB of ring contents are drawn on the GPU (same distribution, another
+    # stream of random numbers) instead of on the host, which takes most of a minute
+    x = synth.make_decode_inputs(cfg, device="cpu", rings_on=dev if device_rings else None)
     host = {nm: x[nm].pin_memory() for nm in ("q", "k_new", "v_new")}
     kr, vr = x["k_ring"].to(dev), x["v_ring"].to(dev)
     q, kn, vn = (host[nm].to(dev) for nm in ("q", "k_new", "v_new"))
@@ -278,7 +408,7 @@ def run_decode_workload(args, rank, local_rank, world):
                                         None, out[l], overlap=args.decode_overlap and l > 0)
 
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and sample_clocks:
         sampler.start()
     for _ in range(args.warmup):
         step()
@@ -327,7 +457,7 @@ def run_decode_workload(args, rank, local_rank, world):
     e1.record(stream)
     torch.cuda.synchronize(); ddist.barrier()
     e2e_ms = ddist.max_over_ranks(e0.elapsed_time(e1), dev if world > 1 else "cpu") / e2e_steps
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if rank == 0 and sample_clocks else None
 
     J = len(cfg.offsets)
     esz = 2
@@ -500,8 +630,11 @@ def main():
                     help="cfg3: launch every layer as an ordinary kernel (default: layers after the first overlap the one before)")
     ap.add_argument("--decode-layers", type=int, default=0, help="cfg3: number of layers (default: the 10 of the configuration)")
     ap.add_argument("--kernel-path", type=int, default=0,
-                    help="dsqg_set_kernel_path value for A/B runs: 0 automatic (default), 1 generic, 2 tensor-core "
-                         "without TMA variants, 3 TMA variants everywhere")
+                    help="dsqg_set_kernel_path value for A/B runs: 0 automatic (default), 1 generic, 2 tensor-core, "
+                         "3 forward with TMA-staged V")
+    ap.add_argument("--no-extras", dest="extras", action="store_false",
+                    help="op workloads: only the headline measurement (default: the line also carries the operator "
+                         "API, the other op configurations, the decode step and, at N > 1, the strong-scaling split)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

@@ -17,6 +17,11 @@ DSQG_DTYPE_F32 = 1
 DSQG_MAX_TAPS = 128
 DSQG_STATIC_SCRATCH_BYTES = 8 << 20
 
+class Strides(ctypes.Structure):
+    """dsqg_strides: element strides of the batch, head and row index."""
+    _fields_ = [("batch", ctypes.c_longlong), ("head", ctypes.c_longlong), ("row", ctypes.c_longlong)]
+
+
 # Every symbol include/dsqg_b200.h declares, with its ctypes signature.
 _SIGNATURES = {
     "dsqg_status_str": (c_char_p, [c_int]),
@@ -36,6 +41,12 @@ _SIGNATURES = {
     "dsqg_bwd_scaled": (c_int, [c_void_p] * 3 + [c_void_p] * 3 + [POINTER(c_int32), c_int] + [c_void_p] * 3
                         + [c_void_p] * 3 + [c_void_p] * 3 + [c_void_p, c_size_t] + [c_int] * 5
                         + [c_void_p, c_float]),
+    "dsqg_fwd_strided": (c_int, [c_void_p] * 3 + [POINTER(Strides)] + [c_void_p] * 2 + [POINTER(c_int32), c_int]
+                         + [c_void_p, POINTER(Strides), c_void_p, c_void_p] + [c_int] * 5 + [c_void_p, c_float]),
+    "dsqg_bwd_strided": (c_int, [c_void_p] * 3 + [POINTER(Strides)] + [c_void_p] * 2 + [POINTER(c_int32), c_int]
+                         + [c_void_p] * 3 + [POINTER(Strides), c_void_p] + [c_void_p] * 5 + [c_void_p, c_size_t]
+                         + [c_int] * 5 + [c_void_p, c_float]),
+    "dsqg_gate_bwd": (c_int, [c_void_p] * 3 + [POINTER(Strides)] + [c_void_p] * 3 + [c_int] * 4 + [c_void_p]),
     "dsqg_bwd_stages": (c_int, [c_void_p] * 3 + [c_void_p] * 3 + [POINTER(c_int32), c_int] + [c_void_p] * 3
                         + [c_void_p] * 3 + [c_void_p] * 3 + [c_void_p, c_size_t] + [c_int] * 5
                         + [c_void_p, c_int]),

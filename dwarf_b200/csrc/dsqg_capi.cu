@@ -85,11 +85,16 @@ int dsqg_tensor_core_path(int dtype, int D, const int32_t* offsets, int J, int h
     return mma_fwd_supported(dtype, D, t, has_scale_embed != 0) && mma_path_supported(dtype, D, t, has_scale_embed != 0) ? 1 : 0;
 }
 
-// scale <= 0 selects the operator's own 1/sqrt(D)
+static inline bool bad_strides(const dsqg_strides* s) {
+    return s->batch < 0 || s->head < 0 || s->row < 0 || (s->batch % 8) || (s->head % 8) || (s->row % 8);
+}
+
+// scale <= 0 selects the operator's own 1/sqrt(D); in_st / out_st == NULL: contiguous [B,H,N,D]
 static int fwd_impl(const void* q, const void* k, const void* v,
                     const float* pos_bias, const float* scale_embed, const float* head_gain,
                     const int32_t* offsets, int J, void* out, float* lse,
-                    int B, int H, int N, int D, int dtype, void* stream, float scale) {
+                    int B, int H, int N, int D, int dtype, void* stream, float scale,
+                    const dsqg_strides* in_st = nullptr, const dsqg_strides* out_st = nullptr, const void* gate = nullptr) {
     if (!q || !k || !v || !pos_bias || !out || !lse) return DSQG_ERR_NULL_POINTER;
     int rc = check_op_shape(B, H, N, D, dtype);
     if (rc) return rc;
@@ -104,6 +109,19 @@ static int fwd_impl(const void* q, const void* k, const void* v,
     a.head_gain = head_gain; a.out = out; a.lse = lse;
     a.B = B; a.H = H; a.N = N; a.D = D;
     a.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
+    a.strided = 0; a.gate = nullptr;
+    a.in_sb = a.in_sh = a.in_sn = a.out_sb = a.out_sh = a.out_sn = 0;
+    if (in_st) {
+        // strided tensors exist for the tensor-core kernels only
+        if (!out_st) return DSQG_ERR_NULL_POINTER;
+        if (bad_strides(in_st) || bad_strides(out_st) || (gate && misaligned16(gate))) return DSQG_ERR_MISALIGNED;
+        if (scale_embed || !mma_fwd_supported(dtype, D, t, false)) return DSQG_ERR_UNSUPPORTED;
+        a.strided = 1; a.gate = gate;
+        a.in_sb = in_st->batch; a.in_sh = in_st->head; a.in_sn = in_st->row;
+        a.out_sb = out_st->batch; a.out_sh = out_st->head; a.out_sn = out_st->row;
+        cudaError_t e = launch_fwd_mma(a, t, static_cast<cudaStream_t>(stream));
+        return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
+    }
     cudaError_t e = launch_fwd(a, t, dtype, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
 }
@@ -121,6 +139,16 @@ int dsqg_fwd_scaled(const void* q, const void* k, const void* v,
                     int B, int H, int N, int D, int dtype, void* stream, float scale) {
     if (!(scale > 0.f) || !(scale < 3.0e38f)) return DSQG_ERR_UNSUPPORTED;
     return fwd_impl(q, k, v, pos_bias, scale_embed, head_gain, offsets, J, out, lse, B, H, N, D, dtype, stream, scale);
+}
+
+int dsqg_fwd_strided(const void* q, const void* k, const void* v, const dsqg_strides* qkv_strides,
+                     const float* pos_bias, const float* head_gain, const int32_t* offsets, int J,
+                     void* out, const dsqg_strides* out_strides, const void* gate, float* lse,
+                     int B, int H, int N, int D, int dtype, void* stream, float scale) {
+    if (!qkv_strides || !out_strides) return DSQG_ERR_NULL_POINTER;
+    if (scale > 3.0e38f) return DSQG_ERR_UNSUPPORTED;
+    return fwd_impl(q, k, v, pos_bias, nullptr, head_gain, offsets, J, out, lse, B, H, N, D, dtype, stream, scale,
+                    qkv_strides, out_strides, gate);
 }
 
 size_t dsqg_bwd_scratch_bytes(int J, int B, int H, int N, int D, int has_scale_embed) {
@@ -155,7 +183,9 @@ static int bwd_impl(const void* q, const void* k, const void* v,
                     void* dq, void* dk, void* dv,
                     float* dpos_bias, float* dscale_embed, float* dhead_gain,
                     void* scratch, size_t scratch_bytes,
-                    int B, int H, int N, int D, int dtype, void* stream, int stages, float scale);
+                    int B, int H, int N, int D, int dtype, void* stream, int stages, float scale,
+                    const dsqg_strides* in_st = nullptr, const dsqg_strides* out_st = nullptr,
+                    const float* delta_pre = nullptr);
 
 int dsqg_bwd_stages(const void* q, const void* k, const void* v,
                     const float* pos_bias, const float* scale_embed, const float* head_gain,
@@ -190,7 +220,8 @@ static int bwd_impl(const void* q, const void* k, const void* v,
                     void* dq, void* dk, void* dv,
                     float* dpos_bias, float* dscale_embed, float* dhead_gain,
                     void* scratch, size_t scratch_bytes,
-                    int B, int H, int N, int D, int dtype, void* stream, int stages, float scale) {
+                    int B, int H, int N, int D, int dtype, void* stream, int stages, float scale,
+                    const dsqg_strides* in_st, const dsqg_strides* out_st, const float* delta_pre) {
     if (stages < 1 || stages > DSQG_BWD_STAGE_ALL) return DSQG_ERR_UNSUPPORTED;
     if (!q || !k || !v || !pos_bias || !out || !lse || !dout || !dq || !dk || !dv || !dpos_bias || !scratch)
         return DSQG_ERR_NULL_POINTER;
@@ -217,7 +248,46 @@ static int bwd_impl(const void* q, const void* k, const void* v,
     a.n_tiles = a.tiles_per_bh = a.n_dse_blocks = 0;
     a.B = B; a.H = H; a.N = N; a.D = D;
     a.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
+    a.strided = 0; a.delta_pre = nullptr;
+    a.in_sb = a.in_sh = a.in_sn = a.out_sb = a.out_sh = a.out_sn = 0;
+    if (in_st) {
+        if (!out_st) return DSQG_ERR_NULL_POINTER;
+        if (bad_strides(in_st) || bad_strides(out_st)) return DSQG_ERR_MISALIGNED;
+        if (scale_embed || !mma_path_supported(dtype, D, t, false)) return DSQG_ERR_UNSUPPORTED;
+        a.strided = 1; a.delta_pre = delta_pre;
+        a.in_sb = in_st->batch; a.in_sh = in_st->head; a.in_sn = in_st->row;
+        a.out_sb = out_st->batch; a.out_sh = out_st->head; a.out_sn = out_st->row;
+        cudaError_t e = launch_bwd_mma(a, t, static_cast<cudaStream_t>(stream), stages);
+        return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
+    }
     cudaError_t e = launch_bwd(a, t, dtype, static_cast<cudaStream_t>(stream), stages);
+    return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
+}
+
+int dsqg_bwd_strided(const void* q, const void* k, const void* v, const dsqg_strides* qkv_strides,
+                     const float* pos_bias, const float* head_gain, const int32_t* offsets, int J,
+                     const void* out, const float* lse, const void* dout, const dsqg_strides* out_strides,
+                     const float* delta_pre,
+                     void* dq, void* dk, void* dv, float* dpos_bias, float* dhead_gain,
+                     void* scratch, size_t scratch_bytes,
+                     int B, int H, int N, int D, int dtype, void* stream, float scale) {
+    if (!qkv_strides || !out_strides) return DSQG_ERR_NULL_POINTER;
+    if (scale > 3.0e38f) return DSQG_ERR_UNSUPPORTED;
+    return bwd_impl(q, k, v, pos_bias, nullptr, head_gain, offsets, J, out, lse, dout, dq, dk, dv,
+                    dpos_bias, nullptr, dhead_gain, scratch, scratch_bytes, B, H, N, D, dtype, stream,
+                    DSQG_BWD_STAGE_ALL, scale, qkv_strides, out_strides, delta_pre);
+}
+
+int dsqg_gate_bwd(const void* dy, const void* y, const void* gate, const dsqg_strides* strides,
+                  void* dout, void* dgate, float* delta, int B, int H, int N, int D, void* stream) {
+    if (!dy || !y || !gate || !strides || !dout || !dgate || !delta) return DSQG_ERR_NULL_POINTER;
+    int rc = check_op_shape(B, H, N, D, DSQG_DTYPE_BF16);
+    if (rc) return rc;
+    if (bad_strides(strides) || misaligned16(dy) || misaligned16(y) || misaligned16(gate) || misaligned16(dout) ||
+        misaligned16(dgate))
+        return DSQG_ERR_MISALIGNED;
+    cudaError_t e = launch_gate_bwd(dy, y, gate, strides->batch, strides->head, strides->row, dout, dgate, delta,
+                                    B, H, N, D, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
 }
 

@@ -30,6 +30,12 @@ struct FwdArgs {
     void* out; float* lse;
     int B, H, N, D;
     float scale;   // 1/sqrt(D)
+    // Strided addressing (tensor-core kernels only; strided == 0: everything is contiguous [B,H,N,D]).
+    // Element strides of batch, head and row for q, k, v (in_*) and for out and gate (out_*); the D
+    // elements of a row are contiguous.  gate (nullable, bf16, laid out like out): out *= sigmoid(gate).
+    int strided;
+    long long in_sb, in_sh, in_sn, out_sb, out_sh, out_sn;
+    const void* gate;
 };
 
 struct BwdArgs {
@@ -50,6 +56,11 @@ struct BwdArgs {
     int n_tiles, tiles_per_bh, n_dse_blocks;
     int B, H, N, D;
     float scale;
+    // Strided addressing as in FwdArgs: in_* for q, k, v, dq, dk, dv; out_* for out and dout.
+    // delta_pre (nullable, [B,H,N] fp32): sum_d dout*out per row when an earlier kernel formed it.
+    int strided;
+    long long in_sb, in_sh, in_sn, out_sb, out_sh, out_sn;
+    const float* delta_pre;
 };
 
 struct DecodeArgs {
@@ -72,6 +83,8 @@ cudaError_t launch_decode(const DecodeArgs& a, const Taps& t, int dtype, cudaStr
 cudaError_t launch_ring_prefill(const void* k, const void* v, void* k_ring, void* v_ring, int32_t* head, int32_t* fill,
                                 int S, int H, int N, int D, int R, int dtype, cudaStream_t s);
 
+cudaError_t launch_gate_bwd(const void* dy, const void* y, const void* gate, long long sb, long long sh, long long sn,
+                            void* dout, void* dgate, float* delta, int B, int H, int N, int D, cudaStream_t s);
 cudaError_t launch_fwd_mma(const FwdArgs& a, const Taps& t, cudaStream_t s);
 cudaError_t launch_bwd_mma(const BwdArgs& a, const Taps& t, cudaStream_t s, int stages);
 bool mma_path_supported(int dtype, int D, const Taps& t, bool has_scale_embed);   // backward

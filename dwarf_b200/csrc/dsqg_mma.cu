@@ -118,24 +118,26 @@ __device__ __forceinline__ void build_qs_tile(const SeTables& se, const RowFrag<
     __syncwarp();
 }
 
-template <int D, int WB, bool INTERIOR, int kTapGroup, bool SE>
+template <int D, int WB, bool INTERIOR, int kTapGroup, bool SE, bool ST>
 __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s, const int2* tap_s, int ns,
                                          int bh, int h, int g0, const Lane& L, const SeTables& se) {
     constexpr int NT = (WB + 16) / 8;
     const int N = a.N, g = L.g, tig = L.tig;
     const int row_lo = g0 + g, row_hi = row_lo + 8;
     const bool ok_lo = INTERIOR || row_lo < N, ok_hi = INTERIOR || row_hi < N;
-    const size_t base = (size_t)bh * N * D;
+    const ptrdiff_t RS = ST ? (ptrdiff_t)a.in_sn : D, OS = ST ? (ptrdiff_t)a.out_sn : D;   // row strides of q/k/v and of out
+    const size_t base = ST ? (size_t)(bh / a.H) * a.in_sb + (size_t)h * a.in_sh : (size_t)bh * N * D;
+    const size_t obase = ST ? (size_t)(bh / a.H) * a.out_sb + (size_t)h * a.out_sh : base;
     const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(a.q) + base;
     // per-thread pointers to this thread's chunk of row row_lo of K and V
-    const __nv_bfloat16* kl = static_cast<const __nv_bfloat16*>(a.k) + base + (ptrdiff_t)row_lo * D + 8 * tig;
-    const __nv_bfloat16* vl = static_cast<const __nv_bfloat16*>(a.v) + base + (ptrdiff_t)row_lo * D + 8 * tig;
+    const __nv_bfloat16* kl = static_cast<const __nv_bfloat16*>(a.k) + base + (ptrdiff_t)row_lo * RS + 8 * tig;
+    const __nv_bfloat16* vl = static_cast<const __nv_bfloat16*>(a.v) + base + (ptrdiff_t)row_lo * RS + 8 * tig;
     const float c2 = a.scale * kLog2e;
     const int kb0 = g0 - WB;
 
     RowFrag<D> qa, qb;
-    load_row(qa, qp + (size_t)row_lo * D, tig, ok_lo);
-    load_row(qb, qp + (size_t)row_hi * D, tig, ok_hi);
+    load_row(qa, qp + (size_t)row_lo * RS, tig, ok_lo);
+    load_row(qb, qp + (size_t)row_hi * RS, tig, ok_hi);
     if constexpr (SE) build_qs_tile<D, false>(se, qa, qb, g, tig);
 
     // ---- dense window: key row of n-tile nt for this thread is kb0 + 8 nt + g = row_lo - WB + 8 nt
@@ -151,10 +153,10 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
         }
         RowFrag<D> kf;
         if (INTERIOR) {
-            load_row_at(kf, kl + (8 * nt - WB) * D);
+            load_row_at(kf, kl + (8 * nt - WB) * RS);
         } else {
             const int kr = kb0 + 8 * nt + g;
-            load_row(kf, kl + (ptrdiff_t)(8 * nt - WB) * D - 8 * tig, tig, kr >= 0 && kr < N);
+            load_row(kf, kl + (ptrdiff_t)(8 * nt - WB) * RS - 8 * tig, tig, kr >= 0 && kr < N);
         }
         mma_rows(S[nt], qa, qb, kf);
     }
@@ -184,12 +186,12 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
     for (int c = 0; c < NT / 2; ++c) {
         RowFrag<D> vf0, vf1, vt0, vt1;
         if (INTERIOR) {
-            load_row_at(vf0, vl + (16 * c - WB) * D);
-            load_row_at(vf1, vl + (16 * c + 8 - WB) * D);
+            load_row_at(vf0, vl + (16 * c - WB) * RS);
+            load_row_at(vf1, vl + (16 * c + 8 - WB) * RS);
         } else {
             const int kr = kb0 + 16 * c + g;
-            load_row(vf0, vl + (ptrdiff_t)(16 * c - WB) * D - 8 * tig, tig, kr >= 0 && kr < N);
-            load_row(vf1, vl + (ptrdiff_t)(16 * c + 8 - WB) * D - 8 * tig, tig, kr + 8 >= 0 && kr + 8 < N);
+            load_row(vf0, vl + (ptrdiff_t)(16 * c - WB) * RS - 8 * tig, tig, kr >= 0 && kr < N);
+            load_row(vf1, vl + (ptrdiff_t)(16 * c + 8 - WB) * RS - 8 * tig, tig, kr + 8 >= 0 && kr + 8 < N);
         }
         transpose_frag(vt0, vf0); transpose_frag(vt1, vf1);
         const uint32_t a0 = pack_bf16x2(S[2 * c][0], S[2 * c][1]), a1 = pack_bf16x2(S[2 * c][2], S[2 * c][3]);
@@ -238,12 +240,12 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
 #pragma unroll
         for (int i = 0; i < G; ++i) {
             const int2 tp = tap_s[si + i];
-            const ptrdiff_t off = (ptrdiff_t)tp.x * D;
+            const ptrdiff_t off = (ptrdiff_t)tp.x * RS;
             pbv[i] = __int_as_float(tp.y);
             load_row_at(kf0[i], kl - off);
-            load_row_at(kf1[i], kl - off + 8 * D);
+            load_row_at(kf1[i], kl - off + 8 * RS);
             load_row_at(vf0[i], vl - off);
-            load_row_at(vf1[i], vl - off + 8 * D);
+            load_row_at(vf1[i], vl - off + 8 * RS);
         }
         float x0[G], x1[G];
 #pragma unroll
@@ -283,12 +285,12 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
             const float pbv = __int_as_float(tap_s[si].y);
             const int kr0 = row_lo - delta, kr1 = row_hi - delta;
             const bool v0 = kr0 >= 0 && kr0 < N, v1 = kr1 >= 0 && kr1 < N;
-            const ptrdiff_t off = (ptrdiff_t)delta * D + 8 * tig;
+            const ptrdiff_t off = (ptrdiff_t)delta * RS + 8 * tig;
             RowFrag<D> kf0, kf1, vf0[1], vf1[1];
             load_row(kf0, kl - off, tig, v0);
-            load_row(kf1, kl - off + 8 * D, tig, v1);
+            load_row(kf1, kl - off + 8 * RS, tig, v1);
             load_row(vf0[0], vl - off, tig, v0);
-            load_row(vf1[0], vl - off + 8 * D, tig, v1);
+            load_row(vf1[0], vl - off + 8 * RS, tig, v1);
             float s0[4], s1[4];
             mma_rows_z(s0, qa, qb, kf0);
             mma_rows_z(s1, qa, qb, kf1);
@@ -302,9 +304,15 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
     }
     l_lo = quad_sum(l_lo); l_hi = quad_sum(l_hi);
     const float gain = a.head_gain ? a.head_gain[h] : 1.f;
-    __nv_bfloat16* op = static_cast<__nv_bfloat16*>(a.out) + base;
-    store_acc_rows<D>(O, op + (size_t)row_lo * D, op + (size_t)row_hi * D, ok_lo, ok_hi,
-                      l_lo > 0.f ? __fdividef(gain, l_lo) : 0.f, l_hi > 0.f ? __fdividef(gain, l_hi) : 0.f, tig);
+    __nv_bfloat16* op = static_cast<__nv_bfloat16*>(a.out) + obase;
+    const float sc_lo = l_lo > 0.f ? __fdividef(gain, l_lo) : 0.f, sc_hi = l_hi > 0.f ? __fdividef(gain, l_hi) : 0.f;
+    if (ST && a.gate) {
+        const __nv_bfloat16* gp = static_cast<const __nv_bfloat16*>(a.gate) + obase;
+        store_acc_rows_gated<D>(O, op + (size_t)row_lo * OS, op + (size_t)row_hi * OS, gp + (size_t)row_lo * OS,
+                                gp + (size_t)row_hi * OS, ok_lo, ok_hi, sc_lo, sc_hi, tig);
+    } else {
+        store_acc_rows<D>(O, op + (size_t)row_lo * OS, op + (size_t)row_hi * OS, ok_lo, ok_hi, sc_lo, sc_hi, tig);
+    }
     if (tig == 0) {
         if (ok_lo) a.lse[(size_t)bh * N + row_lo] = l_lo > 0.f ? (m_lo + __log2f(l_lo)) * kLn2 : -INFINITY;
         if (ok_hi) a.lse[(size_t)bh * N + row_hi] = l_hi > 0.f ? (m_hi + __log2f(l_hi)) * kLn2 : -INFINITY;
@@ -364,7 +372,10 @@ __host__ __device__ inline size_t se_tables_bytes(int J, int D, int NT, int warp
     return (size_t)2 * Jp * D * 2 + (size_t)Jp * 4 + (size_t)NT * 32 * 16 + (size_t)warps * (tile_rows * (Jp + 2) + 4) * 4;
 }
 
-template <int D, int WB, bool SE>
+// ST: q, k, v and out are addressed through the element strides in FwdArgs (rows of D contiguous
+// elements; any batch / head / row strides), e.g. the un-permuted output of a fused qkv projection
+// and a token-major result; with a gate tensor the epilogue multiplies by sigmoid(gate).
+template <int D, int WB, bool SE, bool ST>
 __global__ void __launch_bounds__(FwdTune<D>::warps * 32, FwdTune<D>::ctas)
 fwd_mma_kernel(const FwdArgs a, const Taps t) {
     constexpr int W = FwdTune<D>::warps, G = FwdTune<D>::group;
@@ -396,8 +407,8 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
     __syncthreads();
     const int g0 = blockIdx.x * (16 * W) + L.warp * 16;
     if (g0 >= N) return;
-    if (g0 >= WB && g0 + 16 <= N) fwd_tile<D, WB, true, G, SE>(a, init_s, tap_s, t.n_sparse, bh, h, g0, L, se);
-    else fwd_tile<D, WB, false, G, SE>(a, init_s, tap_s, t.n_sparse, bh, h, g0, L, se);
+    if (g0 >= WB && g0 + 16 <= N) fwd_tile<D, WB, true, G, SE, ST>(a, init_s, tap_s, t.n_sparse, bh, h, g0, L, se);
+    else fwd_tile<D, WB, false, G, SE, ST>(a, init_s, tap_s, t.n_sparse, bh, h, g0, L, se);
 }
 
 // Tuning per head dimension (measured on B200): sparse taps whose loads are issued together and
@@ -419,7 +430,7 @@ struct SeBwd {
     int JS;            // J rounded up to 16
 };
 
-template <int D, int WB, bool INTERIOR, int G, bool SE>
+template <int D, int WB, bool INTERIOR, int G, bool SE, bool ST>
 __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s, const int4* soff_s, const int2* tap_s,
                                          float* stage_w, int nd, int ns, int bh, int h, int g0, const Lane& L,
                                          const SeTables& se, const SeBwd& sb) {
@@ -428,22 +439,24 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
     const int N = a.N, g = L.g, tig = L.tig;
     const int row_lo = g0 + g, row_hi = row_lo + 8;
     const bool ok_lo = INTERIOR || row_lo < N, ok_hi = INTERIOR || row_hi < N;
-    const size_t base = (size_t)bh * N * D;
+    const ptrdiff_t RS = ST ? (ptrdiff_t)a.in_sn : D, OS = ST ? (ptrdiff_t)a.out_sn : D;   // row strides of q/k/v/dq and of out/dout
+    const size_t base = ST ? (size_t)(bh / a.H) * a.in_sb + (size_t)h * a.in_sh : (size_t)bh * N * D;
+    const size_t obase = ST ? (size_t)(bh / a.H) * a.out_sb + (size_t)h * a.out_sh : base;
     const __nv_bfloat16* qp = static_cast<const __nv_bfloat16*>(a.q) + base;
-    const __nv_bfloat16* op = static_cast<const __nv_bfloat16*>(a.out) + base;
-    const __nv_bfloat16* dop = static_cast<const __nv_bfloat16*>(a.dout) + base;
-    const __nv_bfloat16* kl = static_cast<const __nv_bfloat16*>(a.k) + base + (ptrdiff_t)row_lo * D + 8 * tig;
-    const __nv_bfloat16* vl = static_cast<const __nv_bfloat16*>(a.v) + base + (ptrdiff_t)row_lo * D + 8 * tig;
+    const __nv_bfloat16* op = static_cast<const __nv_bfloat16*>(a.out) + obase;
+    const __nv_bfloat16* dop = static_cast<const __nv_bfloat16*>(a.dout) + obase;
+    const __nv_bfloat16* kl = static_cast<const __nv_bfloat16*>(a.k) + base + (ptrdiff_t)row_lo * RS + 8 * tig;
+    const __nv_bfloat16* vl = static_cast<const __nv_bfloat16*>(a.v) + base + (ptrdiff_t)row_lo * RS + 8 * tig;
     const float c2 = a.scale * kLog2e;
     const float gain = a.head_gain ? a.head_gain[h] : 1.f;
     const int kb0 = g0 - WB;
     float dgrow = 0.f;
 
     RowFrag<D> qa, qb, da, db;
-    load_row(qa, qp + (size_t)row_lo * D, tig, ok_lo);
-    load_row(qb, qp + (size_t)row_hi * D, tig, ok_hi);
-    load_row(da, dop + (size_t)row_lo * D, tig, ok_lo);
-    load_row(db, dop + (size_t)row_hi * D, tig, ok_hi);
+    load_row(qa, qp + (size_t)row_lo * RS, tig, ok_lo);
+    load_row(qb, qp + (size_t)row_hi * RS, tig, ok_hi);
+    load_row(da, dop + (size_t)row_lo * OS, tig, ok_lo);
+    load_row(db, dop + (size_t)row_hi * OS, tig, ok_hi);
     if constexpr (SE) {
         // the tile also goes to global memory for the dK/dV kernel (rows of this warp, Jp floats each)
         float* rows = a.qs_rows + ((size_t)bh * N + row_lo) * se.Jp;
@@ -457,10 +470,13 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
         }
     }
     float delta_lo, delta_hi;
-    {
+    if (ST && a.delta_pre) {       // sum_d dout*out was formed by an earlier kernel (gate backward)
+        delta_lo = ok_lo ? a.delta_pre[(size_t)bh * N + row_lo] : 0.f;
+        delta_hi = ok_hi ? a.delta_pre[(size_t)bh * N + row_hi] : 0.f;
+    } else {
         RowFrag<D> oa, ob;
-        load_row(oa, op + (size_t)row_lo * D, tig, ok_lo);
-        load_row(ob, op + (size_t)row_hi * D, tig, ok_hi);
+        load_row(oa, op + (size_t)row_lo * OS, tig, ok_lo);
+        load_row(ob, op + (size_t)row_hi * OS, tig, ok_hi);
         delta_lo = quad_sum(frag_dot(da, oa));
         delta_hi = quad_sum(frag_dot(db, ob));
     }
@@ -505,13 +521,13 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
             float s[4] = {ini.x, ini.y, ini.z, ini.w}, dp[4];
             RowFrag<D> vf;
             if (INTERIOR) {
-                load_row_at(kf[hf], kl + (8 * nt - WB) * D);
-                load_row_at(vf, vl + (8 * nt - WB) * D);
+                load_row_at(kf[hf], kl + (8 * nt - WB) * RS);
+                load_row_at(vf, vl + (8 * nt - WB) * RS);
             } else {
                 const int kr = kb0 + 8 * nt + g;
                 const bool kv = kr >= 0 && kr < N;
-                load_row(kf[hf], kl + (ptrdiff_t)(8 * nt - WB) * D - 8 * tig, tig, kv);
-                load_row(vf, vl + (ptrdiff_t)(8 * nt - WB) * D - 8 * tig, tig, kv);
+                load_row(kf[hf], kl + (ptrdiff_t)(8 * nt - WB) * RS - 8 * tig, tig, kv);
+                load_row(vf, vl + (ptrdiff_t)(8 * nt - WB) * RS - 8 * tig, tig, kv);
             }
             mma_rows(s, qa, qb, kf[hf]);
             mma_rows_z(dp, da, db, vf);
@@ -565,12 +581,12 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
 #pragma unroll
         for (int i = 0; i < GG; ++i) {
             const int2 tp = tap_s[si + i];
-            const ptrdiff_t off = (ptrdiff_t)tp.x * D;
+            const ptrdiff_t off = (ptrdiff_t)tp.x * RS;
             pbv[i] = __int_as_float(tp.y);
             load_row_at(kf0[i], kl - off);
-            load_row_at(kf1[i], kl - off + 8 * D);
+            load_row_at(kf1[i], kl - off + 8 * RS);
             load_row_at(vf0[i], vl - off);
-            load_row_at(vf1[i], vl - off + 8 * D);
+            load_row_at(vf1[i], vl - off + 8 * RS);
         }
 #pragma unroll
         for (int i = 0; i < GG; ++i) {
@@ -594,12 +610,12 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
         } else {
             const float pbv = __int_as_float(tap_s[si].y);
             const bool v0 = row_lo >= delta && row_lo - delta < N, v1 = row_hi >= delta && row_hi - delta < N;
-            const ptrdiff_t off = (ptrdiff_t)delta * D + 8 * tig;
+            const ptrdiff_t off = (ptrdiff_t)delta * RS + 8 * tig;
             RowFrag<D> kf0, kf1, vf0, vf1;
             load_row(kf0, kl - off, tig, v0);
-            load_row(kf1, kl - off + 8 * D, tig, v1);
+            load_row(kf1, kl - off + 8 * RS, tig, v1);
             load_row(vf0, vl - off, tig, v0);
-            load_row(vf1, vl - off + 8 * D, tig, v1);
+            load_row(vf1, vl - off + 8 * RS, tig, v1);
             float s0[4], s1[4], e0[4], e1[4];
             mma_rows_z(s0, qa, qb, kf0); mma_rows_z(s1, qa, qb, kf1);
             mma_rows_z(e0, da, db, vf0); mma_rows_z(e1, da, db, vf1);
@@ -625,7 +641,7 @@ __device__ __forceinline__ float dq_tile(const BwdArgs& a, const float4* init_s,
         }
     }
     __nv_bfloat16* dqp = static_cast<__nv_bfloat16*>(a.dq) + base;
-    store_acc_rows<D>(dQ, dqp + (size_t)row_lo * D, dqp + (size_t)row_hi * D, ok_lo, ok_hi, a.scale, a.scale, tig);
+    store_acc_rows<D>(dQ, dqp + (size_t)row_lo * RS, dqp + (size_t)row_hi * RS, ok_lo, ok_hi, a.scale, a.scale, tig);
     return dgrow;
 }
 
@@ -706,7 +722,7 @@ inline size_t dq_smem_bytes(int J, int n_sparse, int D, int NT, bool se) {
     return n;
 }
 
-template <int D, int WB, int G, int CT, bool SE>
+template <int D, int WB, int G, int CT, bool SE, bool ST>
 __global__ void __launch_bounds__(kWarps * 32, CT)
 bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
     constexpr int NT = (WB + 16) / 8;
@@ -780,9 +796,9 @@ bwd_dq_mma_kernel(const BwdArgs a, const Taps t) {
             for (int e = L.lane; e < 16 * (2 * D + 16) / 16; e += 32)
                 reinterpret_cast<uint4*>(sb.q_s + (size_t)L.warp * 16 * (2 * D + 16))[e] = make_uint4(0u, 0u, 0u, 0u);
     } else if (g0 >= WB && g0 + 16 <= N) {
-        dgrow = dq_tile<D, WB, true, G, SE>(a, init_s, soff_s, tap_s, stage_w, t.n_dense, t.n_sparse, bh, h, g0, L, se, sb);
+        dgrow = dq_tile<D, WB, true, G, SE, ST>(a, init_s, soff_s, tap_s, stage_w, t.n_dense, t.n_sparse, bh, h, g0, L, se, sb);
     } else {
-        dgrow = dq_tile<D, WB, false, G, SE>(a, init_s, soff_s, tap_s, stage_w, t.n_dense, t.n_sparse, bh, h, g0, L, se, sb);
+        dgrow = dq_tile<D, WB, false, G, SE, ST>(a, init_s, soff_s, tap_s, stage_w, t.n_dense, t.n_sparse, bh, h, g0, L, se, sb);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) dgrow += __shfl_xor_sync(0xffffffffu, dgrow, o);
@@ -870,7 +886,7 @@ dse_group_kernel(const float* __restrict__ tmp, float* __restrict__ part, int ti
 // With scale_embed the score accumulators of the dense window start from qsd, the CTA's copy of the
 // dense part of qs_rows (row = query, nd + 1 columns, the last one holding the mask value), and a
 // sparse tap adds the entry of its query row read from global memory.
-template <int D, int WB, bool INTERIOR, int G, bool SE>
+template <int D, int WB, bool INTERIOR, int G, bool SE, bool ST>
 __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s, const int2* tap_s, const float2* stat_w,
                                           int ns, int bh, int h, int m0, const Lane& L, const float* qsd_w,
                                           const int4* qoff, int nd, int Jp) {
@@ -878,20 +894,22 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
     const int N = a.N, g = L.g, tig = L.tig;
     const int row_lo = m0 + g, row_hi = row_lo + 8;
     const bool ok_lo = INTERIOR || row_lo < N, ok_hi = INTERIOR || row_hi < N;
-    const size_t base = (size_t)bh * N * D;
+    const ptrdiff_t RS = ST ? (ptrdiff_t)a.in_sn : D, OS = ST ? (ptrdiff_t)a.out_sn : D;   // row strides of q/k/v/dk/dv and of dout
+    const size_t base = ST ? (size_t)(bh / a.H) * a.in_sb + (size_t)h * a.in_sh : (size_t)bh * N * D;
+    const size_t obase = ST ? (size_t)(bh / a.H) * a.out_sb + (size_t)h * a.out_sh : base;
     const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(a.k) + base;
     const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(a.v) + base;
-    const __nv_bfloat16* ql = static_cast<const __nv_bfloat16*>(a.q) + base + (ptrdiff_t)row_lo * D + 8 * tig;
-    const __nv_bfloat16* dl = static_cast<const __nv_bfloat16*>(a.dout) + base + (ptrdiff_t)row_lo * D + 8 * tig;
+    const __nv_bfloat16* ql = static_cast<const __nv_bfloat16*>(a.q) + base + (ptrdiff_t)row_lo * RS + 8 * tig;
+    const __nv_bfloat16* dl = static_cast<const __nv_bfloat16*>(a.dout) + obase + (ptrdiff_t)row_lo * OS + 8 * tig;
     const float2* rs = reinterpret_cast<const float2*>(a.delta) + (size_t)bh * N + row_lo;
     const float c2 = a.scale * kLog2e;
     const float gain = a.head_gain ? a.head_gain[h] : 1.f;
 
     RowFrag<D> ka, kb, va, vb;
-    load_row(ka, kp + (size_t)row_lo * D, tig, ok_lo);
-    load_row(kb, kp + (size_t)row_hi * D, tig, ok_hi);
-    load_row(va, vp + (size_t)row_lo * D, tig, ok_lo);
-    load_row(vb, vp + (size_t)row_hi * D, tig, ok_hi);
+    load_row(ka, kp + (size_t)row_lo * RS, tig, ok_lo);
+    load_row(kb, kp + (size_t)row_hi * RS, tig, ok_hi);
+    load_row(va, vp + (size_t)row_lo * RS, tig, ok_lo);
+    load_row(vb, vp + (size_t)row_hi * RS, tig, ok_hi);
     float dK[D / 8][4], dV[D / 8][4];
 
     // ---- dense window: query row of n-tile nt for this thread is m0 + 8 nt + g
@@ -912,12 +930,12 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
                 s[0] = ini.x; s[1] = ini.y; s[2] = ini.z; s[3] = ini.w;
             }
             if (INTERIOR) {
-                load_row_at(qf[hf], ql + 8 * nt * D);
-                load_row_at(df[hf], dl + 8 * nt * D);
+                load_row_at(qf[hf], ql + 8 * nt * RS);
+                load_row_at(df[hf], dl + 8 * nt * OS);
             } else {
                 const bool qv = m0 + 8 * nt + g < N;
-                load_row(qf[hf], ql + (ptrdiff_t)8 * nt * D - 8 * tig, tig, qv);
-                load_row(df[hf], dl + (ptrdiff_t)8 * nt * D - 8 * tig, tig, qv);
+                load_row(qf[hf], ql + (ptrdiff_t)8 * nt * RS - 8 * tig, tig, qv);
+                load_row(df[hf], dl + (ptrdiff_t)8 * nt * OS - 8 * tig, tig, qv);
             }
             mma_rows(s, ka, kb, qf[hf]);
             mma_rows_z(dp, va, vb, df[hf]);
@@ -971,7 +989,7 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
 #pragma unroll
         for (int i = 0; i < GG; ++i) {
             const int2 tp = tap_s[si + i];
-            const ptrdiff_t off = (ptrdiff_t)tp.x * D;
+            const ptrdiff_t off = (ptrdiff_t)tp.x * RS, offd = (ptrdiff_t)tp.x * OS;
             if constexpr (SE) {
                 b0[i] = __ldg(qs_r + (size_t)tp.x * Jp + si + i);
                 b1[i] = __ldg(qs_r + (size_t)(tp.x + 8) * Jp + si + i);
@@ -979,9 +997,9 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
                 b0[i] = b1[i] = __int_as_float(tp.y);
             }
             load_row_at(qf0[i], ql + off);
-            load_row_at(qf1[i], ql + off + 8 * D);
-            load_row_at(df0[i], dl + off);
-            load_row_at(df1[i], dl + off + 8 * D);
+            load_row_at(qf1[i], ql + off + 8 * RS);
+            load_row_at(df0[i], dl + offd);
+            load_row_at(df1[i], dl + offd + 8 * OS);
             st0[i] = __ldg(rs + tp.x);
             st1[i] = __ldg(rs + tp.x + 8);
         }
@@ -1009,12 +1027,12 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
                 b0 = v0 ? __ldg(qs_r + (size_t)delta * Jp + si) : 0.f;
                 b1 = v1 ? __ldg(qs_r + (size_t)(delta + 8) * Jp + si) : 0.f;
             }
-            const ptrdiff_t off = (ptrdiff_t)delta * D - 8 * tig;
+            const ptrdiff_t off = (ptrdiff_t)delta * RS - 8 * tig, offd = (ptrdiff_t)delta * OS - 8 * tig;
             RowFrag<D> qf0, qf1, df0, df1;
             load_row(qf0, ql + off, tig, v0);
-            load_row(qf1, ql + off + 8 * D, tig, v1);
-            load_row(df0, dl + off, tig, v0);
-            load_row(df1, dl + off + 8 * D, tig, v1);
+            load_row(qf1, ql + off + 8 * RS, tig, v1);
+            load_row(df0, dl + offd, tig, v0);
+            load_row(df1, dl + offd + 8 * OS, tig, v1);
             const float2 st0 = v0 ? __ldg(rs + delta) : make_float2(0.f, 0.f);
             const float2 st1 = v1 ? __ldg(rs + delta + 8) : make_float2(0.f, 0.f);
             float s0[4], s1[4], e0[4], e1[4];
@@ -1026,15 +1044,15 @@ __device__ __forceinline__ void dkdv_tile(const BwdArgs& a, const float4* init_s
     }
     __nv_bfloat16* dkp = static_cast<__nv_bfloat16*>(a.dk) + base;
     __nv_bfloat16* dvp = static_cast<__nv_bfloat16*>(a.dv) + base;
-    store_acc_rows<D>(dK, dkp + (size_t)row_lo * D, dkp + (size_t)row_hi * D, ok_lo, ok_hi, a.scale, a.scale, tig);
-    store_acc_rows<D>(dV, dvp + (size_t)row_lo * D, dvp + (size_t)row_hi * D, ok_lo, ok_hi, 1.f, 1.f, tig);
+    store_acc_rows<D>(dK, dkp + (size_t)row_lo * RS, dkp + (size_t)row_hi * RS, ok_lo, ok_hi, a.scale, a.scale, tig);
+    store_acc_rows<D>(dV, dvp + (size_t)row_lo * RS, dvp + (size_t)row_hi * RS, ok_lo, ok_hi, 1.f, 1.f, tig);
 }
 
 inline size_t dkdv_smem_bytes(int n_dense, int WB, bool se) {
     return se ? (size_t)(kRows + WB) * (n_dense + 1) * 4 : 0;
 }
 
-template <int D, int WB, int G, int CT, bool SE>
+template <int D, int WB, int G, int CT, bool SE, bool ST>
 __global__ void __launch_bounds__(kWarps * 32, CT)
 bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t, const int n_reduce, const int reduce_stride) {
     constexpr int NT = (WB + 16) / 8;
@@ -1120,9 +1138,9 @@ bwd_dkdv_mma_kernel(const BwdArgs a, const Taps t, const int n_reduce, const int
     const float* qsd_w = qsd + L.warp * 16 * ndp;
     const int4* qoff = reinterpret_cast<const int4*>(init_s);
     if (m0 + 16 + WB <= N)
-        dkdv_tile<D, WB, true, G, SE>(a, init_s, tap_s, stat_s + L.warp * 16, t.n_sparse, bh, h, m0, L, qsd_w, qoff, nd, Jp);
+        dkdv_tile<D, WB, true, G, SE, ST>(a, init_s, tap_s, stat_s + L.warp * 16, t.n_sparse, bh, h, m0, L, qsd_w, qoff, nd, Jp);
     else
-        dkdv_tile<D, WB, false, G, SE>(a, init_s, tap_s, stat_s + L.warp * 16, t.n_sparse, bh, h, m0, L, qsd_w, qoff, nd, Jp);
+        dkdv_tile<D, WB, false, G, SE, ST>(a, init_s, tap_s, stat_s + L.warp * 16, t.n_sparse, bh, h, m0, L, qsd_w, qoff, nd, Jp);
 }
 
 // Raises a kernel's dynamic shared-memory limit to what this launch needs.  The attribute is set
@@ -1149,20 +1167,23 @@ cudaError_t fwd_launch_mma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
     if (a.scale_embed) {
         if constexpr (D <= 64) {
             const size_t smem = se_tables_bytes(t.J, D, (WB + 16) / 8, W, 16);
+            if (a.strided) return cudaErrorInvalidValue;
             static int seen[64] = {0};
-            cudaError_t e = ensure_dynamic_smem(fwd_mma_kernel<D, WB, true>, smem, seen);
+            cudaError_t e = ensure_dynamic_smem(fwd_mma_kernel<D, WB, true, false>, smem, seen);
             if (e != cudaSuccess) return e;
-            fwd_mma_kernel<D, WB, true><<<grid, W * 32, smem, s>>>(a, t);
+            fwd_mma_kernel<D, WB, true, false><<<grid, W * 32, smem, s>>>(a, t);
         } else {
             return cudaErrorInvalidValue;
         }
+    } else if (a.strided) {
+        fwd_mma_kernel<D, WB, false, true><<<grid, W * 32, 0, s>>>(a, t);
     } else {
-        fwd_mma_kernel<D, WB, false><<<grid, W * 32, 0, s>>>(a, t);
+        fwd_mma_kernel<D, WB, false, false><<<grid, W * 32, 0, s>>>(a, t);
     }
     return cudaGetLastError();
 }
 
-template <int D, int WB, bool SE>
+template <int D, int WB, bool SE, bool ST>
 cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stages) {
     using T = BwdTune<D>;
     constexpr int NT = (WB + 16) / 8;
@@ -1174,7 +1195,7 @@ cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stag
             se_prep_kernel<D><<<1, 1024, 0, s>>>(a.scale_embed, a.pos_bias, a.scale, t.J, a.H, t.d_lo, t.n_dense, WB, a.se_pre);
             if ((e = cudaGetLastError()) != cudaSuccess) return e;
         }
-        auto kern = bwd_dq_mma_kernel<D, WB, T::dq_group, SE ? T::dq_ctas_se : T::dq_ctas, SE>;
+        auto kern = bwd_dq_mma_kernel<D, WB, T::dq_group, SE ? T::dq_ctas_se : T::dq_ctas, SE, ST>;
         const size_t smem = dq_smem_bytes(t.J, t.n_sparse, D, NT, SE);
         static int seen[64] = {0};
         if ((e = ensure_dynamic_smem(kern, smem, seen)) != cudaSuccess) return e;
@@ -1192,7 +1213,7 @@ cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stag
     const bool fuse = (stages & DSQG_BWD_STAGE_DKDV) && (stages & DSQG_BWD_STAGE_REDUCE) &&
                       (long long)grid.x * grid.y >= n_out;
     if (stages & DSQG_BWD_STAGE_DKDV) {
-        auto kern = bwd_dkdv_mma_kernel<D, WB, T::dkdv_group, T::dkdv_ctas, SE>;
+        auto kern = bwd_dkdv_mma_kernel<D, WB, T::dkdv_group, T::dkdv_ctas, SE, ST>;
         const size_t smem = dkdv_smem_bytes(t.n_dense, WB, SE);
         static int seen[64] = {0};
         if ((e = ensure_dynamic_smem(kern, smem, seen)) != cudaSuccess) return e;
@@ -1206,10 +1227,12 @@ cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stag
 template <int D, int WB>
 cudaError_t bwd_launch_mma(const BwdArgs& a, const Taps& t, cudaStream_t s, int stages) {
     if (a.scale_embed) {
-        if constexpr (D <= 64) return bwd_launch_mma_se<D, WB, true>(a, t, s, stages);
+        if (a.strided) return cudaErrorInvalidValue;
+        if constexpr (D <= 64) return bwd_launch_mma_se<D, WB, true, false>(a, t, s, stages);
         else return cudaErrorInvalidValue;
     }
-    return bwd_launch_mma_se<D, WB, false>(a, t, s, stages);
+    if (a.strided) return bwd_launch_mma_se<D, WB, false, true>(a, t, s, stages);
+    return bwd_launch_mma_se<D, WB, false, false>(a, t, s, stages);
 }
 
 int band_width(const Taps& t) {

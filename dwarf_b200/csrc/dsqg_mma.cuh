@@ -140,6 +140,36 @@ __device__ __forceinline__ void store_acc_rows(const float (&acc)[D / 8][4], __n
     }
 }
 
+// As store_acc_rows, with every element multiplied by sigmoid(gate) of the same position (gate rows
+// are bf16 in the layout of the output rows): the sigmoid gate of the attention block folded into
+// the epilogue (DWARF train/train_2048_condU.py:190-191).
+template <int D>
+__device__ __forceinline__ void store_acc_rows_gated(const float (&acc)[D / 8][4], __nv_bfloat16* row_lo, __nv_bfloat16* row_hi,
+                                                     const __nv_bfloat16* gate_lo, const __nv_bfloat16* gate_hi,
+                                                     bool ok_lo, bool ok_hi, float s_lo, float s_hi, int tig) {
+    auto sig2 = [](uint32_t u, float& a, float& b) {
+        a = __fdividef(1.f, 1.f + __expf(-__uint_as_float(u << 16)));
+        b = __fdividef(1.f, 1.f + __expf(-__uint_as_float(u & 0xffff0000u)));
+    };
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+        uint4 gl = make_uint4(0u, 0u, 0u, 0u), gh = gl;
+        if (ok_lo) gl = __ldg(reinterpret_cast<const uint4*>(gate_lo + 32 * c + 8 * tig));
+        if (ok_hi) gh = __ldg(reinterpret_cast<const uint4*>(gate_hi + 32 * c + 8 * tig));
+        const uint32_t gls[4] = {gl.x, gl.y, gl.z, gl.w}, ghs[4] = {gh.x, gh.y, gh.z, gh.w};
+        uint32_t lo[4], hi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float a0, a1, b0, b1;
+            sig2(gls[j], a0, a1); sig2(ghs[j], b0, b1);
+            lo[j] = pack_bf16x2(acc[4 * c + j][0] * s_lo * a0, acc[4 * c + j][1] * s_lo * a1);
+            hi[j] = pack_bf16x2(acc[4 * c + j][2] * s_hi * b0, acc[4 * c + j][3] * s_hi * b1);
+        }
+        if (ok_lo) *reinterpret_cast<uint4*>(row_lo + 32 * c + 8 * tig) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        if (ok_hi) *reinterpret_cast<uint4*>(row_hi + 32 * c + 8 * tig) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    }
+}
+
 // Partial dot product of two row fragments over this thread's elements (fp32).
 template <int D>
 __device__ __forceinline__ float frag_dot(const RowFrag<D>& a, const RowFrag<D>& b) {

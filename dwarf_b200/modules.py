@@ -19,7 +19,7 @@ from typing import Optional, Sequence
 import torch
 import torch.nn as nn
 
-from .ops import ALL_OFFSETS, dsqg_attention
+from .ops import ALL_OFFSETS, dsqg_attention, dsqg_attention_packed, packed_path_available
 
 
 def dsqg_attention_v2(q, k, v, pos_bias, offsets: Sequence[int] = ALL_OFFSETS):
@@ -75,6 +75,7 @@ class _DSQGAttentionBase(nn.Module):
         if with_if_gain:
             self.if_gain = nn.Parameter(torch.ones(num_heads))
         self.dropout = nn.Dropout(dropout)
+        self._packed = None            # decided on first use: can the copy-free path take this layer?
 
     def _project_heads(self, x):
         """x [B,N,D] -> q, k, v [B,H,N,HD] contiguous."""
@@ -83,11 +84,32 @@ class _DSQGAttentionBase(nn.Module):
         return tuple(t.view(B, N, H, HD).permute(0, 2, 1, 3).contiguous()
                      for t in self.qkv_proj(x).split(D, dim=-1))
 
+    def _packed_ok(self, qkv, kv_inject):
+        """The copy-free path applies to bf16 activations (autocast), no K/V injection, no scale_embed,
+        and head widths / offset sets the tensor-core kernels take."""
+        if kv_inject is not None or hasattr(self, "scale_embed") or qkv.dtype != torch.bfloat16 or not qkv.is_cuda:
+            return False
+        if self._packed is None:
+            self._packed = packed_path_available(self.head_dim, self._offsets)
+        return self._packed
+
     def attend(self, x, kv_inject=None):
         """The layer's output together with the k, v [B,H,N,HD] bf16 the op saw (what a decode
         cache has to be filled with)."""
         B, N, D = x.shape
-        q, k, v = self._project_heads(x)
+        qkv = self.qkv_proj(x)
+        if self._packed_ok(qkv, kv_inject):
+            # q, k, v are read in place from the projection output, the result comes back
+            # token-major and already gated: none of the reference's permute copies
+            # (train/train_2048_condU.py:171-175,189-191) is made
+            H, HD = self.num_heads, self.head_dim
+            qkv5 = qkv.contiguous().view(B, N, 3, H, HD)
+            gate = self.gate_proj(x)
+            y = dsqg_attention_packed(qkv5, self.pos_bias, getattr(self, "if_gain", None),
+                                      gate.to(torch.bfloat16), self._offsets)
+            return (self.dropout(self.out_proj(y)), qkv5[:, :, 1].permute(0, 2, 1, 3), qkv5[:, :, 2].permute(0, 2, 1, 3))
+        H, HD = self.num_heads, self.head_dim
+        q, k, v = (t.view(B, N, H, HD).permute(0, 2, 1, 3).contiguous() for t in qkv.split(D, dim=-1))
         if kv_inject is not None:          # Huygens K/V injection, train_2048_condU.py:178-181
             k = k + kv_inject[0]
             v = v + kv_inject[1]

@@ -141,6 +141,89 @@ class DSQGFunction(torch.autograd.Function):
                 None if dse is None else dse.to(se_dt), None)
 
 
+class DSQGPackedFunction(torch.autograd.Function):
+    """DSQG on the un-permuted output of a fused qkv projection, with a token-major result.
+
+    qkv [B,N,3,H,HD] bf16 (a view of the [B,N,3*H*HD] projection output; q, k, v are read in place
+    through strides), gate [B,N,H*HD] bf16 or None -> y [B,N,H*HD] = DSQG(q,k,v) (* sigmoid(gate)).
+    Replaces the three `.permute(0,2,1,3).contiguous()` copies, the output permute and the gate
+    multiply of the reference's attention modules (train/train_2048_condU.py:171-175,189-191) and
+    their autograd backward; the gradient comes back as one dqkv tensor in the layout of qkv."""
+
+    @staticmethod
+    def forward(ctx, qkv, gate, pos_bias, head_gain, offsets):
+        lib = _lib.load()
+        off, J = _lib.offsets_array(offsets)
+        B, N, three, H, D = qkv.shape
+        if three != 3 or qkv.dtype != torch.bfloat16 or not qkv.is_contiguous():
+            raise ValueError("dsqg packed: qkv must be a contiguous bf16 [B,N,3,H,HD] tensor")
+        if gate is not None and (gate.dtype != torch.bfloat16 or tuple(gate.shape) != (B, N, H * D)):
+            raise ValueError("dsqg packed: gate must be bf16 [B,N,H*HD]")
+        gate = None if gate is None else gate.contiguous()
+        pb, hg = _f32c(pos_bias), _f32c(head_gain)
+        if tuple(pb.shape) != (J, H):
+            raise ValueError(f"dsqg: pos_bias must be [{J},{H}], got {tuple(pb.shape)}")
+        y = torch.empty(B, N, H * D, device=qkv.device, dtype=qkv.dtype)
+        lse = torch.empty(B, H, N, device=qkv.device, dtype=torch.float32)
+        st_in = _lib.Strides(N * 3 * H * D, D, 3 * H * D)
+        st_out = _lib.Strides(N * H * D, D, H * D)
+        p0, esz = qkv.data_ptr(), qkv.element_size()
+        with torch.cuda.device(qkv.device):
+            stream = torch.cuda.current_stream(qkv.device).cuda_stream
+            _lib.check(lib.dsqg_fwd_strided(p0, p0 + H * D * esz, p0 + 2 * H * D * esz, st_in, pb.data_ptr(), _ptr(hg),
+                                            off, J, y.data_ptr(), st_out, _ptr(gate), lse.data_ptr(),
+                                            B, H, N, D, _lib.DSQG_DTYPE_BF16, stream, 0.0), "dsqg_fwd_strided")
+        ctx.save_for_backward(qkv, gate, pb, hg, y, lse)
+        ctx.offsets = tuple(offsets)
+        ctx.param_dtypes = (pos_bias.dtype, None if head_gain is None else head_gain.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.load()
+        qkv, gate, pb, hg, y, lse = ctx.saved_tensors
+        off, J = _lib.offsets_array(ctx.offsets)
+        B, N, _, H, D = qkv.shape
+        dy = dy.to(qkv.dtype).contiguous()
+        st_in = _lib.Strides(N * 3 * H * D, D, 3 * H * D)
+        st_out = _lib.Strides(N * H * D, D, H * D)
+        dqkv = torch.empty_like(qkv)
+        dpb = torch.empty_like(pb)
+        dhg = None if hg is None else torch.empty_like(hg)
+        nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, 0)
+        scratch = torch.empty(nbytes, device=qkv.device, dtype=torch.uint8)
+        p0, g0, esz = qkv.data_ptr(), dqkv.data_ptr(), qkv.element_size()
+        with torch.cuda.device(qkv.device):
+            stream = torch.cuda.current_stream(qkv.device).cuda_stream
+            dgate, dout, delta = None, dy, None
+            if gate is not None:
+                dout, dgate = torch.empty_like(y), torch.empty_like(gate)
+                delta = torch.empty(B, H, N, device=qkv.device, dtype=torch.float32)
+                _lib.check(lib.dsqg_gate_bwd(dy.data_ptr(), y.data_ptr(), gate.data_ptr(), st_out, dout.data_ptr(),
+                                             dgate.data_ptr(), delta.data_ptr(), B, H, N, D, stream), "dsqg_gate_bwd")
+            _lib.check(lib.dsqg_bwd_strided(p0, p0 + H * D * esz, p0 + 2 * H * D * esz, st_in, pb.data_ptr(), _ptr(hg),
+                                            off, J, y.data_ptr(), lse.data_ptr(), dout.data_ptr(), st_out, _ptr(delta),
+                                            g0, g0 + H * D * esz, g0 + 2 * H * D * esz, dpb.data_ptr(), _ptr(dhg),
+                                            scratch.data_ptr(), nbytes, B, H, N, D, _lib.DSQG_DTYPE_BF16, stream, 0.0),
+                       "dsqg_bwd_strided")
+        pb_dt, hg_dt = ctx.param_dtypes
+        return dqkv, dgate, dpb.to(pb_dt), None if dhg is None else dhg.to(hg_dt), None
+
+
+def packed_path_available(head_dim: int, offsets: Sequence[int]) -> bool:
+    """True when dsqg_attention_packed can take this head width and offset set (the bf16 tensor-core
+    kernels without scale_embed); otherwise callers use dsqg_attention on permuted copies."""
+    off, J = _lib.offsets_array(offsets)
+    return bool(_lib.load().dsqg_tensor_core_path(_lib.DSQG_DTYPE_BF16, int(head_dim), off, J, 0))
+
+
+def dsqg_attention_packed(qkv, pos_bias, head_gain=None, gate=None, offsets: Sequence[int] = ALL_OFFSETS):
+    """DSQG straight on the fused projection output.  qkv: [B,N,3,H,HD] bf16 contiguous; gate: None
+    or [B,N,H*HD] bf16 (pre-sigmoid).  Returns [B,N,H*HD] bf16, already multiplied by
+    sigmoid(gate) when a gate is given."""
+    return DSQGPackedFunction.apply(qkv, gate, pos_bias, head_gain, tuple(int(o) for o in offsets))
+
+
 def dsqg_attention(q, k, v, pos_bias, head_gain=None, scale_embed=None,
                    offsets: Sequence[int] = ALL_OFFSETS):
     """General DSQG entry: any ascending offset set, optional per-head output gain and

@@ -95,8 +95,11 @@ class DecodeConfig:
         return max(self.offsets) + 1
 
 
-def make_decode_inputs(cfg: DecodeConfig, device="cpu", S: Optional[int] = None, layers: Optional[int] = None):
-    """Fully populated rings ~ N(0,1), a random write head per sequence, new q,k,v ~ N(0,1)."""
+def make_decode_inputs(cfg: DecodeConfig, device="cpu", S: Optional[int] = None, layers: Optional[int] = None,
+                       rings_on=None):
+    """Fully populated rings ~ N(0,1), a random write head per sequence, new q,k,v ~ N(0,1).
+    rings_on: a CUDA device on which the two ring tensors are drawn directly (seeded generator of
+    that device) instead of on the host; everything else stays on `device`."""
     g = torch.Generator(device="cpu").manual_seed(cfg.seed)
     S = cfg.S if S is None else S
     L = cfg.layers if layers is None else layers
@@ -105,7 +108,12 @@ def make_decode_inputs(cfg: DecodeConfig, device="cpu", S: Optional[int] = None,
     gain = torch.rand(cfg.H, generator=g) * 0.4 + 0.8
     head = torch.randint(0, cfg.R, (S,), generator=g, dtype=torch.int32)
     mk = lambda *shape: torch.randn(*shape, generator=g).to(cfg.dtype).to(device)
-    return {"k_ring": mk(L, S, cfg.H, cfg.R, cfg.D), "v_ring": mk(L, S, cfg.H, cfg.R, cfg.D),
+    if rings_on is not None:
+        gd = torch.Generator(device=rings_on).manual_seed(cfg.seed + 1)
+        ring = lambda: torch.randn(L, S, cfg.H, cfg.R, cfg.D, generator=gd, device=rings_on, dtype=cfg.dtype)
+    else:
+        ring = lambda: mk(L, S, cfg.H, cfg.R, cfg.D)
+    return {"k_ring": ring(), "v_ring": ring(),
             "q": mk(L, S, cfg.H, cfg.D), "k_new": mk(L, S, cfg.H, cfg.D), "v_new": mk(L, S, cfg.H, cfg.D),
             "head": head.to(device), "pos_bias": pb.to(device), "head_gain": gain.to(device),
             "offsets": cfg.offsets}

@@ -187,6 +187,43 @@ int dsqg_bwd_scaled(const void* q, const void* k, const void* v,
                     void* scratch, size_t scratch_bytes,
                     int B, int H, int N, int D, int dtype, void* stream, float scale);
 
+/* Strided tensors: the caller's layouts instead of contiguous [B,H,N,D] copies.
+ * Replaces: the three transposing copies a DWARF attention module makes before the op and the
+ *   permute + gate multiply after it -- `view(B,N,H,HD).permute(0,2,1,3).contiguous()` on each of
+ *   q, k, v (train/train_2048_condU.py:171-175, kernels/dsqg_attention_v2.py:462-467), then
+ *   `out.permute(0,2,1,3).reshape(B,N,D)` and `* torch.sigmoid(self.gate_proj(x))`
+ *   (train/train_2048_condU.py:189-191) -- and the autograd backward of those PyTorch ops.
+ * A dsqg_strides gives the ELEMENT strides of the batch, head and row index of a tensor whose D
+ * elements per (batch, head, row) are contiguous; all three must be multiples of 8 (16 bytes).
+ *   qkv_strides: layout shared by q, k, v (and by dq, dk, dv in the backward).  For the output of a
+ *     fused qkv projection, [B,N,3*H*D] seen as [B,N,3,H,D]: {N*3*H*D, D, 3*H*D}, with q, k, v
+ *     pointing at elements 0, H*D and 2*H*D of that buffer.
+ *   out_strides: layout shared by out, gate (and by dout in the backward).  Token-major
+ *     [B,N,H*D]: {N*H*D, D, H*D}.
+ *   gate (dsqg_fwd_strided, nullable): bf16 tensor laid out like out; the kernel writes
+ *     out * sigmoid(gate).  With a gate, dsqg_gate_bwd turns the gradient dy of that product into
+ *     the dout, dgate and delta ([B,H,N] fp32 = sum_d dy*y) that dsqg_bwd_strided takes; y is the
+ *     forward's (gated) output, which is also what dsqg_bwd_strided gets as `out`.  Without a gate
+ *     pass delta_pre = NULL and the forward's output and its gradient as out and dout.
+ * lse, dpos_bias, dhead_gain, scratch (dsqg_bwd_scratch_bytes(..., 0)) are as in dsqg_fwd / dsqg_bwd.
+ * bf16 only, no scale_embed, and only shapes the tensor-core kernels take
+ * (dsqg_tensor_core_path(...) == 1): DSQG_ERR_UNSUPPORTED otherwise, so that a caller can fall
+ * back to the copies.  scale <= 0 selects 1/sqrt(D). */
+typedef struct { long long batch, head, row; } dsqg_strides;
+int dsqg_fwd_strided(const void* q, const void* k, const void* v, const dsqg_strides* qkv_strides,
+                     const float* pos_bias, const float* head_gain, const int32_t* offsets, int J,
+                     void* out, const dsqg_strides* out_strides, const void* gate, float* lse,
+                     int B, int H, int N, int D, int dtype, void* stream, float scale);
+int dsqg_bwd_strided(const void* q, const void* k, const void* v, const dsqg_strides* qkv_strides,
+                     const float* pos_bias, const float* head_gain, const int32_t* offsets, int J,
+                     const void* out, const float* lse, const void* dout, const dsqg_strides* out_strides,
+                     const float* delta_pre,
+                     void* dq, void* dk, void* dv, float* dpos_bias, float* dhead_gain,
+                     void* scratch, size_t scratch_bytes,
+                     int B, int H, int N, int D, int dtype, void* stream, float scale);
+int dsqg_gate_bwd(const void* dy, const void* y, const void* gate, const dsqg_strides* strides,
+                  void* dout, void* dgate, float* delta, int B, int H, int N, int D, void* stream);
+
 /* Single-token decode over a circular K/V ring buffer.
  * Replaces: nothing executable -- the reference only describes the O(1) cache in prose
  *   (DWARF README.md:175-179; generate() in train/train_2048_condU.py:463-487 re-runs the

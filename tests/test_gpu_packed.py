@@ -1,0 +1,132 @@
+"""GPU tests of the copy-free layout path (dsqg_fwd_strided / dsqg_bwd_strided / dsqg_gate_bwd through
+DSQGPackedFunction): q, k, v read in place from a fused qkv projection output [B,N,3,H,HD], result
+token-major [B,N,H*HD], sigmoid gate folded into the epilogue.  The check is the chain the reference
+runs -- permute copies, op, permute, gate multiply (train/train_2048_condU.py:171-175,184-191) --
+evaluated with the C oracle in fp32."""
+import pytest
+import torch
+
+import dwarf_b200
+from dwarf_b200 import synth
+from oracle import dsqg_oracle as O
+from tests.gpu_util import (PARAM_REL_TOL_BF16, assert_bf16_close, assert_param_grad_close, oracle_fwd_bwd)
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(B, N, H, D, offsets, seed):
+    g = torch.Generator().manual_seed(seed)
+    qkv = (torch.randn(B, N, 3, H, D, generator=g) * 0.5).bfloat16()
+    gate = torch.randn(B, N, H * D, generator=g).bfloat16()
+    dy = torch.randn(B, N, H * D, generator=g).bfloat16()
+    pb = synth.log_linear_pos_bias(offsets, H) + torch.randn(len(offsets), H, generator=g) * 0.05
+    gain = torch.rand(H, generator=g) * 0.4 + 0.8
+    return qkv, gate, dy, pb, gain
+
+
+def _reference(qkv, gate, dy, pb, gain, offsets):
+    """permute -> oracle op -> permute -> * sigmoid(gate), and the gradients of that chain."""
+    B, N, _, H, D = qkv.shape
+    q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3).float().contiguous() for i in range(3))
+    tok = lambda t: t.permute(0, 2, 1, 3).reshape(B, N, H * D)            # [B,H,N,D] -> [B,N,H*D]
+    heads = lambda t: t.view(B, N, H, D).permute(0, 2, 1, 3).contiguous()
+    fwd = oracle_fwd_bwd(q, k, v, pb, None, None, gain, offsets)
+    o = tok(fwd["out"])
+    if gate is None:
+        y, dout, dgate = o, dy.float(), None
+    else:
+        s = torch.sigmoid(gate.float())
+        y, dout = o * s, dy.float() * s
+        dgate = dy.float() * o * s * (1 - s)
+    bwd = oracle_fwd_bwd(q, k, v, pb, heads(dout), None, gain, offsets)
+    dqkv = torch.stack([bwd[nm].permute(0, 2, 1, 3) for nm in ("dq", "dk", "dv")], dim=2)   # [B,N,3,H,D]
+    return y, dqkv, dgate, bwd["dpb"], bwd["dgain"]
+
+
+@pytest.mark.parametrize("shape", [(2, 300, 4, 32), (1, 2047, 8, 32), (2, 130, 3, 64), (1, 70, 2, 128), (1, 1, 2, 32)])
+@pytest.mark.parametrize("offsets", [O.OFFSETS_43, O.OFFSETS_44], ids=["J43", "J44"])
+@pytest.mark.parametrize("with_gate", [True, False])
+def test_packed_qkv_token_major_out_and_gate_fold_vs_oracle_chain(shape, offsets, with_gate):
+    B, N, H, D = shape
+    qkv, gate, dy, pb, gain = _case(B, N, H, D, offsets, 11 + N + D)
+    if not with_gate:
+        gate = None
+    y_ref, dqkv_ref, dgate_ref, dpb_ref, dgain_ref = _reference(qkv, gate, dy, pb, gain, offsets)
+    dev = torch.device("cuda", 0)
+    assert dwarf_b200.packed_path_available(D, offsets)
+    qkv_d = qkv.to(dev).requires_grad_(True)
+    gate_d = None if gate is None else gate.to(dev).requires_grad_(True)
+    pb_d, gain_d = pb.to(dev).requires_grad_(True), gain.to(dev).requires_grad_(True)
+    y = dwarf_b200.dsqg_attention_packed(qkv_d, pb_d, gain_d, gate_d, offsets)
+    assert y.shape == (B, N, H * D) and y.dtype == torch.bfloat16
+    y.backward(dy.to(dev))
+    assert_bf16_close(y.detach().float().cpu(), y_ref, "y")
+    assert_bf16_close(qkv_d.grad.float().cpu(), dqkv_ref, "dqkv")
+    if with_gate:
+        assert_bf16_close(gate_d.grad.float().cpu(), dgate_ref, "dgate")
+    assert_param_grad_close(pb_d.grad.cpu(), dpb_ref, "dpb", PARAM_REL_TOL_BF16)
+    assert_param_grad_close(gain_d.grad.cpu(), dgain_ref, "dgain", PARAM_REL_TOL_BF16)
+
+
+def test_packed_path_equals_copy_path_bitwise_without_gate():
+    """Same kernels, same arithmetic, other addresses: without the gate the strided entries must give
+    exactly the bits of the contiguous entries on permuted copies."""
+    dev = torch.device("cuda", 0)
+    B, N, H, D = 2, 777, 4, 32
+    qkv, _, dy, pb, gain = _case(B, N, H, D, O.OFFSETS_43, 5)
+    qkv_d = qkv.to(dev).requires_grad_(True)
+    pb_d, gain_d = pb.to(dev).requires_grad_(True), gain.to(dev).requires_grad_(True)
+    y = dwarf_b200.dsqg_attention_packed(qkv_d, pb_d, gain_d, None, O.OFFSETS_43)
+    y.backward(dy.to(dev))
+    q, k, v = (qkv.to(dev)[:, :, i].permute(0, 2, 1, 3).contiguous().requires_grad_(True) for i in range(3))
+    pb2, gain2 = pb.to(dev).requires_grad_(True), gain.to(dev).requires_grad_(True)
+    o = dwarf_b200.dsqg_attention(q, k, v, pb2, gain2, None, O.OFFSETS_43)
+    o.backward(dy.to(dev).view(B, N, H, D).permute(0, 2, 1, 3).contiguous())
+    assert torch.equal(y.detach(), o.detach().permute(0, 2, 1, 3).reshape(B, N, H * D))
+    for i, t in enumerate((q, k, v)):
+        assert torch.equal(qkv_d.grad[:, :, i], t.grad.permute(0, 2, 1, 3))
+    assert torch.equal(pb_d.grad, pb2.grad) and torch.equal(gain_d.grad, gain2.grad)
+
+
+def test_module_takes_the_packed_path_under_autocast_and_matches_the_copy_path():
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(2)
+    m = dwarf_b200.DSQGAttentionN_Fused(256, 8, dropout=0.0, offsets=O.OFFSETS_43).to(dev)
+    x = torch.randn(2, 200, 256, device=dev, requires_grad=True)
+
+    def run(packed):
+        m._packed = packed
+        for p in m.parameters():
+            p.grad = None
+        x.grad = None
+        with torch.amp.autocast("cuda", dtype=torch.bfloat16):
+            y = m(x)
+        y.float().sum().backward()
+        return y.detach().float(), x.grad.clone(), m.pos_bias.grad.clone(), m.gate_proj.weight.grad.clone()
+
+    a, b = run(None), run(False)
+    assert m._packed is False
+    m._packed = None
+    for nm, u, w in zip(("y", "dx", "dpos_bias", "dgate_w"), a, b):
+        scale = w.abs().max().item() + 1e-6
+        assert (u - w).abs().max().item() <= 2e-2 * max(1.0, scale), nm
+    # fp32 activations (no autocast) and layers with scale_embed keep the copy path
+    assert not m._packed_ok(torch.zeros(1, device=dev), None)
+    assert not dwarf_b200.DSQGAttentionV3(64, 2).to(dev)._packed_ok(torch.zeros(1, device=dev, dtype=torch.bfloat16), None)
+
+
+def test_strided_entries_refuse_what_they_cannot_take():
+    from dwarf_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    x = torch.zeros(4096, device=dev, dtype=torch.bfloat16)
+    p = x.data_ptr()
+    off, J = _lib.offsets_array(O.OFFSETS_43)
+    ok = _lib.Strides(3 * 2 * 32 * 16, 32, 3 * 2 * 32)
+    odd = _lib.Strides(3 * 2 * 32 * 16, 32, 3 * 2 * 32 + 4)
+    f32 = torch.zeros(64, device=dev).data_ptr()
+    args = lambda st, D, dt: (p, p, p, st, f32, None, off, J, p, st, None, f32, 1, 2, 16, D, dt, None, 0.0)
+    assert lib.dsqg_fwd_strided(*args(odd, 32, 0)) == -5             # strides must be multiples of 8 elements
+    assert lib.dsqg_fwd_strided(*args(ok, 80, 0)) == -8              # no tensor-core kernel for this width
+    assert lib.dsqg_fwd_strided(*args(ok, 32, 1)) == -8              # fp32
+    assert not dwarf_b200.packed_path_available(80, O.OFFSETS_43)
