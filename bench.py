@@ -500,7 +500,11 @@ def run_train_workload(args, rank, local_rank, world):
     torch.cuda.set_device(dev)
     B, N, V = 32, 2048, 32000
     torch.manual_seed(1234)
-    model = CondMLM(vocab=V, seq_len=N).to(dev)
+    model = CondMLM(vocab=V, seq_len=N, attention=args.lm_attention).to(dev)
+    if not args.packed_layout:          # A/B: the reference's permute copies and separate gate multiply
+        for blk in model.blocks:
+            if hasattr(blk.attn, "_packed"):
+                blk.attn._packed = False
     if world > 1:
         model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank])
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True)
@@ -542,6 +546,9 @@ def run_train_workload(args, rank, local_rank, world):
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "cfg4 condM-shaped LM train step: 6 layers d256 8x32 heads FFN1024 vocab32000, "
                                "DSQG layers 0-4 + full attention layer 5, B32/GPU N2048, AdamW",
+                   "dsqg_layers": args.lm_attention + (", q/k/v read in place, gate folded (strided entry points)"
+                                                       if args.packed_layout and args.lm_attention == "condM"
+                                                       else ", permute copies + separate gate multiply"),
                    "parameters": n_params, "final_loss": float(loss_host),
                    "parallelism": f"dp{world} (DDP, NCCL gradient all-reduce)" if world > 1 else "single GPU"},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": B * (N + 1) * 8, "d2h_bytes_per_step": 4,
@@ -632,6 +639,12 @@ def main():
     ap.add_argument("--kernel-path", type=int, default=0,
                     help="dsqg_set_kernel_path value for A/B runs: 0 automatic (default), 1 generic, 2 tensor-core, "
                          "3 forward with TMA-staged V")
+    ap.add_argument("--lm-attention", choices=["condM", "condU"], default="condM",
+                    help="cfg4: DSQG layers with the position bias only (condM, the configuration's shape) or with "
+                         "scale_embed and the per-head gain (condU)")
+    ap.add_argument("--no-packed-layout", dest="packed_layout", action="store_false",
+                    help="cfg4: make the permute copies before / after the op and the gate multiply in PyTorch, as the "
+                         "reference does, instead of the strided entry points (A/B measurement)")
     ap.add_argument("--no-extras", dest="extras", action="store_false",
                     help="op workloads: only the headline measurement (default: the line also carries the operator "
                          "API, the other op configurations, the decode step and, at N > 1, the strong-scaling split)")

@@ -13,7 +13,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .modules import DSQGAttentionQW
+from .modules import DSQGAttentionN_Fused, DSQGAttentionQW
 from .ops import OFFSETS_43
 
 
@@ -67,11 +67,12 @@ class FullCausalAttention(nn.Module):
 
 
 class Block(nn.Module):
-    def __init__(self, dim, heads, ffn, seq_len, full_attention, offsets):
+    def __init__(self, dim, heads, ffn, seq_len, full_attention, offsets, attention="condM"):
         super().__init__()
         self.norm1, self.norm2 = RMSNorm(dim), RMSNorm(dim)
+        dsqg_cls = {"condM": DSQGAttentionN_Fused, "condU": DSQGAttentionQW}[attention]
         self.attn = FullCausalAttention(dim, heads) if full_attention else \
-            DSQGAttentionQW(dim, heads, seq_len=seq_len, dropout=0.0, offsets=offsets)
+            dsqg_cls(dim, heads, seq_len=seq_len, dropout=0.0, offsets=offsets)
         self.ffn = FFN(dim, ffn)
 
     def forward(self, x):
@@ -85,12 +86,16 @@ class Block(nn.Module):
 
 
 class CondMLM(nn.Module):
+    """attention = "condM": DSQG layers with the position bias only (the reference's condM,
+    kernels/dsqg_attention_v2.py:434-477) -- the shape the end-to-end benchmark configuration names;
+    "condU": with scale_embed and the per-head gain (train/train_2048_condU.py:116-205)."""
+
     def __init__(self, vocab=32000, dim=256, heads=8, layers=6, ffn=1024, seq_len=2048,
-                 full_attention_layer=5, offsets=OFFSETS_43):
+                 full_attention_layer=5, offsets=OFFSETS_43, attention="condM"):
         super().__init__()
         self.embedding = nn.Embedding(vocab, dim)
         self.pos_embed = nn.Embedding(seq_len, dim)
-        self.blocks = nn.ModuleList(Block(dim, heads, ffn, seq_len, i == full_attention_layer, offsets)
+        self.blocks = nn.ModuleList(Block(dim, heads, ffn, seq_len, i == full_attention_layer, offsets, attention)
                                     for i in range(layers))
         self.norm = RMSNorm(dim)
         self.apply(self._init)

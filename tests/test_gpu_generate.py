@@ -10,10 +10,10 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def small_model(offsets, seq_len=160):
+def small_model(offsets, seq_len=160, attention="condU"):
     torch.manual_seed(7)
     m = CondMLM(vocab=211, dim=64, heads=2, layers=3, ffn=128, seq_len=seq_len,
-                full_attention_layer=1, offsets=offsets).to(DEV).eval()
+                full_attention_layer=1, offsets=offsets, attention=attention).to(DEV).eval()
     with torch.no_grad():          # the zero/one initial values would hide these terms
         for blk in m.blocks:
             if hasattr(blk.attn, "scale_embed"):
@@ -27,8 +27,9 @@ def small_model(offsets, seq_len=160):
 
 @pytest.mark.parametrize("offsets,prompt", [((0, 1, 2, 3, 4, 8, 16, 48), 70),     # ring of 49 slots wraps
                                             ((0, 1, 2, 3, 5, 64, 150), 9)])       # ring longer than the text
-def test_decode_token_logits_equal_full_recompute(offsets, prompt):
-    m = small_model(offsets)
+@pytest.mark.parametrize("attention", ["condU", "condM"])
+def test_decode_token_logits_equal_full_recompute(offsets, prompt, attention):
+    m = small_model(offsets, attention=attention)
     S, new = 3, 24
     ids = torch.randint(0, 211, (S, prompt + new), device=DEV, generator=torch.Generator(DEV).manual_seed(1))
     full = m(ids).float()                                   # logits of every position, one pass
