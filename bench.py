@@ -391,9 +391,16 @@ def run_decode_workload(args, rank, local_rank, world, sample_clocks=True, devic
     torch.cuda.set_device(dev)
     # device_rings: the 12 GB of ring contents are drawn on the GPU (same distribution, another
     # stream of random numbers) instead of on the host, which takes most of a minute
-    x = synth.make_decode_inputs(cfg, device="cpu", rings_on=dev if device_rings else None)
+    inter = args.ring_layout == "interleaved"
+    x = synth.make_decode_inputs(cfg, device="cpu", rings_on="meta" if inter else (dev if device_rings else None))
     host = {nm: x[nm].pin_memory() for nm in ("q", "k_new", "v_new")}
-    kr, vr = x["k_ring"].to(dev), x["v_ring"].to(dev)
+    if inter:
+        # one ring per layer with key and value of a slot side by side, drawn on the device
+        gd = torch.Generator(device=dev).manual_seed(cfg.seed + 1)
+        kv = torch.randn(cfg.layers, cfg.S, cfg.H, cfg.R, 2, cfg.D, generator=gd, device=dev, dtype=cfg.dtype)
+        kr = vr = None
+    else:
+        kr, vr = x["k_ring"].to(dev), x["v_ring"].to(dev)
     q, kn, vn = (host[nm].to(dev) for nm in ("q", "k_new", "v_new"))
     head = x["head"].to(dev); pb = x["pos_bias"].to(dev); gain = x["head_gain"].to(dev)
     out = torch.empty_like(q)
@@ -404,8 +411,12 @@ def run_decode_workload(args, rank, local_rank, world, sample_clocks=True, devic
         for l in range(L):
             # from the second layer of a token on, the kernel ahead in the stream is another layer's
             # step (its own rings), so the overlapped launch is allowed
-            dwarf_b200.dsqg_decode_step(q[l], kn[l], vn[l], kr[l], vr[l], head, pb, gain, None, cfg.offsets,
-                                        None, out[l], overlap=args.decode_overlap and l > 0)
+            if inter:
+                dwarf_b200.dsqg_decode_step_kv(q[l], kn[l], vn[l], kv[l], head, pb, gain, None, cfg.offsets,
+                                               None, out[l], overlap=args.decode_overlap and l > 0)
+            else:
+                dwarf_b200.dsqg_decode_step(q[l], kn[l], vn[l], kr[l], vr[l], head, pb, gain, None, cfg.offsets,
+                                            None, out[l], overlap=args.decode_overlap and l > 0)
 
     sampler = ClockSampler(local_rank)
     if rank == 0 and sample_clocks:
@@ -472,6 +483,8 @@ def run_decode_workload(args, rank, local_rank, world, sample_clocks=True, devic
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": cfg.name, "l2": f"ring footprint {2 * L * cfg.S * cfg.H * cfg.R * cfg.D * esz / 1e9:.1f} GB >> L2",
+                   "rings": ("one ring per layer, key and value of a slot side by side [S,H,R,2,D]" if inter
+                             else "separate K and V rings per layer [S,H,R,D]"),
                    "launch": f"one CUDA graph of the {L} per-layer launches per step"
                              + ("; layers after the first launched with programmatic dependent launch "
                                 "(ring gather overlaps the layer before)" if args.decode_overlap else ""),
@@ -635,6 +648,8 @@ def main():
                          "strong = the configuration's batch is split over the GPUs")
     ap.add_argument("--no-decode-overlap", dest="decode_overlap", action="store_false",
                     help="cfg3: launch every layer as an ordinary kernel (default: layers after the first overlap the one before)")
+    ap.add_argument("--ring-layout", choices=["interleaved", "separate"], default="interleaved",
+                    help="cfg3: one K/V ring per layer with key and value of a slot side by side (default) or two rings")
     ap.add_argument("--decode-layers", type=int, default=0, help="cfg3: number of layers (default: the 10 of the configuration)")
     ap.add_argument("--kernel-path", type=int, default=0,
                     help="dsqg_set_kernel_path value for A/B runs: 0 automatic (default), 1 generic, 2 tensor-core, "

@@ -55,6 +55,10 @@ _SIGNATURES = {
     "dsqg_ring_prefill": (c_int, [c_void_p] * 6 + [c_int] * 6 + [c_void_p]),
     "dsqg_decode": (c_int, [c_void_p] * 3 + [c_void_p] * 2 + [c_void_p] * 2 + [c_void_p] * 3
                     + [POINTER(c_int32), c_int, c_int] + [c_void_p] + [c_int] * 4 + [c_void_p]),
+    "dsqg_causal_mean": (c_int, [c_void_p, c_void_p] + [c_int] * 5 + [c_void_p]),
+    "dsqg_decode_kv": (c_int, [c_void_p] * 3 + [c_void_p] + [c_void_p] * 2 + [c_void_p] * 3
+                       + [POINTER(c_int32), c_int, c_int] + [c_void_p] + [c_int] * 4 + [c_void_p, c_int]),
+    "dsqg_ring_prefill_kv": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_void_p]),
     "dsqg_decode_overlapped": (c_int, [c_void_p] * 3 + [c_void_p] * 2 + [c_void_p] * 2 + [c_void_p] * 3
                                + [POINTER(c_int32), c_int, c_int] + [c_void_p] + [c_int] * 4 + [c_void_p]),
 }

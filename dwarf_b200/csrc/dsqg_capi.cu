@@ -295,11 +295,11 @@ static int decode_impl(const void* q, const void* k_new, const void* v_new,
                        void* k_ring, void* v_ring, const int32_t* head, const int32_t* fill,
                        const float* pos_bias, const float* scale_embed, const float* head_gain,
                        const int32_t* offsets, int J, int R,
-                       void* out, int S, int H, int D, int dtype, void* stream, bool overlap) {
+                       void* out, int S, int H, int D, int dtype, void* stream, bool overlap, bool interleaved = false) {
     if (!q || !k_new || !v_new || !k_ring || !v_ring || !head || !pos_bias || !out) return DSQG_ERR_NULL_POINTER;
     int rc = check_shape(S, H, 1, D, dtype);
     if (rc) return rc;
-    if (R < 1 || (long long)S * H * R > 0x7fffffffLL) return DSQG_ERR_BAD_SHAPE;
+    if (R < 1 || (long long)S * H * R * (interleaved ? 2 : 1) > 0x7fffffffLL) return DSQG_ERR_BAD_SHAPE;
     Taps t;
     rc = build_taps(offsets, J, &t);
     if (rc) return rc;
@@ -312,6 +312,7 @@ static int decode_impl(const void* q, const void* k_new, const void* v_new,
     a.head = head; a.fill = fill; a.pos_bias = pos_bias; a.scale_embed = scale_embed;
     a.head_gain = head_gain; a.out = out; a.S = S; a.H = H; a.D = D; a.R = R;
     a.scale = 1.0f / sqrtf((float)D);
+    a.ring_stride = interleaved ? 2 * D : D;
     cudaError_t e = launch_decode(a, t, dtype, static_cast<cudaStream_t>(stream), overlap);
     return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
 }
@@ -332,6 +333,40 @@ int dsqg_decode_overlapped(const void* q, const void* k_new, const void* v_new,
                            void* out, int S, int H, int D, int dtype, void* stream) {
     return decode_impl(q, k_new, v_new, k_ring, v_ring, head, fill, pos_bias, scale_embed, head_gain,
                        offsets, J, R, out, S, H, D, dtype, stream, true);
+}
+
+int dsqg_causal_mean(const void* x, void* out, int B, int N, int D, int dtype, int reverse, void* stream) {
+    if (!x || !out) return DSQG_ERR_NULL_POINTER;
+    if (dtype != DSQG_DTYPE_BF16 && dtype != DSQG_DTYPE_F32) return DSQG_ERR_BAD_DTYPE;
+    if (B < 1 || N < 1 || D < 8 || (D % 8) != 0 || B > 65535 || (long long)B * N * D > 0x7fffffffffLL) return DSQG_ERR_BAD_SHAPE;
+    if (misaligned16(x) || misaligned16(out)) return DSQG_ERR_MISALIGNED;
+    cudaError_t e = launch_causal_mean(x, out, B, N, D, dtype, reverse != 0, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
+}
+
+int dsqg_decode_kv(const void* q, const void* k_new, const void* v_new, void* kv_ring,
+                   const int32_t* head, const int32_t* fill,
+                   const float* pos_bias, const float* scale_embed, const float* head_gain,
+                   const int32_t* offsets, int J, int R,
+                   void* out, int S, int H, int D, int dtype, void* stream, int overlapped) {
+    if (!kv_ring) return DSQG_ERR_NULL_POINTER;
+    if (check_shape(S, H, 1, D, dtype)) return check_shape(S, H, 1, D, dtype);
+    char* v_ring = static_cast<char*>(kv_ring) + (size_t)D * (dtype == DSQG_DTYPE_BF16 ? 2 : 4);
+    return decode_impl(q, k_new, v_new, kv_ring, v_ring, head, fill, pos_bias, scale_embed, head_gain,
+                       offsets, J, R, out, S, H, D, dtype, stream, overlapped != 0, true);
+}
+
+int dsqg_ring_prefill_kv(const void* k, const void* v, void* kv_ring,
+                         int32_t* head, int32_t* fill, int S, int H, int N, int D, int R, int dtype, void* stream) {
+    if (!k || !v || !kv_ring || !head || !fill) return DSQG_ERR_NULL_POINTER;
+    int rc = check_shape(S, H, N, D, dtype);
+    if (rc) return rc;
+    if (R < 1 || (long long)S * H * R * 2 > 0x7fffffffLL) return DSQG_ERR_BAD_SHAPE;
+    if (misaligned16(k) || misaligned16(v) || misaligned16(kv_ring)) return DSQG_ERR_MISALIGNED;
+    char* v_ring = static_cast<char*>(kv_ring) + (size_t)D * (dtype == DSQG_DTYPE_BF16 ? 2 : 4);
+    cudaError_t e = launch_ring_prefill(k, v, kv_ring, v_ring, head, fill, S, H, N, D, R, dtype,
+                                        static_cast<cudaStream_t>(stream), true);
+    return e == cudaSuccess ? DSQG_OK : cuda_fail(e);
 }
 
 int dsqg_ring_prefill(const void* k, const void* v, void* k_ring, void* v_ring,

@@ -71,6 +71,7 @@ struct DecodeArgs {
     void* out;
     int S, H, D, R;
     float scale;
+    int ring_stride;   // elements between two slots of a ring: D for separate K and V rings [S,H,R,D], 2 D for one ring [S,H,R,2,D]
 };
 
 // Launchers (defined in the .cu files; return a cudaError_t from the launch).
@@ -81,8 +82,9 @@ cudaError_t launch_bwd_generic(const BwdArgs& a, const Taps& t, int dtype, cudaS
 cudaError_t launch_reduce_params(const BwdArgs& a, int J, cudaStream_t s);
 cudaError_t launch_decode(const DecodeArgs& a, const Taps& t, int dtype, cudaStream_t s, bool overlap);
 cudaError_t launch_ring_prefill(const void* k, const void* v, void* k_ring, void* v_ring, int32_t* head, int32_t* fill,
-                                int S, int H, int N, int D, int R, int dtype, cudaStream_t s);
+                                int S, int H, int N, int D, int R, int dtype, cudaStream_t s, bool interleaved = false);
 
+cudaError_t launch_causal_mean(const void* x, void* out, int B, int N, int D, int dtype, bool reverse, cudaStream_t s);
 cudaError_t launch_gate_bwd(const void* dy, const void* y, const void* gate, long long sb, long long sh, long long sn,
                             void* dout, void* dgate, float* delta, int B, int H, int N, int D, cudaStream_t s);
 cudaError_t launch_fwd_mma(const FwdArgs& a, const Taps& t, cudaStream_t s);

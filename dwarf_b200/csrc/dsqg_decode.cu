@@ -117,15 +117,16 @@ decode_kernel(const DecodeArgs a, const Taps t) {
     const T* q = static_cast<const T*>(a.q) + (size_t)sh * D;
     const T* kn = static_cast<const T*>(a.k_new) + (size_t)sh * D;
     const T* vn = static_cast<const T*>(a.v_new) + (size_t)sh * D;
-    T* kr = static_cast<T*>(a.k_ring) + (size_t)sh * a.R * D;
-    T* vr = static_cast<T*>(a.v_ring) + (size_t)sh * a.R * D;
+    const int RS = a.ring_stride;                           // elements between two slots of a ring: D, or 2 D when K and V interleave
+    T* kr = static_cast<T*>(a.k_ring) + (size_t)sh * a.R * RS;
+    T* vr = static_cast<T*>(a.v_ring) + (size_t)sh * a.R * RS;
 
     float qx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (active) load8(q + d0, qx);
     if (g == 0 && active) {          // store the new token in the ring (bf16->fp32->bf16 is exact)
         float t8[8];
-        load8(kn + d0, t8); store8(kr + (size_t)head * D + d0, t8);
-        load8(vn + d0, t8); store8(vr + (size_t)head * D + d0, t8);
+        load8(kn + d0, t8); store8(kr + (size_t)head * RS + d0, t8);
+        load8(vn + d0, t8); store8(vr + (size_t)head * RS + d0, t8);
     }
     TapState st;
     const int rounds = (t.J + GROUPS - 1) / GROUPS;
@@ -143,8 +144,8 @@ decode_kernel(const DecodeArgs a, const Taps t) {
             if (j < t.J && delta < fill && active) {
                 // taps with delta == 0 read k_new / v_new directly, so nothing depends on the ring
                 // store above becoming visible inside the kernel
-                kraw[r].load(delta == 0 ? kn + d0 : kr + (size_t)slot * D + d0);
-                vraw[r].load(delta == 0 ? vn + d0 : vr + (size_t)slot * D + d0);
+                kraw[r].load(delta == 0 ? kn + d0 : kr + (size_t)slot * RS + d0);
+                vraw[r].load(delta == 0 ? vn + d0 : vr + (size_t)slot * RS + d0);
             }
         }
         // ---- scores and online softmax over this lane group's taps
@@ -200,8 +201,9 @@ decode_1pass_kernel(const DecodeArgs a, const Taps t) {
     const int fill = a.fill ? a.fill[s] : a.R;
     const T* kn = static_cast<const T*>(a.k_new) + (size_t)sh * D;
     const T* vn = static_cast<const T*>(a.v_new) + (size_t)sh * D;
-    T* kr = static_cast<T*>(a.k_ring) + (size_t)sh * a.R * D;
-    T* vr = static_cast<T*>(a.v_ring) + (size_t)sh * a.R * D;
+    const int RS = a.ring_stride;
+    T* kr = static_cast<T*>(a.k_ring) + (size_t)sh * a.R * RS;
+    T* vr = static_cast<T*>(a.v_ring) + (size_t)sh * a.R * RS;
 
     // ---- request every row of the step
     Raw8<T> vraw[VREG > 0 ? VREG : 1];
@@ -215,8 +217,8 @@ decode_1pass_kernel(const DecodeArgs a, const Taps t) {
         const bool on = j < t.J && delta < fill && active;
         if (PDL && j == 0 && delta == 0) continue;       // the new token itself: after the wait
         // the tap with delta == 0 reads k_new / v_new, so nothing waits for the ring store below
-        const T* ksrc = delta == 0 ? kn + d0 : kr + (size_t)slot * D + d0;
-        const T* vsrc = delta == 0 ? vn + d0 : vr + (size_t)slot * D + d0;
+        const T* ksrc = delta == 0 ? kn + d0 : kr + (size_t)slot * RS + d0;
+        const T* vsrc = delta == 0 ? vn + d0 : vr + (size_t)slot * RS + d0;
         if (on) cp_async16(&k_sm[warp][r][lane], ksrc); else k_sm[warp][r][lane] = zero4;
         if (r < VSM) {
             if (on) cp_async16(&v_sm[warp][r][lane], vsrc); else v_sm[warp][r][lane] = zero4;
@@ -241,8 +243,8 @@ decode_1pass_kernel(const DecodeArgs a, const Taps t) {
     float qx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (active) load8(static_cast<const T*>(a.q) + (size_t)sh * D + d0, qx);
     if (g == 0 && active) {          // store the new token in the ring
-        *reinterpret_cast<uint4*>(kr + (size_t)head * D + d0) = *reinterpret_cast<const uint4*>(kn + d0);
-        *reinterpret_cast<uint4*>(vr + (size_t)head * D + d0) = *reinterpret_cast<const uint4*>(vn + d0);
+        *reinterpret_cast<uint4*>(kr + (size_t)head * RS + d0) = *reinterpret_cast<const uint4*>(kn + d0);
+        *reinterpret_cast<uint4*>(vr + (size_t)head * RS + d0) = *reinterpret_cast<const uint4*>(vn + d0);
     }
     cp_async_wait_all();
 
@@ -315,8 +317,10 @@ cudaError_t decode_launch(const DecodeArgs& a, const Taps& t, cudaStream_t s, bo
 // Ring prefill: copies the last min(N, R) positions of K and V from the training layout
 // [S,H,N,D] into the rings [S,H,R,D] so that position p lands in slot p mod R, and sets
 // head[s] = (N-1) mod R, fill[s] = min(N, R).  One 16-byte chunk per thread.
+// ring_chunks: 16-byte chunks between two slots of a ring (chunks_per_row, or twice that when K and V interleave).
 __global__ void ring_prefill_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, uint4* k_ring, uint4* v_ring,
-                                    int32_t* head, int32_t* fill, int SH, int H, int N, int R, int chunks_per_row) {
+                                    int32_t* head, int32_t* fill, int SH, int H, int N, int R, int chunks_per_row,
+                                    int ring_chunks) {
     const int keep = N < R ? N : R;
     const long long total = (long long)SH * keep * chunks_per_row;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -327,7 +331,7 @@ __global__ void ring_prefill_kernel(const uint4* __restrict__ k, const uint4* __
         const int p = N - keep + j;                       // position in the sequence
         const int slot = p % R;
         const long long src = ((long long)sh * N + p) * chunks_per_row + c;
-        const long long dst = ((long long)sh * R + slot) * chunks_per_row + c;
+        const long long dst = ((long long)sh * R + slot) * ring_chunks + c;
         k_ring[dst] = k[src];
         v_ring[dst] = v[src];
     }
@@ -336,7 +340,7 @@ __global__ void ring_prefill_kernel(const uint4* __restrict__ k, const uint4* __
 }
 
 cudaError_t launch_ring_prefill(const void* k, const void* v, void* k_ring, void* v_ring, int32_t* head, int32_t* fill,
-                                int S, int H, int N, int D, int R, int dtype, cudaStream_t s) {
+                                int S, int H, int N, int D, int R, int dtype, cudaStream_t s, bool interleaved) {
     const int chunks = D * (dtype == DSQG_DTYPE_BF16 ? 2 : 4) / 16;
     const long long total = (long long)S * H * (N < R ? N : R) * chunks;
     long long blocks = (total + 255) / 256;
@@ -344,7 +348,7 @@ cudaError_t launch_ring_prefill(const void* k, const void* v, void* k_ring, void
     if (blocks > 148 * 16) blocks = 148 * 16;
     ring_prefill_kernel<<<(int)blocks, 256, 0, s>>>(static_cast<const uint4*>(k), static_cast<const uint4*>(v),
                                                   static_cast<uint4*>(k_ring), static_cast<uint4*>(v_ring), head, fill,
-                                                  S * H, H, N, R, chunks);
+                                                  S * H, H, N, R, chunks, interleaved ? 2 * chunks : chunks);
     return cudaGetLastError();
 }
 

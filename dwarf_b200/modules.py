@@ -19,7 +19,7 @@ from typing import Optional, Sequence
 import torch
 import torch.nn as nn
 
-from .ops import ALL_OFFSETS, dsqg_attention, dsqg_attention_packed, packed_path_available
+from .ops import ALL_OFFSETS, causal_mean, dsqg_attention, dsqg_attention_packed, packed_path_available
 
 
 def dsqg_attention_v2(q, k, v, pos_bias, offsets: Sequence[int] = ALL_OFFSETS):
@@ -179,3 +179,29 @@ class DSQGAttentionQW(_DSQGAttentionBase):
     def __init__(self, embedding_dim, num_heads, seq_len=2048, dropout=0.1, offsets=None):
         super().__init__(embedding_dim, num_heads, seq_len, offsets, dropout, gate_bias=0.0,
                          with_scale_embed=True, with_if_gain=True, offsets_in_state_dict=False)
+
+
+class InterferenceInjection(nn.Module):
+    """The K/V deltas of the condU "interference" block (train/train_2048_condU.py:277-295): a
+    gated causal running mean of the normalised block input, projected to key and value space.
+    Parameter names match the reference block (`inter_norm`, `inter_gate`, `inter_k_proj`,
+    `inter_v_proj`).  forward(x [B,N,D]) returns (k_delta, v_delta), each [B,H,N,HD], ready for
+    `DSQGAttentionQW.forward(x, kv_inject=...)`; the pooling runs as one scan kernel."""
+
+    def __init__(self, embedding_dim, num_heads):
+        super().__init__()
+        self.num_heads, self.head_dim = num_heads, embedding_dim // num_heads
+        self.inter_norm = nn.LayerNorm(embedding_dim)
+        self.inter_gate = nn.Linear(embedding_dim, embedding_dim)
+        self.inter_k_proj = nn.Linear(embedding_dim, embedding_dim)
+        self.inter_v_proj = nn.Linear(embedding_dim, embedding_dim)
+
+    def forward(self, x):
+        xi = self.inter_norm(x)
+        B, N, D = xi.shape
+        H, HD = self.num_heads, self.head_dim
+        pool = causal_mean(xi)                                  # xi.cumsum(dim=1) / counts
+        inter = torch.sigmoid(self.inter_gate(xi)) * pool
+        k_delta = self.inter_k_proj(inter).view(B, N, H, HD).permute(0, 2, 1, 3)
+        v_delta = self.inter_v_proj(inter).view(B, N, H, HD).permute(0, 2, 1, 3)
+        return k_delta, v_delta

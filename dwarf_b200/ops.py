@@ -141,6 +141,42 @@ class DSQGFunction(torch.autograd.Function):
                 None if dse is None else dse.to(se_dt), None)
 
 
+class CausalMeanFunction(torch.autograd.Function):
+    """pool[b,n,:] = mean(x[b,0..n,:]) with autograd (the backward is the kernel's reverse mode)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        if not x.is_cuda or x.dim() != 3 or x.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("causal_mean: x must be a CUDA [B,N,D] tensor in bfloat16 or float32")
+        x = x.contiguous()
+        ctx.meta = tuple(x.shape)
+        return CausalMeanFunction._run(x, 0)
+
+    @staticmethod
+    def backward(ctx, dout):
+        return CausalMeanFunction._run(dout.contiguous(), 1)
+
+    @staticmethod
+    def _run(x, reverse):
+        lib = _lib.load()
+        B, N, D = x.shape
+        out = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            stream = torch.cuda.current_stream(x.device).cuda_stream
+            _lib.check(lib.dsqg_causal_mean(x.data_ptr(), out.data_ptr(), B, N, D, _dtype_code(x), reverse, stream),
+                       "dsqg_causal_mean")
+        return out
+
+
+def causal_mean(x):
+    """Causal running mean over the sequence dimension of x [B,N,D] (bf16 or fp32; other dtypes are
+    computed in fp32 and cast back): the pooling of the reference's interference block,
+    `x.cumsum(dim=1) / counts` (train/train_2048_condU.py:289-292), as one kernel."""
+    if x.dtype in (torch.bfloat16, torch.float32):
+        return CausalMeanFunction.apply(x)
+    return CausalMeanFunction.apply(x.float()).to(x.dtype)
+
+
 class DSQGPackedFunction(torch.autograd.Function):
     """DSQG on the un-permuted output of a fused qkv projection, with a token-major result.
 

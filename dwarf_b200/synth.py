@@ -108,7 +108,9 @@ def make_decode_inputs(cfg: DecodeConfig, device="cpu", S: Optional[int] = None,
     gain = torch.rand(cfg.H, generator=g) * 0.4 + 0.8
     head = torch.randint(0, cfg.R, (S,), generator=g, dtype=torch.int32)
     mk = lambda *shape: torch.randn(*shape, generator=g).to(cfg.dtype).to(device)
-    if rings_on is not None:
+    if rings_on == "meta":            # the caller draws the rings itself
+        ring = lambda: None
+    elif rings_on is not None:
         gd = torch.Generator(device=rings_on).manual_seed(cfg.seed + 1)
         ring = lambda: torch.randn(L, S, cfg.H, cfg.R, cfg.D, generator=gd, device=rings_on, dtype=cfg.dtype)
     else:

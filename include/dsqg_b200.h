@@ -224,6 +224,15 @@ int dsqg_bwd_strided(const void* q, const void* k, const void* v, const dsqg_str
 int dsqg_gate_bwd(const void* dy, const void* y, const void* gate, const dsqg_strides* strides,
                   void* dout, void* dgate, float* delta, int B, int H, int N, int D, void* stream);
 
+/* Causal mean along the sequence of a contiguous [B,N,D] tensor (bf16 or fp32, D a multiple of 8):
+ *   reverse == 0:  out[b,n,:] = (x[b,0,:] + ... + x[b,n,:]) / (n + 1)
+ *   reverse != 0:  out[b,n,:] = sum_{m >= n} x[b,m,:] / (m + 1)        (the adjoint: its backward pass)
+ * Replaces: the pooling of the condU "interference" block that feeds the K/V injection of its DSQG
+ *   layer, `pool = xi.cumsum(dim=1) / counts` (DWARF train/train_2048_condU.py:289-292), and the
+ *   autograd backward of those two PyTorch ops.  fp32 accumulation, fixed order of additions, no
+ *   scratch memory; out may not alias x. */
+int dsqg_causal_mean(const void* x, void* out, int B, int N, int D, int dtype, int reverse, void* stream);
+
 /* Single-token decode over a circular K/V ring buffer.
  * Replaces: nothing executable -- the reference only describes the O(1) cache in prose
  *   (DWARF README.md:175-179; generate() in train/train_2048_condU.py:463-487 re-runs the
@@ -238,6 +247,20 @@ int dsqg_decode(const void* q, const void* k_new, const void* v_new,
                 const float* pos_bias, const float* scale_embed, const float* head_gain,
                 const int32_t* offsets, int J, int R,
                 void* out, int S, int H, int D, int dtype, void* stream);
+
+/* dsqg_decode / dsqg_ring_prefill over ONE ring per layer that holds the key and the value of a slot
+ * side by side: kv_ring [S,H,R,2,D] (slot-major; element 0 of the pair is the key row, element 1 the
+ * value row).  A tap is then one contiguous read of 2*D elements and a step touches half as many
+ * memory pages as with two separate rings.  Same semantics, arguments and results as dsqg_decode
+ * (overlapped != 0: as dsqg_decode_overlapped) and dsqg_ring_prefill otherwise.
+ * Replaces: nothing executable (see dsqg_decode). */
+int dsqg_decode_kv(const void* q, const void* k_new, const void* v_new, void* kv_ring,
+                   const int32_t* head, const int32_t* fill,
+                   const float* pos_bias, const float* scale_embed, const float* head_gain,
+                   const int32_t* offsets, int J, int R,
+                   void* out, int S, int H, int D, int dtype, void* stream, int overlapped);
+int dsqg_ring_prefill_kv(const void* k, const void* v, void* kv_ring,
+                         int32_t* head, int32_t* fill, int S, int H, int N, int D, int R, int dtype, void* stream);
 
 /* dsqg_decode launched so that it overlaps the kernel ahead of it in the stream (programmatic
  * dependent launch).  Same arguments and results as dsqg_decode.

@@ -12,13 +12,29 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
+LAYOUT = "separate"
+
+
+@pytest.fixture(autouse=True, params=["separate", "interleaved"])
+def ring_layout(request):
+    """Every test runs over two rings [S,H,R,D] (dsqg_decode) and over one ring that holds key and value
+    of a slot side by side, [S,H,R,2,D] (dsqg_decode_kv)."""
+    global LAYOUT
+    LAYOUT = request.param
+    yield request.param
+    LAYOUT = "separate"
+
+
 def run_cuda(q, kn, vn, kr, vr, head, pb, gain, offsets, fill=None, se=None, dtype=torch.bfloat16):
     to = lambda t: t.to(DEV, dtype).contiguous()
+    args = (head.to(DEV), pb.to(DEV), None if gain is None else gain.to(DEV), None if se is None else se.to(DEV),
+            offsets, None if fill is None else fill.to(DEV))
+    if LAYOUT == "interleaved":
+        kv = torch.stack([to(kr), to(vr)], dim=-2).contiguous()
+        out = dwarf_b200.dsqg_decode_step_kv(to(q), to(kn), to(vn), kv, *args)
+        return out.float().cpu(), kv[..., 0, :].float().cpu(), kv[..., 1, :].float().cpu()
     krd, vrd = to(kr), to(vr)
-    out = dwarf_b200.dsqg_decode_step(to(q), to(kn), to(vn), krd, vrd, head.to(DEV), pb.to(DEV),
-                                      None if gain is None else gain.to(DEV),
-                                      None if se is None else se.to(DEV), offsets,
-                                      None if fill is None else fill.to(DEV))
+    out = dwarf_b200.dsqg_decode_step(to(q), to(kn), to(vn), krd, vrd, *args)
     return out.float().cpu(), krd.float().cpu(), vrd.float().cpu()
 
 
@@ -89,7 +105,7 @@ def test_decode_reproduces_training_forward_token_by_token():
     pb = torch.randn(len(offsets), H, generator=g).to(DEV)
     gain = (torch.rand(H, generator=g) + 0.5).to(DEV)
     full = dwarf_b200.dsqg_attention(q, k, v, pb, gain, None, offsets).float()
-    cache = dwarf_b200.DSQGRingCache(1, S, H, D, offsets)
+    cache = dwarf_b200.DSQGRingCache(1, S, H, D, offsets, interleaved=LAYOUT == "interleaved")
     assert cache.R == 49
     for t in range(N):
         cache.advance()
@@ -107,7 +123,7 @@ def test_prefill_then_decode_continues_the_sequence(N):
     q, k, v = (bf16v(S, H, N + 1, D, gen=g).to(DEV, torch.bfloat16) for _ in range(3))
     pb = torch.randn(len(offsets), H, generator=g).to(DEV)
     full = dwarf_b200.dsqg_attention(q, k, v, pb, None, None, offsets).float()
-    cache = dwarf_b200.DSQGRingCache(1, S, H, D, offsets)
+    cache = dwarf_b200.DSQGRingCache(1, S, H, D, offsets, interleaved=LAYOUT == "interleaved")
     cache.prefill(0, k[:, :, :N].contiguous(), v[:, :, :N].contiguous())
     assert int(cache.head[0]) == (N - 1) % cache.R and int(cache.fill[0]) == min(N, cache.R)
     cache.advance()
@@ -145,6 +161,13 @@ def test_overlapped_launch_equals_plain_launch_over_a_stack_of_layers(D, J):
     pb = synth.log_linear_pos_bias(offsets, H).to(DEV)
 
     def run(overlap, kr, vr, out):
+        if LAYOUT == "interleaved":       # one ring per layer; the results are copied back into kr, vr for the comparison
+            kv = torch.stack([kr, vr], dim=-2).contiguous()
+            for l in range(L):
+                dwarf_b200.dsqg_decode_step_kv(q[l], kn[l], vn[l], kv[l], head, pb, None, None, offsets,
+                                               fill, out[l], overlap=overlap)
+            kr.copy_(kv[..., 0, :]); vr.copy_(kv[..., 1, :])
+            return
         for l in range(L):
             dwarf_b200.dsqg_decode_step(q[l], kn[l], vn[l], kr[l], vr[l], head, pb, None, None, offsets,
                                         fill, out[l], overlap=overlap)

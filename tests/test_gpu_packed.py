@@ -130,3 +130,51 @@ def test_strided_entries_refuse_what_they_cannot_take():
     assert lib.dsqg_fwd_strided(*args(ok, 80, 0)) == -8              # no tensor-core kernel for this width
     assert lib.dsqg_fwd_strided(*args(ok, 32, 1)) == -8              # fp32
     assert not dwarf_b200.packed_path_available(80, O.OFFSETS_43)
+
+
+# ------------------------------------------------------------------ causal mean (interference pooling)
+@pytest.mark.parametrize("shape", [(2, 2048, 256), (3, 777, 64), (1, 1, 8), (2, 33, 40), (1, 4096, 768)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_causal_mean_forward_and_backward_vs_float64(shape, dtype):
+    """out[n] = mean(x[0..n]) and its adjoint against float64 numpy (the reference computes
+    `xi.cumsum(dim=1) / counts`, train/train_2048_condU.py:289-292)."""
+    import numpy as np
+    B, N, D = shape
+    g = torch.Generator().manual_seed(N + D)
+    x = torch.randn(B, N, D, generator=g).to(dtype)
+    dy = torch.randn(B, N, D, generator=g).to(dtype)
+    counts = np.arange(1, N + 1, dtype=np.float64)[None, :, None]
+    ref = np.cumsum(x.double().numpy(), axis=1) / counts
+    ref_dx = np.flip(np.cumsum(np.flip(dy.double().numpy() / counts, axis=1), axis=1), axis=1)
+    xd = x.to("cuda:0").requires_grad_(True)
+    y = dwarf_b200.causal_mean(xd)
+    y.backward(dy.to("cuda:0"))
+    tol = 1e-5 if dtype == torch.float32 else 2.0 ** -8
+    for got, want, nm in ((y.detach(), ref, "out"), (xd.grad, ref_dx, "dx")):
+        err = np.abs(got.double().cpu().numpy() - want)
+        assert (err <= tol * (np.abs(want) + 1.0)).all(), (nm, err.max())
+    # fp16 activations (the reference's autocast default) go through fp32
+    assert dwarf_b200.causal_mean(x.half().to("cuda:0")).dtype == torch.float16
+
+
+def test_interference_injection_feeds_kv_inject_like_the_reference_block():
+    """The reference's interference block (train/train_2048_condU.py:283-297) written with PyTorch's
+    cumsum against InterferenceInjection + DSQGAttentionQW(kv_inject=...): same output, same gradient."""
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(4)
+    E, H, N = 64, 2, 150
+    inj = dwarf_b200.InterferenceInjection(E, H).to(dev)
+    attn = dwarf_b200.DSQGAttentionQW(E, H, dropout=0.0).to(dev)
+    x = torch.randn(2, N, E, device=dev, requires_grad=True)
+
+    def reference_deltas(x):
+        xi = inj.inter_norm(x)
+        counts = torch.arange(1, N + 1, device=dev, dtype=xi.dtype).view(1, N, 1)
+        pool = xi.cumsum(dim=1) / counts
+        inter = torch.sigmoid(inj.inter_gate(xi)) * pool
+        f = lambda t: t.view(2, N, H, E // H).permute(0, 2, 1, 3).contiguous()
+        return f(inj.inter_k_proj(inter)), f(inj.inter_v_proj(inter))
+
+    ya = attn(x, kv_inject=inj(x)); ya.sum().backward(); ga = x.grad.clone(); x.grad = None
+    yb = attn(x, kv_inject=reference_deltas(x)); yb.sum().backward(); gb = x.grad.clone()
+    assert (ya - yb).abs().max().item() < 2e-2 and (ga - gb).abs().max().item() < 2e-2 * max(1.0, gb.abs().max().item())
