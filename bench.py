@@ -549,6 +549,23 @@ def run_train_workload(args, rank, local_rank, world):
     e1.record(stream)
     torch.cuda.synchronize(); ddist.barrier()
     ms = ddist.max_over_ranks(e0.elapsed_time(e1), dev if world > 1 else "cpu") / args.steps
+    allreduce = None
+    if world > 1:
+        # the same steps with DDP's gradient all-reduce switched off (no_sync): the difference is what the
+        # all-reduce adds to the step after its overlap with the backward pass
+        with model.no_sync():
+            for _ in range(2):
+                step()
+            ddist.barrier(); torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(args.steps):
+                step()
+            e1.record(stream)
+            torch.cuda.synchronize(); ddist.barrier()
+        ms_ns = ddist.max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
+        grad_bytes = sum(p.numel() * 4 for p in model.parameters() if p.requires_grad)
+        allreduce = {"ms_per_step_without_allreduce": ms_ns, "exposed_ms": ms - ms_ns, "share_of_step": (ms - ms_ns) / ms,
+                     "gradient_bytes": grad_bytes, "backend": "nccl"}
     clocks = sampler.stop() if rank == 0 else None
     tokens = B * N * world
     val = tokens / (ms * 1e-3)
@@ -567,6 +584,7 @@ def run_train_workload(args, rank, local_rank, world):
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": B * (N + 1) * 8, "d2h_bytes_per_step": 4,
                 "note": "the timed step already starts from pinned host token ids and ends with the loss on the host"},
         "gpu_launches": 3 * 5 * args.steps,      # DSQG forward + dQ + dK/dV kernels of the 5 DSQG layers (others are library GEMMs)
+        "allreduce": allreduce,
         "clocks": clocks,
     }
 
