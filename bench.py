@@ -294,6 +294,19 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     e1.record(stream)
     torch.cuda.synchronize(); ddist.barrier()
     e2e_ms = ddist.max_over_ranks(e0.elapsed_time(e1), dev if world > 1 else "cpu") / e2e_steps
+    # what the host side delivers when every rank copies at the same time, one direction at a time:
+    # the e2e figure is bounded by these (4 T bytes each way per step)
+    pcie = {}
+    for name, src, dst in (("h2d", host["q"], q), ("d2h", q, res_host["out"])):
+        ddist.barrier(); torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(10):
+            dst.copy_(src, non_blocking=True)
+        e1.record(stream)
+        torch.cuda.synchronize(); ddist.barrier()
+        gbs = 10 * src.numel() * src.element_size() / (e0.elapsed_time(e1) * 1e-3) / 1e9
+        pcie[name + "_gbs_per_gpu_min"] = -ddist.max_over_ranks(-gbs, dev if world > 1 else "cpu")
+        pcie[name + "_gbs_all_gpus"] = ddist.sum_over_ranks(gbs, dev if world > 1 else "cpu")
     clocks = sampler.stop() if rank == 0 else None
 
     T = op_bytes(cfg)
@@ -321,7 +334,7 @@ def run_op_workload(args, cfg, rank, local_rank, world):
                                    else f"batch replicated x{world}, no collective")},
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": 4 * T, "d2h_bytes_per_step": 4 * T, "ms_per_step": e2e_ms,
-                "steps": e2e_steps},
+                "steps": e2e_steps, "host_copy_bandwidth": pcie},
         "gpu_launches": ((3 if args.kernel_path in (0, 2) else 4) + (2 if se is not None and args.kernel_path in (0, 2) else 0)) * args.steps,   # other paths reduce in a 4th kernel
         "roofline": {"bound": "hbm", "kernel": names[top], "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": ncu_traffic[top], "traffic_from": (
