@@ -143,3 +143,50 @@ def test_tensor_core_path_query_and_scaled_entry_checks(lib):
                                             _fake(5), _fake(6), _fake(7), _fake(10), _fake(11), _fake(12),
                                             _fake(13), None, None, _fake(20), 1 << 20, 1, 1, 16, 32, 0, None, scale)
     assert bwd(0.0) == -8 and bwd(float("nan")) == -8
+
+
+def test_strided_gate_scan_and_interleaved_ring_argument_errors(lib):
+    """The entries added for caller layouts, the gate backward, the causal mean and the one-ring decode:
+    every bad argument is a status on the host, nothing is launched."""
+    off, J = _off((0, 1, 2, 8))
+    good = _lib.Strides(3 * 2 * 32 * 16, 32, 3 * 2 * 32)
+    odd = _lib.Strides(3 * 2 * 32 * 16, 32, 3 * 2 * 32 + 4)           # not a multiple of 8 elements
+    neg = _lib.Strides(-8, 32, 192)
+
+    def fwd(st_in=good, st_out=good, q=_fake(1), D=32, dtype=0, gate=None, scale=0.0):
+        return lib.dsqg_fwd_strided(q, _fake(2), _fake(3), st_in, _fake(4), None, off, J, _fake(5), st_out, gate,
+                                    _fake(6), 1, 2, 16, D, dtype, None, scale)
+    assert fwd(st_in=None) == -1 and fwd(st_out=None) == -1 and fwd(q=None) == -1
+    assert fwd(st_in=odd) == -5 and fwd(st_out=neg) == -5 and fwd(gate=_fake(9) + 2) == -5
+    assert fwd(D=80) == -8 and fwd(dtype=1) == -8 and fwd(D=12) == -2
+    assert fwd(scale=float("inf")) == -8
+
+    need = lib.dsqg_bwd_scratch_bytes(J, 1, 2, 16, 32, 0)
+
+    def bwd(st_in=good, st_out=good, scratch=_fake(20), nbytes=need, D=32, dq=_fake(10)):
+        return lib.dsqg_bwd_strided(_fake(1), _fake(2), _fake(3), st_in, _fake(4), None, off, J, _fake(5), _fake(6),
+                                    _fake(7), st_out, None, dq, _fake(11), _fake(12), _fake(13), None,
+                                    scratch, nbytes, 1, 2, 16, D, 0, None, 0.0)
+    assert bwd(st_in=None) == -1 and bwd(dq=None) == -1 and bwd(scratch=None) == -1
+    assert bwd(st_out=odd) == -5 and bwd(nbytes=need - 1) == -6 and bwd(D=80) == -8
+
+    gate = lambda **kw: lib.dsqg_gate_bwd(kw.get("dy", _fake(1)), _fake(2), _fake(3), kw.get("st", good), _fake(4),
+                                          _fake(5), kw.get("delta", _fake(6)), 1, 2, 16, kw.get("D", 32), None)
+    assert gate(dy=None) == -1 and gate(st=None) == -1 and gate(delta=None) == -1
+    assert gate(st=odd) == -5 and gate(dy=_fake(1) + 8) == -5 and gate(D=12) == -2
+
+    mean = lambda **kw: lib.dsqg_causal_mean(kw.get("x", _fake(1)), kw.get("out", _fake(2)), kw.get("B", 2), kw.get("N", 16),
+                                             kw.get("D", 64), kw.get("dtype", 0), 0, None)
+    assert mean(x=None) == -1 and mean(out=None) == -1 and mean(dtype=3) == -4
+    assert mean(D=12) == -2 and mean(N=0) == -2 and mean(B=70000) == -2 and mean(x=_fake(1) + 4) == -5
+
+    off4, J4 = _off((0, 1, 2, 5))
+    dec = lambda **kw: lib.dsqg_decode_kv(_fake(1), _fake(2), _fake(3), kw.get("kv", _fake(4)), kw.get("head", _fake(8)), None,
+                                          _fake(6), None, None, off4, J4, kw.get("R", 6), _fake(7), kw.get("S", 2), 2,
+                                          kw.get("D", 64), 0, None, 0)
+    assert dec(kv=None) == -1 and dec(head=None) == -1 and dec(R=5) == -3 and dec(D=12) == -2 and dec(S=0) == -2
+    assert dec(kv=_fake(4) + 8) == -5
+    pre = lambda **kw: lib.dsqg_ring_prefill_kv(kw.get("k", _fake(1)), _fake(2), kw.get("kv", _fake(3)), _fake(5), _fake(6),
+                                                2, 2, kw.get("N", 8), kw.get("D", 64), kw.get("R", 16), 0, None)
+    assert pre(k=None) == -1 and pre(kv=None) == -1 and pre(N=0) == -2 and pre(R=0) == -2 and pre(kv=_fake(3) + 4) == -5
+    assert lib.dsqg_test_wait_timeout(0, None) == -8 and lib.dsqg_test_wait_timeout(3 * 10 ** 9, None) == -8
