@@ -178,3 +178,39 @@ def test_interference_injection_feeds_kv_inject_like_the_reference_block():
     ya = attn(x, kv_inject=inj(x)); ya.sum().backward(); ga = x.grad.clone(); x.grad = None
     yb = attn(x, kv_inject=reference_deltas(x)); yb.sum().backward(); gb = x.grad.clone()
     assert (ya - yb).abs().max().item() < 2e-2 and (ga - gb).abs().max().item() < 2e-2 * max(1.0, gb.abs().max().item())
+
+
+def test_strided_entries_take_any_row_layouts_not_only_the_packed_one():
+    """q, k, v as three separate token-major tensors [B,N,H,D] and a head-major result [B,H,N,D]
+    (different strides for inputs and output), straight through the C ABI: bitwise the contiguous kernels."""
+    from dwarf_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    B, N, H, D = 2, 257, 3, 64
+    offsets = O.OFFSETS_44
+    g = torch.Generator().manual_seed(21)
+    q, k, v = ((torch.randn(B, N, H, D, generator=g) * 0.5).bfloat16().to(dev) for _ in range(3))      # token-major
+    dout = torch.randn(B, H, N, D, generator=g).bfloat16().to(dev)                                      # head-major
+    pb = (synth.log_linear_pos_bias(offsets, H)).to(dev)
+    off, J = _lib.offsets_array(offsets)
+    st = torch.cuda.current_stream().cuda_stream
+    tok, head = _lib.Strides(N * H * D, D, H * D), _lib.Strides(H * N * D, N * D, D)
+    out = torch.empty(B, H, N, D, device=dev, dtype=torch.bfloat16); lse = torch.empty(B, H, N, device=dev)
+    _lib.check(lib.dsqg_fwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), tok, pb.data_ptr(), None, off, J,
+                                    out.data_ptr(), head, None, lse.data_ptr(), B, H, N, D, 0, st, 0.0), "fwd")
+    dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+    dpb = torch.empty(J, H, device=dev)
+    nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, 0)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    _lib.check(lib.dsqg_bwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), tok, pb.data_ptr(), None, off, J,
+                                    out.data_ptr(), lse.data_ptr(), dout.data_ptr(), head, None,
+                                    dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dpb.data_ptr(), None,
+                                    scratch.data_ptr(), nbytes, B, H, N, D, 0, st, 0.0), "bwd")
+    qc, kc, vc = (t.permute(0, 2, 1, 3).contiguous().requires_grad_(True) for t in (q, k, v))
+    pb2 = pb.clone().requires_grad_(True)
+    ref = dwarf_b200.dsqg_attention(qc, kc, vc, pb2, None, None, offsets)
+    ref.backward(dout)
+    assert torch.equal(out, ref.detach())
+    for got, want in ((dq, qc.grad), (dk, kc.grad), (dv, vc.grad)):
+        assert torch.equal(got, want.permute(0, 2, 1, 3))
+    assert torch.equal(dpb, pb2.grad)
