@@ -44,13 +44,23 @@ struct Lane {
 template <int D>
 __device__ __forceinline__ void diag_fma(float (&acc)[D / 8][4], float x_lo, float x_hi, const RowFrag<D>& f_lo,
                                          const RowFrag<D>& f_hi) {
+    // packed fp32 FMA (fma.rn.f32x2, sm_100): one instruction updates the two accumulators a row has
+    // in an n-tile; measured 1 % off the step against scalar FMAs (cfg1: 284.8 against 287.6 us)
+    unsigned long long xl, xh;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(xl) : "f"(x_lo));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(xh) : "f"(x_hi));
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) {
         const uint32_t u0 = f_lo.r[j], u1 = f_hi.r[j];
-        acc[j][0] = fmaf(x_lo, __uint_as_float(u0 << 16), acc[j][0]);
-        acc[j][1] = fmaf(x_lo, __uint_as_float(u0 & 0xffff0000u), acc[j][1]);
-        acc[j][2] = fmaf(x_hi, __uint_as_float(u1 << 16), acc[j][2]);
-        acc[j][3] = fmaf(x_hi, __uint_as_float(u1 & 0xffff0000u), acc[j][3]);
+        unsigned long long v0, v1, c0, c1;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(v0) : "r"(u0 << 16), "r"(u0 & 0xffff0000u));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(v1) : "r"(u1 << 16), "r"(u1 & 0xffff0000u));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(c0) : "f"(acc[j][0]), "f"(acc[j][1]));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(c1) : "f"(acc[j][2]), "f"(acc[j][3]));
+        asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c0) : "l"(xl), "l"(v0));
+        asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c1) : "l"(xh), "l"(v1));
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[j][0]), "=f"(acc[j][1]) : "l"(c0));
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[j][2]), "=f"(acc[j][3]) : "l"(c1));
     }
 }
 
