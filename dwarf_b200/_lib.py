@@ -46,6 +46,11 @@ _SIGNATURES = {
     "dsqg_bwd_strided": (c_int, [c_void_p] * 3 + [POINTER(Strides)] + [c_void_p] * 2 + [POINTER(c_int32), c_int]
                          + [c_void_p] * 3 + [POINTER(Strides), c_void_p] + [c_void_p] * 5 + [c_void_p, c_size_t]
                          + [c_int] * 5 + [c_void_p, c_float]),
+    "dsqg_fwd_strided_se": (c_int, [c_void_p] * 3 + [POINTER(Strides)] + [c_void_p] * 3 + [POINTER(c_int32), c_int]
+                            + [c_void_p, POINTER(Strides), c_void_p, c_void_p] + [c_int] * 5 + [c_void_p, c_float]),
+    "dsqg_bwd_strided_se": (c_int, [c_void_p] * 3 + [POINTER(Strides)] + [c_void_p] * 3 + [POINTER(c_int32), c_int]
+                            + [c_void_p] * 3 + [POINTER(Strides), c_void_p] + [c_void_p] * 6 + [c_void_p, c_size_t]
+                            + [c_int] * 5 + [c_void_p, c_float]),
     "dsqg_gate_bwd": (c_int, [c_void_p] * 3 + [POINTER(Strides)] + [c_void_p] * 3 + [c_int] * 4 + [c_void_p]),
     "dsqg_bwd_stages": (c_int, [c_void_p] * 3 + [c_void_p] * 3 + [POINTER(c_int32), c_int] + [c_void_p] * 3
                         + [c_void_p] * 3 + [c_void_p] * 3 + [c_void_p, c_size_t] + [c_int] * 5

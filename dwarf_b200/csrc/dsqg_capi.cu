@@ -125,7 +125,7 @@ static int fwd_impl(const void* q, const void* k, const void* v,
         // strided tensors exist for the tensor-core kernels only
         if (!out_st) return DSQG_ERR_NULL_POINTER;
         if (bad_strides(in_st) || bad_strides(out_st) || (gate && misaligned16(gate))) return DSQG_ERR_MISALIGNED;
-        if (scale_embed || !mma_fwd_supported(dtype, D, t, false)) return DSQG_ERR_UNSUPPORTED;
+        if (!mma_fwd_supported(dtype, D, t, scale_embed != nullptr)) return DSQG_ERR_UNSUPPORTED;
         a.strided = 1; a.gate = gate;
         a.in_sb = in_st->batch; a.in_sh = in_st->head; a.in_sn = in_st->row;
         a.out_sb = out_st->batch; a.out_sh = out_st->head; a.out_sn = out_st->row;
@@ -264,7 +264,7 @@ static int bwd_impl(const void* q, const void* k, const void* v,
     if (in_st) {
         if (!out_st) return DSQG_ERR_NULL_POINTER;
         if (bad_strides(in_st) || bad_strides(out_st)) return DSQG_ERR_MISALIGNED;
-        if (scale_embed || !mma_path_supported(dtype, D, t, false)) return DSQG_ERR_UNSUPPORTED;
+        if (!mma_path_supported(dtype, D, t, scale_embed != nullptr)) return DSQG_ERR_UNSUPPORTED;
         a.strided = 1; a.delta_pre = delta_pre;
         a.in_sb = in_st->batch; a.in_sh = in_st->head; a.in_sn = in_st->row;
         a.out_sb = out_st->batch; a.out_sh = out_st->head; a.out_sn = out_st->row;
@@ -286,6 +286,32 @@ int dsqg_bwd_strided(const void* q, const void* k, const void* v, const dsqg_str
     if (scale > 3.0e38f) return DSQG_ERR_UNSUPPORTED;
     return bwd_impl(q, k, v, pos_bias, nullptr, head_gain, offsets, J, out, lse, dout, dq, dk, dv,
                     dpos_bias, nullptr, dhead_gain, scratch, scratch_bytes, B, H, N, D, dtype, stream,
+                    DSQG_BWD_STAGE_ALL, scale, qkv_strides, out_strides, delta_pre);
+}
+
+int dsqg_fwd_strided_se(const void* q, const void* k, const void* v, const dsqg_strides* qkv_strides,
+                        const float* pos_bias, const float* scale_embed, const float* head_gain,
+                        const int32_t* offsets, int J,
+                        void* out, const dsqg_strides* out_strides, const void* gate, float* lse,
+                        int B, int H, int N, int D, int dtype, void* stream, float scale) {
+    if (!qkv_strides || !out_strides || !scale_embed) return DSQG_ERR_NULL_POINTER;
+    if (scale > 3.0e38f) return DSQG_ERR_UNSUPPORTED;
+    return fwd_impl(q, k, v, pos_bias, scale_embed, head_gain, offsets, J, out, lse, B, H, N, D, dtype, stream, scale,
+                    qkv_strides, out_strides, gate);
+}
+
+int dsqg_bwd_strided_se(const void* q, const void* k, const void* v, const dsqg_strides* qkv_strides,
+                        const float* pos_bias, const float* scale_embed, const float* head_gain,
+                        const int32_t* offsets, int J,
+                        const void* out, const float* lse, const void* dout, const dsqg_strides* out_strides,
+                        const float* delta_pre,
+                        void* dq, void* dk, void* dv, float* dpos_bias, float* dscale_embed, float* dhead_gain,
+                        void* scratch, size_t scratch_bytes,
+                        int B, int H, int N, int D, int dtype, void* stream, float scale) {
+    if (!qkv_strides || !out_strides || !scale_embed) return DSQG_ERR_NULL_POINTER;
+    if (scale > 3.0e38f) return DSQG_ERR_UNSUPPORTED;
+    return bwd_impl(q, k, v, pos_bias, scale_embed, head_gain, offsets, J, out, lse, dout, dq, dk, dv,
+                    dpos_bias, dscale_embed, dhead_gain, scratch, scratch_bytes, B, H, N, D, dtype, stream,
                     DSQG_BWD_STAGE_ALL, scale, qkv_strides, out_strides, delta_pre);
 }
 

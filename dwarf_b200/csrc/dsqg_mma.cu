@@ -1177,11 +1177,12 @@ cudaError_t fwd_launch_mma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
     if (a.scale_embed) {
         if constexpr (D <= 64) {
             const size_t smem = se_tables_bytes(t.J, D, (WB + 16) / 8, W, 16);
-            if (a.strided) return cudaErrorInvalidValue;
-            static int seen[64] = {0};
-            cudaError_t e = ensure_dynamic_smem(fwd_mma_kernel<D, WB, true, false>, smem, seen);
+            static int seen[64] = {0}, seen_st[64] = {0};
+            cudaError_t e = a.strided ? ensure_dynamic_smem(fwd_mma_kernel<D, WB, true, true>, smem, seen_st)
+                                      : ensure_dynamic_smem(fwd_mma_kernel<D, WB, true, false>, smem, seen);
             if (e != cudaSuccess) return e;
-            fwd_mma_kernel<D, WB, true, false><<<grid, W * 32, smem, s>>>(a, t);
+            if (a.strided) fwd_mma_kernel<D, WB, true, true><<<grid, W * 32, smem, s>>>(a, t);
+            else fwd_mma_kernel<D, WB, true, false><<<grid, W * 32, smem, s>>>(a, t);
         } else {
             return cudaErrorInvalidValue;
         }
@@ -1237,9 +1238,12 @@ cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stag
 template <int D, int WB>
 cudaError_t bwd_launch_mma(const BwdArgs& a, const Taps& t, cudaStream_t s, int stages) {
     if (a.scale_embed) {
-        if (a.strided) return cudaErrorInvalidValue;
-        if constexpr (D <= 64) return bwd_launch_mma_se<D, WB, true, false>(a, t, s, stages);
-        else return cudaErrorInvalidValue;
+        if constexpr (D <= 64) {
+            if (a.strided) return bwd_launch_mma_se<D, WB, true, true>(a, t, s, stages);
+            return bwd_launch_mma_se<D, WB, true, false>(a, t, s, stages);
+        } else {
+            return cudaErrorInvalidValue;
+        }
     }
     if (a.strided) return bwd_launch_mma_se<D, WB, false, true>(a, t, s, stages);
     return bwd_launch_mma_se<D, WB, false, false>(a, t, s, stages);

@@ -19,7 +19,8 @@ from typing import Optional, Sequence
 import torch
 import torch.nn as nn
 
-from .ops import ALL_OFFSETS, causal_mean, dsqg_attention, dsqg_attention_packed, packed_path_available
+from .ops import (ALL_OFFSETS, InjectKVFunction, causal_mean, dsqg_attention, dsqg_attention_packed,
+                  packed_path_available)
 
 
 def dsqg_attention_v2(q, k, v, pos_bias, offsets: Sequence[int] = ALL_OFFSETS):
@@ -84,13 +85,13 @@ class _DSQGAttentionBase(nn.Module):
         return tuple(t.view(B, N, H, HD).permute(0, 2, 1, 3).contiguous()
                      for t in self.qkv_proj(x).split(D, dim=-1))
 
-    def _packed_ok(self, qkv, kv_inject):
-        """The copy-free path applies to bf16 activations (autocast), no K/V injection, no scale_embed,
-        and head widths / offset sets the tensor-core kernels take."""
-        if kv_inject is not None or hasattr(self, "scale_embed") or qkv.dtype != torch.bfloat16 or not qkv.is_cuda:
+    def _packed_ok(self, qkv):
+        """The copy-free path applies to bf16 activations (autocast) and head widths / offset sets
+        the tensor-core kernels take (with scale_embed: head widths up to 64)."""
+        if qkv.dtype != torch.bfloat16 or not qkv.is_cuda:
             return False
         if self._packed is None:
-            self._packed = packed_path_available(self.head_dim, self._offsets)
+            self._packed = packed_path_available(self.head_dim, self._offsets, hasattr(self, "scale_embed"))
         return self._packed
 
     def attend(self, x, kv_inject=None):
@@ -98,15 +99,24 @@ class _DSQGAttentionBase(nn.Module):
         cache has to be filled with)."""
         B, N, D = x.shape
         qkv = self.qkv_proj(x)
-        if self._packed_ok(qkv, kv_inject):
+        if self._packed_ok(qkv):
             # q, k, v are read in place from the projection output, the result comes back
             # token-major and already gated: none of the reference's permute copies
             # (train/train_2048_condU.py:171-175,189-191) is made
             H, HD = self.num_heads, self.head_dim
-            qkv5 = qkv.contiguous().view(B, N, 3, H, HD)
+            qkv = qkv.contiguous()
+            if kv_inject is not None:
+                # Huygens K/V injection (train_2048_condU.py:178-181) as two in-place adds on the key and
+                # value thirds of the projection output; the deltas arrive [B,H,N,HD] (permuted views of
+                # token-major projections cost nothing to bring back)
+                if qkv._is_view():          # an in-place autograd function needs a tensor that owns its history
+                    qkv = qkv.clone()
+                qkv = InjectKVFunction.apply(qkv, kv_inject[0].permute(0, 2, 1, 3).reshape(B, N, D),
+                                             kv_inject[1].permute(0, 2, 1, 3).reshape(B, N, D))
+            qkv5 = qkv.view(B, N, 3, H, HD)
             gate = self.gate_proj(x)
             y = dsqg_attention_packed(qkv5, self.pos_bias, getattr(self, "if_gain", None),
-                                      gate.to(torch.bfloat16), self._offsets)
+                                      gate.to(torch.bfloat16), self._offsets, getattr(self, "scale_embed", None))
             return (self.dropout(self.out_proj(y)), qkv5[:, :, 1].permute(0, 2, 1, 3), qkv5[:, :, 2].permute(0, 2, 1, 3))
         H, HD = self.num_heads, self.head_dim
         q, k, v = (t.view(B, N, H, HD).permute(0, 2, 1, 3).contiguous() for t in qkv.split(D, dim=-1))

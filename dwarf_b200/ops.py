@@ -187,7 +187,7 @@ class DSQGPackedFunction(torch.autograd.Function):
     their autograd backward; the gradient comes back as one dqkv tensor in the layout of qkv."""
 
     @staticmethod
-    def forward(ctx, qkv, gate, pos_bias, head_gain, offsets):
+    def forward(ctx, qkv, gate, pos_bias, head_gain, offsets, scale_embed=None):
         lib = _lib.load()
         off, J = _lib.offsets_array(offsets)
         B, N, three, H, D = qkv.shape
@@ -199,6 +199,9 @@ class DSQGPackedFunction(torch.autograd.Function):
         pb, hg = _f32c(pos_bias), _f32c(head_gain)
         if tuple(pb.shape) != (J, H):
             raise ValueError(f"dsqg: pos_bias must be [{J},{H}], got {tuple(pb.shape)}")
+        se = _f32c(scale_embed)
+        if se is not None and tuple(se.shape) != (J, D):
+            raise ValueError(f"dsqg: scale_embed must be [{J},{D}], got {tuple(se.shape)}")
         y = torch.empty(B, N, H * D, device=qkv.device, dtype=qkv.dtype)
         lse = torch.empty(B, H, N, device=qkv.device, dtype=torch.float32)
         st_in = _lib.Strides(N * 3 * H * D, D, 3 * H * D)
@@ -206,18 +209,25 @@ class DSQGPackedFunction(torch.autograd.Function):
         p0, esz = qkv.data_ptr(), qkv.element_size()
         with torch.cuda.device(qkv.device):
             stream = torch.cuda.current_stream(qkv.device).cuda_stream
-            _lib.check(lib.dsqg_fwd_strided(p0, p0 + H * D * esz, p0 + 2 * H * D * esz, st_in, pb.data_ptr(), _ptr(hg),
-                                            off, J, y.data_ptr(), st_out, _ptr(gate), lse.data_ptr(),
-                                            B, H, N, D, _lib.DSQG_DTYPE_BF16, stream, 0.0), "dsqg_fwd_strided")
-        ctx.save_for_backward(qkv, gate, pb, hg, y, lse)
+            if se is None:
+                _lib.check(lib.dsqg_fwd_strided(p0, p0 + H * D * esz, p0 + 2 * H * D * esz, st_in, pb.data_ptr(),
+                                                _ptr(hg), off, J, y.data_ptr(), st_out, _ptr(gate), lse.data_ptr(),
+                                                B, H, N, D, _lib.DSQG_DTYPE_BF16, stream, 0.0), "dsqg_fwd_strided")
+            else:
+                _lib.check(lib.dsqg_fwd_strided_se(p0, p0 + H * D * esz, p0 + 2 * H * D * esz, st_in, pb.data_ptr(),
+                                                   se.data_ptr(), _ptr(hg), off, J, y.data_ptr(), st_out, _ptr(gate),
+                                                   lse.data_ptr(), B, H, N, D, _lib.DSQG_DTYPE_BF16, stream, 0.0),
+                           "dsqg_fwd_strided_se")
+        ctx.save_for_backward(qkv, gate, pb, hg, y, lse, se)
         ctx.offsets = tuple(offsets)
-        ctx.param_dtypes = (pos_bias.dtype, None if head_gain is None else head_gain.dtype)
+        ctx.param_dtypes = (pos_bias.dtype, None if head_gain is None else head_gain.dtype,
+                            None if scale_embed is None else scale_embed.dtype)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         lib = _lib.load()
-        qkv, gate, pb, hg, y, lse = ctx.saved_tensors
+        qkv, gate, pb, hg, y, lse, se = ctx.saved_tensors
         off, J = _lib.offsets_array(ctx.offsets)
         B, N, _, H, D = qkv.shape
         dy = dy.to(qkv.dtype).contiguous()
@@ -226,7 +236,8 @@ class DSQGPackedFunction(torch.autograd.Function):
         dqkv = torch.empty_like(qkv)
         dpb = torch.empty_like(pb)
         dhg = None if hg is None else torch.empty_like(hg)
-        nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, 0)
+        dse = None if se is None else torch.empty_like(se)
+        nbytes = lib.dsqg_bwd_scratch_bytes(J, B, H, N, D, 0 if se is None else 1)
         scratch = torch.empty(nbytes, device=qkv.device, dtype=torch.uint8)
         p0, g0, esz = qkv.data_ptr(), dqkv.data_ptr(), qkv.element_size()
         with torch.cuda.device(qkv.device):
@@ -237,27 +248,65 @@ class DSQGPackedFunction(torch.autograd.Function):
                 delta = torch.empty(B, H, N, device=qkv.device, dtype=torch.float32)
                 _lib.check(lib.dsqg_gate_bwd(dy.data_ptr(), y.data_ptr(), gate.data_ptr(), st_out, dout.data_ptr(),
                                              dgate.data_ptr(), delta.data_ptr(), B, H, N, D, stream), "dsqg_gate_bwd")
-            _lib.check(lib.dsqg_bwd_strided(p0, p0 + H * D * esz, p0 + 2 * H * D * esz, st_in, pb.data_ptr(), _ptr(hg),
-                                            off, J, y.data_ptr(), lse.data_ptr(), dout.data_ptr(), st_out, _ptr(delta),
-                                            g0, g0 + H * D * esz, g0 + 2 * H * D * esz, dpb.data_ptr(), _ptr(dhg),
-                                            scratch.data_ptr(), nbytes, B, H, N, D, _lib.DSQG_DTYPE_BF16, stream, 0.0),
-                       "dsqg_bwd_strided")
-        pb_dt, hg_dt = ctx.param_dtypes
-        return dqkv, dgate, dpb.to(pb_dt), None if dhg is None else dhg.to(hg_dt), None
+            if se is None:
+                _lib.check(lib.dsqg_bwd_strided(p0, p0 + H * D * esz, p0 + 2 * H * D * esz, st_in, pb.data_ptr(),
+                                                _ptr(hg), off, J, y.data_ptr(), lse.data_ptr(), dout.data_ptr(), st_out,
+                                                _ptr(delta), g0, g0 + H * D * esz, g0 + 2 * H * D * esz, dpb.data_ptr(),
+                                                _ptr(dhg), scratch.data_ptr(), nbytes, B, H, N, D,
+                                                _lib.DSQG_DTYPE_BF16, stream, 0.0), "dsqg_bwd_strided")
+            else:
+                _lib.check(lib.dsqg_bwd_strided_se(p0, p0 + H * D * esz, p0 + 2 * H * D * esz, st_in, pb.data_ptr(),
+                                                   se.data_ptr(), _ptr(hg), off, J, y.data_ptr(), lse.data_ptr(),
+                                                   dout.data_ptr(), st_out, _ptr(delta), g0, g0 + H * D * esz,
+                                                   g0 + 2 * H * D * esz, dpb.data_ptr(), dse.data_ptr(), _ptr(dhg),
+                                                   scratch.data_ptr(), nbytes, B, H, N, D, _lib.DSQG_DTYPE_BF16,
+                                                   stream, 0.0), "dsqg_bwd_strided_se")
+        pb_dt, hg_dt, se_dt = ctx.param_dtypes
+        return (dqkv, dgate, dpb.to(pb_dt), None if dhg is None else dhg.to(hg_dt), None,
+                None if dse is None else dse.to(se_dt))
 
 
-def packed_path_available(head_dim: int, offsets: Sequence[int]) -> bool:
+class InjectKVFunction(torch.autograd.Function):
+    """k += k_delta; v += v_delta (train/train_2048_condU.py:178-181) applied IN PLACE to the key
+    and value thirds of a fused projection output qkv [B,N,3*D] (a non-leaf tensor that is not a
+    view, e.g. what nn.Linear returned), so the packed operator can go on reading q, k, v in place.
+    k_delta, v_delta: [B,N,D] token-major.  Backward: the deltas' gradients are the key and value
+    thirds of qkv's gradient (views, no copy)."""
+
+    @staticmethod
+    def forward(ctx, qkv, k_delta, v_delta):
+        B, N, D3 = qkv.shape
+        if D3 % 3 or tuple(k_delta.shape) != (B, N, D3 // 3) or tuple(v_delta.shape) != (B, N, D3 // 3):
+            raise ValueError("dsqg inject: qkv must be [B,N,3*D] and the deltas [B,N,D]")
+        thirds = qkv.view(B, N, 3, D3 // 3)
+        thirds[:, :, 1].add_(k_delta)
+        thirds[:, :, 2].add_(v_delta)
+        ctx.mark_dirty(qkv)
+        ctx.delta_dtypes = (k_delta.dtype, v_delta.dtype)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, g):
+        B, N, D3 = g.shape
+        thirds = g.view(B, N, 3, D3 // 3) if g.is_contiguous() else g.reshape(B, N, 3, D3 // 3)
+        kdt, vdt = ctx.delta_dtypes
+        return g, thirds[:, :, 1].to(kdt), thirds[:, :, 2].to(vdt)
+
+
+def packed_path_available(head_dim: int, offsets: Sequence[int], scale_embed: bool = False) -> bool:
     """True when dsqg_attention_packed can take this head width and offset set (the bf16 tensor-core
-    kernels without scale_embed); otherwise callers use dsqg_attention on permuted copies."""
+    kernels; with scale_embed head widths up to 64); otherwise callers use dsqg_attention on
+    permuted copies."""
     off, J = _lib.offsets_array(offsets)
-    return bool(_lib.load().dsqg_tensor_core_path(_lib.DSQG_DTYPE_BF16, int(head_dim), off, J, 0))
+    return bool(_lib.load().dsqg_tensor_core_path(_lib.DSQG_DTYPE_BF16, int(head_dim), off, J, 1 if scale_embed else 0))
 
 
-def dsqg_attention_packed(qkv, pos_bias, head_gain=None, gate=None, offsets: Sequence[int] = ALL_OFFSETS):
+def dsqg_attention_packed(qkv, pos_bias, head_gain=None, gate=None, offsets: Sequence[int] = ALL_OFFSETS,
+                          scale_embed=None):
     """DSQG straight on the fused projection output.  qkv: [B,N,3,H,HD] bf16 contiguous; gate: None
-    or [B,N,H*HD] bf16 (pre-sigmoid).  Returns [B,N,H*HD] bf16, already multiplied by
-    sigmoid(gate) when a gate is given."""
-    return DSQGPackedFunction.apply(qkv, gate, pos_bias, head_gain, tuple(int(o) for o in offsets))
+    or [B,N,H*HD] bf16 (pre-sigmoid); scale_embed: None or [J,HD] (the reference's v3 op).  Returns
+    [B,N,H*HD] bf16, already multiplied by sigmoid(gate) when a gate is given."""
+    return DSQGPackedFunction.apply(qkv, gate, pos_bias, head_gain, tuple(int(o) for o in offsets), scale_embed)
 
 
 def dsqg_attention(q, k, v, pos_bias, head_gain=None, scale_embed=None,

@@ -206,7 +206,7 @@ int dsqg_bwd_scaled(const void* q, const void* k, const void* v,
  *     forward's (gated) output, which is also what dsqg_bwd_strided gets as `out`.  Without a gate
  *     pass delta_pre = NULL and the forward's output and its gradient as out and dout.
  * lse, dpos_bias, dhead_gain, scratch (dsqg_bwd_scratch_bytes(..., 0)) are as in dsqg_fwd / dsqg_bwd.
- * bf16 only, no scale_embed, and only shapes the tensor-core kernels take
+ * bf16 only, and only shapes the tensor-core kernels take
  * (dsqg_tensor_core_path(...) == 1): DSQG_ERR_UNSUPPORTED otherwise, so that a caller can fall
  * back to the copies.  scale <= 0 selects 1/sqrt(D). */
 typedef struct { long long batch, head, row; } dsqg_strides;
@@ -221,6 +221,23 @@ int dsqg_bwd_strided(const void* q, const void* k, const void* v, const dsqg_str
                      void* dq, void* dk, void* dv, float* dpos_bias, float* dhead_gain,
                      void* scratch, size_t scratch_bytes,
                      int B, int H, int N, int D, int dtype, void* stream, float scale);
+/* The same two entries with the reference's scale_embed term (dsqg_attention_v3,
+ * kernels/dsqg_attention_v3.py:112-118; the op of DSQGAttentionQW, train/train_2048_condU.py:184):
+ * scale_embed [J,D] fp32 is required, dscale_embed [J,D] fp32 receives its gradient, the scratch
+ * size is dsqg_bwd_scratch_bytes(..., 1), D <= 64. */
+int dsqg_fwd_strided_se(const void* q, const void* k, const void* v, const dsqg_strides* qkv_strides,
+                        const float* pos_bias, const float* scale_embed, const float* head_gain,
+                        const int32_t* offsets, int J,
+                        void* out, const dsqg_strides* out_strides, const void* gate, float* lse,
+                        int B, int H, int N, int D, int dtype, void* stream, float scale);
+int dsqg_bwd_strided_se(const void* q, const void* k, const void* v, const dsqg_strides* qkv_strides,
+                        const float* pos_bias, const float* scale_embed, const float* head_gain,
+                        const int32_t* offsets, int J,
+                        const void* out, const float* lse, const void* dout, const dsqg_strides* out_strides,
+                        const float* delta_pre,
+                        void* dq, void* dk, void* dv, float* dpos_bias, float* dscale_embed, float* dhead_gain,
+                        void* scratch, size_t scratch_bytes,
+                        int B, int H, int N, int D, int dtype, void* stream, float scale);
 int dsqg_gate_bwd(const void* dy, const void* y, const void* gate, const dsqg_strides* strides,
                   void* dout, void* dgate, float* delta, int B, int H, int N, int D, void* stream);
 

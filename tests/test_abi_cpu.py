@@ -170,6 +170,21 @@ def test_strided_gate_scan_and_interleaved_ring_argument_errors(lib):
     assert bwd(st_in=None) == -1 and bwd(dq=None) == -1 and bwd(scratch=None) == -1
     assert bwd(st_out=odd) == -5 and bwd(nbytes=need - 1) == -6 and bwd(D=80) == -8
 
+    # the scale_embed variants: the table is required, head widths above 64 have no kernel, and the
+    # backward wants the larger scratch
+    def fwd_se(se=_fake(8), D=32, st_in=good):
+        return lib.dsqg_fwd_strided_se(_fake(1), _fake(2), _fake(3), st_in, _fake(4), se, None, off, J, _fake(5), good,
+                                       None, _fake(6), 1, 2, 16, D, 0, None, 0.0)
+    assert fwd_se(se=None) == -1 and fwd_se(se=_fake(8) + 4) == -5 and fwd_se(D=128) == -8 and fwd_se(st_in=odd) == -5
+    need_se = lib.dsqg_bwd_scratch_bytes(J, 1, 2, 16, 32, 1)
+
+    def bwd_se(se=_fake(8), dse=_fake(14), nbytes=need_se, D=32):
+        return lib.dsqg_bwd_strided_se(_fake(1), _fake(2), _fake(3), good, _fake(4), se, None, off, J, _fake(5),
+                                       _fake(6), _fake(7), good, None, _fake(10), _fake(11), _fake(12), _fake(13),
+                                       dse, None, _fake(20), nbytes, 1, 2, 16, D, 0, None, 0.0)
+    assert bwd_se(se=None) == -1 and bwd_se(dse=None) == -1 and bwd_se(D=128, nbytes=1 << 30) == -8
+    assert need_se > need and bwd_se(nbytes=need) == -6
+
     gate = lambda **kw: lib.dsqg_gate_bwd(kw.get("dy", _fake(1)), _fake(2), _fake(3), kw.get("st", good), _fake(4),
                                           _fake(5), kw.get("delta", _fake(6)), 1, 2, 16, kw.get("D", 32), None)
     assert gate(dy=None) == -1 and gate(st=None) == -1 and gate(delta=None) == -1

@@ -110,9 +110,107 @@ def test_module_takes_the_packed_path_under_autocast_and_matches_the_copy_path()
     for nm, u, w in zip(("y", "dx", "dpos_bias", "dgate_w"), a, b):
         scale = w.abs().max().item() + 1e-6
         assert (u - w).abs().max().item() <= 2e-2 * max(1.0, scale), nm
-    # fp32 activations (no autocast) and layers with scale_embed keep the copy path
-    assert not m._packed_ok(torch.zeros(1, device=dev), None)
-    assert not dwarf_b200.DSQGAttentionV3(64, 2).to(dev)._packed_ok(torch.zeros(1, device=dev, dtype=torch.bfloat16), None)
+    # fp32 activations (no autocast) keep the copy path; so do layers with scale_embed on head widths above 64
+    assert not m._packed_ok(torch.zeros(1, device=dev))
+    assert dwarf_b200.DSQGAttentionV3(64, 2).to(dev)._packed_ok(torch.zeros(1, device=dev, dtype=torch.bfloat16))
+    assert not dwarf_b200.DSQGAttentionV3(256, 2).to(dev)._packed_ok(torch.zeros(1, device=dev, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("shape", [(2, 300, 4, 32), (1, 1500, 3, 64), (1, 1, 2, 32)])
+@pytest.mark.parametrize("offsets", [O.OFFSETS_43, O.OFFSETS_44], ids=["J43", "J44"])
+@pytest.mark.parametrize("with_gate", [True, False])
+def test_packed_path_with_scale_embed_vs_oracle_chain(shape, offsets, with_gate):
+    """The reference's v3 op (q-weighted scale selection) on the packed layout: the chain of
+    train/train_2048_condU.py:171-175,184-191 with the oracle in fp32."""
+    B, N, H, D = shape
+    qkv, gate, dy, pb, gain = _case(B, N, H, D, offsets, 31 + N + D)
+    g = torch.Generator().manual_seed(99)
+    se = torch.randn(len(offsets), D, generator=g) * 0.3
+    if not with_gate:
+        gate = None
+    q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3).float().contiguous() for i in range(3))
+    tok = lambda t: t.permute(0, 2, 1, 3).reshape(B, N, H * D)
+    heads = lambda t: t.view(B, N, H, D).permute(0, 2, 1, 3).contiguous()
+    o = tok(oracle_fwd_bwd(q, k, v, pb, None, se, gain, offsets)["out"])
+    if gate is None:
+        y_ref, dout, dgate_ref = o, dy.float(), None
+    else:
+        sg = torch.sigmoid(gate.float())
+        y_ref, dout, dgate_ref = o * sg, dy.float() * sg, dy.float() * o * sg * (1 - sg)
+    bwd = oracle_fwd_bwd(q, k, v, pb, heads(dout), se, gain, offsets)
+    dqkv_ref = torch.stack([bwd[nm].permute(0, 2, 1, 3) for nm in ("dq", "dk", "dv")], dim=2)
+    dev = torch.device("cuda", 0)
+    assert dwarf_b200.packed_path_available(D, offsets, scale_embed=True)
+    qkv_d = qkv.to(dev).requires_grad_(True)
+    gate_d = None if gate is None else gate.to(dev).requires_grad_(True)
+    pb_d, gain_d, se_d = (t.to(dev).requires_grad_(True) for t in (pb, gain, se))
+    y = dwarf_b200.dsqg_attention_packed(qkv_d, pb_d, gain_d, gate_d, offsets, scale_embed=se_d)
+    y.backward(dy.to(dev))
+    assert_bf16_close(y.detach().float().cpu(), y_ref, "y")
+    assert_bf16_close(qkv_d.grad.float().cpu(), dqkv_ref, "dqkv")
+    if with_gate:
+        assert_bf16_close(gate_d.grad.float().cpu(), dgate_ref, "dgate")
+    assert_param_grad_close(pb_d.grad.cpu(), bwd["dpb"], "dpb", PARAM_REL_TOL_BF16)
+    assert_param_grad_close(gain_d.grad.cpu(), bwd["dgain"], "dgain", PARAM_REL_TOL_BF16)
+    assert_param_grad_close(se_d.grad.cpu(), bwd["dse"], "dse", PARAM_REL_TOL_BF16)
+
+
+def test_packed_path_with_scale_embed_equals_copy_path_bitwise():
+    dev = torch.device("cuda", 0)
+    B, N, H, D = 2, 777, 4, 32
+    qkv, _, dy, pb, gain = _case(B, N, H, D, O.OFFSETS_43, 6)
+    se = torch.randn(43, D, generator=torch.Generator().manual_seed(3)) * 0.3
+    leaf = lambda t: t.to(dev).requires_grad_(True)
+    qkv_d, pb_d, gain_d, se_d = leaf(qkv), leaf(pb), leaf(gain), leaf(se)
+    y = dwarf_b200.dsqg_attention_packed(qkv_d, pb_d, gain_d, None, O.OFFSETS_43, scale_embed=se_d)
+    y.backward(dy.to(dev))
+    q, k, v = (qkv.to(dev)[:, :, i].permute(0, 2, 1, 3).contiguous().requires_grad_(True) for i in range(3))
+    pb2, gain2, se2 = leaf(pb), leaf(gain), leaf(se)
+    o = dwarf_b200.dsqg_attention(q, k, v, pb2, gain2, se2, O.OFFSETS_43)
+    o.backward(dy.to(dev).view(B, N, H, D).permute(0, 2, 1, 3).contiguous())
+    assert torch.equal(y.detach(), o.detach().permute(0, 2, 1, 3).reshape(B, N, H * D))
+    for i, t in enumerate((q, k, v)):
+        assert torch.equal(qkv_d.grad[:, :, i], t.grad.permute(0, 2, 1, 3))
+    assert torch.equal(pb_d.grad, pb2.grad) and torch.equal(gain_d.grad, gain2.grad) and torch.equal(se_d.grad, se2.grad)
+
+
+def test_condu_layer_with_kv_injection_takes_the_packed_path_and_matches_the_copy_path():
+    """DSQGAttentionQW (scale_embed, if_gain) with kv_inject under autocast: the injection becomes two
+    in-place adds on the projection output (train/train_2048_condU.py:178-181); output and every
+    gradient, the deltas' included, agree with the copy path."""
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(4)
+    m = dwarf_b200.DSQGAttentionQW(256, 8, dropout=0.0, offsets=O.OFFSETS_44).to(dev)
+    with torch.no_grad():
+        m.scale_embed.normal_(0, 0.2)
+        m.if_gain.uniform_(0.8, 1.2)
+    B, N = 2, 333
+    x = torch.randn(B, N, 256, device=dev, requires_grad=True)
+    kd = (torch.randn(B, 8, N, 32, device=dev) * 0.3).requires_grad_(True)
+    vd = (torch.randn(B, 8, N, 32, device=dev) * 0.3).requires_grad_(True)
+
+    def run(packed):
+        m._packed = packed
+        for p in list(m.parameters()) + [x, kd, vd]:
+            p.grad = None
+        with torch.amp.autocast("cuda", dtype=torch.bfloat16):
+            y = m(x, kv_inject=(kd.bfloat16(), vd.bfloat16()))
+        (y.float() * torch.linspace(-1, 1, 256, device=dev)).sum().backward()
+        return (y.detach().float(), x.grad.clone(), kd.grad.clone(), vd.grad.clone(), m.scale_embed.grad.clone(),
+                m.pos_bias.grad.clone(), m.if_gain.grad.clone())
+
+    a, b = run(None), run(False)
+    assert m._packed is False
+    m._packed = None
+    for nm, u, w in zip(("y", "dx", "dk_delta", "dv_delta", "dscale_embed", "dpos_bias", "dif_gain"), a, b):
+        scale = w.abs().max().item() + 1e-6
+        assert (u - w).abs().max().item() <= 2e-2 * max(1.0, scale), nm
+    # the key/value tensors handed to a decode cache are the injected ones
+    with torch.no_grad(), torch.amp.autocast("cuda", dtype=torch.bfloat16):
+        _, k_seen, _ = m.attend(x, kv_inject=(kd.bfloat16(), vd.bfloat16()))
+        qkv = m.qkv_proj(x).view(B, N, 3, 8, 32)
+        want = (qkv[:, :, 1].permute(0, 2, 1, 3) + kd.bfloat16())
+    assert torch.equal(k_seen, want)
 
 
 def test_strided_entries_refuse_what_they_cannot_take():
