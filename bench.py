@@ -251,6 +251,10 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     if args.batch > 0:                                  # a smaller case of the same workload (e.g. for an ncu capture)
         import dataclasses
         cfg = dataclasses.replace(cfg, B=args.batch, name=cfg.name.replace(f"B{cfg.B} ", f"B{args.batch} "))
+    if args.dense_window_only:                          # kernel experiments on the dense window alone (offsets 0..32)
+        import dataclasses
+        dense = tuple(o for o in cfg.offsets if o <= 32)
+        cfg = dataclasses.replace(cfg, offsets=dense, name=cfg.name.replace(f"J{len(cfg.offsets)}", f"J{len(dense)} dense window only"))
     x = synth.make_op_inputs(cfg)                       # CPU, seeded
     x_full, cfg_full = x, cfg
     strong = args.scaling == "strong" and world > 1
@@ -315,7 +319,7 @@ def run_op_workload(args, cfg, rank, local_rank, world):
     # reported together with the kernel instantiation they were taken on; only known for the
     # workloads that were captured (full batch, automatic kernel choice, no scale_embed).
     names = ["dsqg_fwd", "dsqg_bwd_dq", "dsqg_bwd_dkdv"]
-    prof = profiled_traffic("" if se is not None or strong or args.batch > 0 or args.kernel_path else args.workload)
+    prof = profiled_traffic("" if se is not None or strong or args.batch > 0 or args.kernel_path or args.dense_window_only else args.workload)
     ncu_traffic = [prof.get(nm, {}).get("bytes") for nm in names]
     ncu_kernel = [prof.get(nm, {}).get("kernel") for nm in names]
     alg = [4 * T, 6 * T, 6 * T]           # per launch: fwd Q,K,V->O ; dq Q,K,V,O,dO->dQ ; dkdv Q,K,V,dO->dK,dV
@@ -684,7 +688,10 @@ def main():
     ap.add_argument("--decode-layers", type=int, default=0, help="cfg3: number of layers (default: the 10 of the configuration)")
     ap.add_argument("--kernel-path", type=int, default=0,
                     help="dsqg_set_kernel_path value for A/B runs: 0 automatic (default), 1 generic, 2 tensor-core, "
-                         "3 forward with TMA-staged V")
+                         "3 forward with TMA-staged V, 4 forward with the dense window on tcgen05 (dense-only offset sets)")
+    ap.add_argument("--dense-window-only", action="store_true",
+                    help="op workloads: keep only the offsets 0..32 of the configuration's set (A/B measurement of the "
+                         "dense-window part of the kernels; not a configuration of the specification)")
     ap.add_argument("--lm-attention", choices=["condM", "condU"], default="condM",
                     help="cfg4: DSQG layers with the position bias only (condM, the configuration's shape) or with "
                          "scale_embed and the per-head gain (condU)")

@@ -10,7 +10,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libdsqg_b200.so")
-SOURCES = ["dsqg_capi.cu", "dsqg_dispatch.cu", "dsqg_generic.cu", "dsqg_decode.cu", "dsqg_mma.cu", "dsqg_staged.cu", "dsqg_static.cu", "dsqg_gate.cu", "dsqg_scan.cu"]
+SOURCES = ["dsqg_capi.cu", "dsqg_dispatch.cu", "dsqg_generic.cu", "dsqg_decode.cu", "dsqg_mma.cu", "dsqg_staged.cu", "dsqg_umma.cu", "dsqg_static.cu", "dsqg_gate.cu", "dsqg_scan.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

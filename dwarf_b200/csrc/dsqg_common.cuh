@@ -96,6 +96,10 @@ bool staged_supported(int dtype, int D, const Taps& t, bool has_scale_embed);
 cudaError_t launch_fwd_staged(const FwdArgs& a, const Taps& t, cudaStream_t s);
 cudaError_t read_stage_error(int* value, bool reset);
 cudaError_t launch_wait_timeout(long long limit_cycles, int site, cudaStream_t s);
+// forward with the dense window on tcgen05 tensor cores and tensor memory (dsqg_umma.cu)
+bool umma_supported(int dtype, int D, const Taps& t, bool has_scale_embed);
+cudaError_t launch_fwd_umma(const FwdArgs& a, const Taps& t, cudaStream_t s);
+cudaError_t read_umma_error(int* value, bool reset);
 
 // Backward scratch layout: row statistics (8 bytes per row) | dpos_bias partials | dhead_gain partials | dscale_embed
 // partials, each block rounded up to 256 bytes.  A "tile" is the set of rows whose partial

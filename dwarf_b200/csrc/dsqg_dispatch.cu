@@ -10,11 +10,13 @@ namespace dsqg {
 
 // 0 = automatic, 1 = always the generic kernels, 2 = the tensor-core kernels (what the automatic
 // choice uses where they apply), 3 = the forward with TMA-staged V wherever it applies
-// (dsqg_staged.cu; not chosen automatically: it measures slower on B200).
+// (dsqg_staged.cu; not chosen automatically: it measures slower on B200), 4 = the forward with the
+// dense window on tcgen05 / tensor memory wherever it applies (dsqg_umma.cu; not chosen automatically).
 static std::atomic<int> g_path{0};
 
 cudaError_t launch_fwd(const FwdArgs& a, const Taps& t, int dtype, cudaStream_t s) {
     const int path = g_path.load();
+    if (path == 4 && !a.strided && umma_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_umma(a, t, s);
     if (path == 3 && staged_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_staged(a, t, s);
     if (path != 1 && mma_fwd_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_mma(a, t, s);
     return launch_fwd_generic(a, t, dtype, s);
@@ -30,15 +32,16 @@ cudaError_t launch_bwd(const BwdArgs& a, const Taps& t, int dtype, cudaStream_t 
 }  // namespace dsqg
 
 extern "C" int dsqg_set_kernel_path(int path) {
-    if (path < 0 || path > 3) return DSQG_ERR_UNSUPPORTED;
+    if (path < 0 || path > 4) return DSQG_ERR_UNSUPPORTED;
     dsqg::g_path.store(path);
     return DSQG_OK;
 }
 
 extern "C" int dsqg_device_error(int reset) {
-    int v = 0;
+    int v = 0, w = 0;
     if (dsqg::read_stage_error(&v, reset != 0) != cudaSuccess) return -1;
-    return v;
+    if (dsqg::read_umma_error(&w, reset != 0) != cudaSuccess) return -1;
+    return v ? v : w;
 }
 
 extern "C" int dsqg_test_wait_timeout(long long limit_cycles, void* stream) {

@@ -105,6 +105,15 @@ inline bool build_plan(const Taps& t, bool ahead, Plan* p) {
     return true;
 }
 
+// Host side (dsqg_staged.cu): a bf16 tensor addressed as [batch][head][row][D] through element
+// strides sb, sh, sn (rows of D contiguous elements) as a 4-D tiled tensor map whose box is
+// box_rows consecutive rows of one head, written with the 64-byte (D = 32) or 128-byte swizzle.
+// The two middle dimensions are ordered by stride; *head_first tells the kernel which order the
+// coordinates take.  false when the driver's encoder is missing or refuses the shape.
+bool make_map(CUtensorMap* m, bool* head_first, const void* ptr, int B, int H, int N, int D,
+              long long sb, long long sh, long long sn, int box_rows);
+bool tensor_map_encoder_available();
+
 // ------------------------------------------------------------------------------ device side
 #ifdef __CUDACC__
 

@@ -362,11 +362,13 @@ __global__ void wait_timeout_kernel(long long limit_cycles, int site) {
 }
 
 // ------------------------------------------------------------------------------ host side
+}  // namespace
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiledFn encode_fn() {
+static EncodeTiledFn encode_fn() {
     static EncodeTiledFn fn = [] {
         void* p = nullptr;
         cudaDriverEntryPointQueryResult q;
@@ -395,6 +397,10 @@ bool make_map(CUtensorMap* m, bool* head_first, const void* ptr, int B, int H, i
               CU_TENSOR_MAP_INTERLEAVE_NONE, D == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+bool tensor_map_encoder_available() { return encode_fn() != nullptr; }
+
+namespace {
 
 // cudaFuncSetAttribute once per kernel and device is enough; `done` is that kernel's flag word.
 template <typename K>

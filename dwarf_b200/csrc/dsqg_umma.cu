@@ -1,0 +1,415 @@
+// DSQG forward with the dense window on the 5th-generation tensor cores (tcgen05.mma, accumulators
+// in tensor memory, operands staged by the copy engine), bf16, D = 32, sm_100a.  Kernel path 4
+// (dsqg_set_kernel_path(4)); not chosen automatically.
+//
+// Reference math: kernels/dsqg_attention_v3.py:60-163 (scores, bias, causal mask, softmax over the
+// taps, weighted sum of the value rows) without scale_embed.
+//
+// A thread block is persistent and walks a contiguous range of 128-row tiles.  Per tile
+//   producer (warp 4, one lane):  copies Q[128 x D], the key band K[n0-32, n0+128) and the value
+//       band into shared memory (cp.async.bulk.tensor, double buffered, one tile ahead), then issues
+//       S = Q . Kband^T        (M 128, N 160, K = D)  -> tensor memory columns [0, 160)
+//       O = P . Vband          (M 128, N D,  K = 160) -> tensor memory columns [160, 160 + D)
+//   softmax (warps 0-3, one thread per query row = tensor-memory lane): reads its row's 64-column
+//       window of S (tcgen05.ld), adds the bias / mask table, takes the row maximum and
+//       the exponentials, writes P as bf16 pairs over S in tensor memory (the A operand of the second
+//       product; zero outside the row's window), later reads O, scales by gain / sum and stores the row.
+// Row r of warp w (r = 32 w + l) needs band columns c = r + 32 - delta, delta = 0..32, i.e.
+// c - 32 w in [l, l + 32]: a window of 64 columns per warp holds them, and the bias/mask table
+// Bm[l][c - 32 w] (pos_bias[delta, h] * log2 e inside the window, "minus infinity" outside) is
+// the same for every warp and tile of a head.
+//
+// Every wait on a barrier is bounded (stg::mbar_wait): a wait that gives up sets the block's
+// abort flag and the device error word, every other wait of the block returns at once, tensor
+// memory is released and the kernel ends.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "dsqg_common.cuh"
+#include "dsqg_stage.cuh"
+
+namespace dsqg {
+namespace umma {
+
+using namespace stg;
+
+constexpr int kTM = 128;                 // query rows per tile (= tensor-memory lanes)
+constexpr int kBand = kTM + kWB;         // key rows of the dense window of a tile: 160
+constexpr int kThreads = 480;            // 3 softmax groups of 4 warps + two MMA issuer warps + copy warp
+constexpr int kTmemCols = 512;           // three slots of 160 columns
+constexpr int kBmPitch = 68;             // floats per row of the bias/mask table (64 + 4: conflict-free float4 reads)
+
+// ---- tcgen05 / tensor memory
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] . B[smem], bf16 operands, fp32 accumulation; issued by one thread.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The same with A read from tensor memory (bf16 pairs per 32-bit column, lane = row).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// The barrier gets one arrival when every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Non-blocking test of a barrier phase (try_wait may suspend the thread for a while before it answers).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// 32 consecutive fp32 columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t taddr) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: 128-byte-swizzled (layout 2) or 64-byte-swizzled (layout 4)
+// tile whose 8-row groups are `sbo` bytes apart.  The leading-dimension offset is not used by the
+// swizzled layouts of one atom width; bits 46-47 carry the descriptor version of this architecture.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t sbo, uint32_t layout) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(sbo >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)layout << 61);
+}
+// Instruction descriptor: fp32 accumulator, bf16 A and B, A K-major, B K-major or MN-major.
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) |
+           ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+constexpr int kSlots = 3;                // tiles in flight per thread block = softmax warp groups = tensor-memory slots
+constexpr int kBufs = 2 * kSlots;        // Q / K-band / V-band buffers in shared memory
+constexpr int kSlotCols = 160;           // tensor-memory columns per slot: S [0,160), then P over [0,80) and O over [128,160)
+constexpr int kOCol = 128;
+
+template <int D>
+struct Layout {
+    static constexpr int row_bytes = 2 * D;                       // 64
+    static constexpr int q_bytes = kTM * row_bytes;               // 8 KB
+    static constexpr int band_bytes = kBand * row_bytes;          // 10 KB
+    static constexpr int buf_bytes = q_bytes + 2 * band_bytes;    // 28 KB: Q | K band | V band
+    static constexpr int bm0 = kBufs * buf_bytes;
+    static constexpr int bm_bytes = 32 * kBmPitch * 4;
+    static constexpr int bars0 = bm0 + kSlots * bm_bytes;
+    static constexpr int total = bars0 + 256;
+};
+
+// barrier slots (8 bytes each) behind the tables
+enum { kBarFull = 0, kBarEmpty = kBarFull + kBufs, kBarS = kBarEmpty + kBufs, kBarP = kBarS + kSlots,
+       kBarO = kBarP + kSlots, kBarORead = kBarO + kSlots, kNumBars = kBarORead + kSlots };
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
+                const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v) {
+    static_assert(D == 32, "one 64-byte swizzle atom per row");
+    using Lay = Layout<D>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t sb = smem_u32(smem);
+    const uint32_t bars = sb + Lay::bars0;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Lay::bars0 + 8 * kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Lay::bars0 + 8 * kNumBars + 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int N = a.N, H = a.H;
+    const long long tile_lo = (long long)blockIdx.x * n_tiles / gridDim.x;
+    const long long tile_hi = (long long)(blockIdx.x + 1) * n_tiles / gridDim.x;
+    const int my_tiles = (int)(tile_hi - tile_lo);
+    constexpr int kProducerWarp = 4 * kSlots, kOWarp = kProducerWarp + 1, kCopyWarp = kProducerWarp + 2;
+
+    // ---- one-time setup: barriers, tensor memory
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < kBufs; ++i) { mbar_init(bars + 8 * (kBarFull + i), 1); mbar_init(bars + 8 * (kBarEmpty + i), 1); }
+        for (int i = 0; i < kSlots; ++i) {
+            mbar_init(bars + 8 * (kBarS + i), 1); mbar_init(bars + 8 * (kBarP + i), kTM);
+            mbar_init(bars + 8 * (kBarO + i), 1); mbar_init(bars + 8 * (kBarORead + i), kTM);
+        }
+        fence_mbar_init();
+    }
+    if (warp == kProducerWarp) {
+        if (lane == 0) { prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); }
+        __syncwarp();
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == kCopyWarp) {
+        // ================================================================= copies: Q, key band, value band of tile j -> buffer j % 6
+        if (lane == 0) {
+            int bh = (int)(tile_lo / tiles_per_seq), nt = (int)(tile_lo % tiles_per_seq);
+            int b = bh / H, h = bh % H, j = 0;
+            for (; j < my_tiles; ++j) {
+                const int buf = j % kBufs;
+                // the buffer comes back when O of the tile six before this one has completed
+                if (j >= kBufs && !mbar_wait(bars + 8 * (kBarEmpty + buf), ((j - kBufs) / kBufs) & 1, abort_flag, 0x401)) break;
+                const uint32_t bar = bars + 8 * (kBarFull + buf), dst = sb + buf * Lay::buf_bytes;
+                const int n0 = nt * kTM;
+                mbar_arrive_expect_tx(bar, Lay::buf_bytes);
+                tma_load(dst, &map_q, bar, n0, h, b);
+                tma_load(dst + Lay::q_bytes, &map_k, bar, n0 - kWB, h, b);
+                tma_load(dst + Lay::q_bytes + Lay::band_bytes, &map_v, bar, n0 - kWB, h, b);
+                if (++nt == tiles_per_seq) { nt = 0; if (++h == H) { h = 0; ++b; } }
+            }
+            // after an abort: no copy of this block may be in flight when its shared memory is released
+            if (*abort_flag)
+                for (int i = j > kBufs ? j - kBufs : 0; i < j; ++i) mbar_wait(bars + 8 * (kBarFull + i % kBufs), (i / kBufs) & 1, abort_flag, 0x404);
+        }
+        __syncwarp();
+    } else if (warp == kProducerWarp) {
+        // ================================================================= issuer of S(j) = Q(j) . Kband(j)^T
+        // S(j) needs its operands in shared memory and its slot back from tile j - 3 (O read by the softmax group).
+        if (lane == 0) {
+            constexpr uint32_t kIdS = instr_desc(kTM, kBand, false);
+            const uint64_t desc0 = smem_desc(sb, 512, 4);       // tiles differ in the start-address field only (16-byte units)
+            for (int j = 0; j < my_tiles; ++j) {
+                const int slot = j % kSlots, buf = j % kBufs;
+                if (!mbar_wait(bars + 8 * (kBarFull + buf), (j / kBufs) & 1, abort_flag, 0x402)) break;
+                if (j >= kSlots && !mbar_wait(bars + 8 * (kBarORead + slot), ((j - kSlots) / kSlots) & 1, abort_flag, 0x405)) break;
+                tc_fence_after();
+                const uint64_t dq = desc0 + (uint32_t)((buf * Lay::buf_bytes) >> 4), dk = dq + (uint32_t)(Lay::q_bytes >> 4);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk)
+                    umma_bf16(tmem + kSlotCols * slot, dq + 2 * kk, dk + 2 * kk, kIdS, kk > 0);
+                umma_commit(bars + 8 * (kBarS + slot));
+            }
+        }
+        __syncwarp();
+    } else if (warp == kOWarp) {
+        // ================================================================= issuer of O(j) = P(j) . Vband(j)
+        // P: 16 bf16 = 8 columns of tensor memory per step.  The second commit hands the shared-memory buffer back.
+        if (lane == 0) {
+            constexpr uint32_t kIdO = instr_desc(kTM, D, true);
+            const uint64_t desc0 = smem_desc(sb, 512, 4);
+            for (int j = 0; j < my_tiles; ++j) {
+                const int slot = j % kSlots, buf = j % kBufs;
+                if (!mbar_wait(bars + 8 * (kBarP + slot), (j / kSlots) & 1, abort_flag, 0x403)) break;
+                tc_fence_after();
+                const uint32_t tS = tmem + kSlotCols * slot;
+                const uint64_t dv = desc0 + (uint32_t)((buf * Lay::buf_bytes + Lay::q_bytes + Lay::band_bytes) >> 4);
+#pragma unroll
+                for (int kk = 0; kk < kBand / 16; ++kk)
+                    umma_bf16_ts(tS + kOCol, tS + 8 * kk, dv + (uint32_t)((kk * 16 * Lay::row_bytes) >> 4), kIdO, kk > 0);
+                umma_commit(bars + 8 * (kBarO + slot));
+                umma_commit(bars + 8 * (kBarEmpty + buf));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ================================================================= softmax groups: thread = query row
+        const int grp = warp >> 2, wq = warp & 3, r = tid & (kTM - 1), l = lane;
+        float* Bm = reinterpret_cast<float*>(smem + Lay::bm0 + grp * Lay::bm_bytes);
+        const uint32_t tS = tmem + kSlotCols * grp + ((uint32_t)(32 * wq) << 16);
+        const float c2 = a.scale * kLog2e;
+        const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1;
+        int cur_h = -1;
+        for (int j = grp, k = 0; j < my_tiles; j += kSlots, ++k) {
+            const long long tile = tile_lo + j;
+            const int bh = (int)(tile / tiles_per_seq), n0 = (int)(tile % tiles_per_seq) * kTM;
+            const int h = bh % H, n = n0 + r;
+            if (h != cur_h) {
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
+            for (int e = r; e < 32 * 64; e += kTM) {
+                    const int ll = e >> 6, cc = e & 63, delta = ll + 32 - cc;
+                    Bm[ll * kBmPitch + cc] = (delta >= d_lo && delta <= d_hi) ? a.pos_bias[(delta - d_lo) * H + h] * kLog2e : kNeg;
+                }
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
+                cur_h = h;
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBarS + grp), k & 1, abort_flag, 0x411))) break;
+            tc_fence_after();
+            float z[64];
+            {
+                float x0[32], x1[32];
+                tmem_ld32(x0, tS + 32 * wq);
+                tmem_ld32(x1, tS + 32 * wq + 32);
+                tmem_wait_ld();
+                const float4* brow = reinterpret_cast<const float4*>(Bm + l * kBmPitch);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float4 b0 = brow[c], b1 = brow[8 + c];
+                    z[4 * c + 0] = fmaf(x0[4 * c + 0], c2, b0.x); z[4 * c + 1] = fmaf(x0[4 * c + 1], c2, b0.y);
+                    z[4 * c + 2] = fmaf(x0[4 * c + 2], c2, b0.z); z[4 * c + 3] = fmaf(x0[4 * c + 3], c2, b0.w);
+                    z[32 + 4 * c + 0] = fmaf(x1[4 * c + 0], c2, b1.x); z[32 + 4 * c + 1] = fmaf(x1[4 * c + 1], c2, b1.y);
+                    z[32 + 4 * c + 2] = fmaf(x1[4 * c + 2], c2, b1.z); z[32 + 4 * c + 3] = fmaf(x1[4 * c + 3], c2, b1.w);
+                }
+            }
+            if (n0 == 0 && wq == 0) {            // band columns 0..31 of the first tile are key rows -32..-1
+#pragma unroll
+                for (int c = 0; c < 32; ++c) z[c] = kNeg;
+            }
+            float m4[4] = {kNeg, kNeg, kNeg, kNeg};
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
+                m4[0] = fmaxf(m4[0], z[c]); m4[1] = fmaxf(m4[1], z[c + 1]);
+                m4[2] = fmaxf(m4[2], z[c + 2]); m4[3] = fmaxf(m4[3], z[c + 3]);
+            }
+            float m = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            m = m < kMinM ? 0.f : m;             // a row without a valid tap: every p becomes 0
+            // P (bf16 pairs) replaces S in tensor memory: band column c sits in 32-bit column c / 2, so the
+            // row's window is columns 16 wq .. 16 wq + 31 of the 80; the other 48 are zeroed
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pw[2][16];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const float p0 = ex2(z[2 * c] - m), p1 = ex2(z[2 * c + 1] - m);
+                s4[c & 3] += p0 + p1;
+                pw[c >> 4][c & 15] = pack_bf16x2(p0, p1);
+            }
+            const float lsum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            {
+                const uint32_t zero[16] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+                for (int ch = 0; ch < kBand / 32; ++ch) {
+                    if (ch == wq) tmem_st16(tS + 16 * ch, pw[0]);
+                    else if (ch == wq + 1) tmem_st16(tS + 16 * ch, pw[1]);
+                    else tmem_st16(tS + 16 * ch, zero);
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bars + 8 * (kBarP + grp));
+
+            if (!__all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBarO + grp), k & 1, abort_flag, 0x412))) break;
+            tc_fence_after();
+            float o[32];
+            tmem_ld32(o, tS + kOCol);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bars + 8 * (kBarORead + grp));       // the slot may take the next tile's S
+            if (n < N) {
+                const float gain = a.head_gain ? a.head_gain[h] : 1.f;
+                const float sc = lsum > 0.f ? __fdividef(gain, lsum) : 0.f;
+                uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + ((size_t)bh * N + n) * D);
+#pragma unroll
+                for (int c = 0; c < D / 8; ++c)
+                    dst[c] = make_uint4(pack_bf16x2(o[8 * c] * sc, o[8 * c + 1] * sc), pack_bf16x2(o[8 * c + 2] * sc, o[8 * c + 3] * sc),
+                                        pack_bf16x2(o[8 * c + 4] * sc, o[8 * c + 5] * sc), pack_bf16x2(o[8 * c + 6] * sc, o[8 * c + 7] * sc));
+                a.lse[(size_t)bh * N + n] = lsum > 0.f ? (m + __log2f(lsum)) * kLn2 : -INFINITY;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kProducerWarp) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace umma
+
+cudaError_t read_umma_error(int* value, bool reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(value, stg::g_stage_error, sizeof(int));
+    if (e == cudaSuccess && reset && *value != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(stg::g_stage_error, &zero, sizeof(int));
+    }
+    return e;
+}
+
+bool umma_supported(int dtype, int D, const Taps& t, bool has_scale_embed) {
+    return dtype == DSQG_DTYPE_BF16 && D == 32 && !has_scale_embed && t.n_sparse == 0 &&
+           t.d_lo + t.n_dense - 1 <= stg::kWB && stg::tensor_map_encoder_available();
+}
+
+cudaError_t launch_fwd_umma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
+    using namespace umma;
+    constexpr int D = 32;
+    if (a.strided || a.D != D) return cudaErrorInvalidValue;
+    const long long sn = D, sh = (long long)a.N * D, sbt = (long long)a.H * a.N * D;
+    CUtensorMap mq, mk, mv;
+    bool hf = false;
+    if (!stg::make_map(&mq, &hf, a.q, a.B, a.H, a.N, D, sbt, sh, sn, kTM) || hf ||
+        !stg::make_map(&mk, &hf, a.k, a.B, a.H, a.N, D, sbt, sh, sn, kBand) || hf ||
+        !stg::make_map(&mv, &hf, a.v, a.B, a.H, a.N, D, sbt, sh, sn, kBand) || hf)
+        return cudaErrorInvalidValue;
+    const int smem = Layout<D>::total + 1024;
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    static std::mutex mu;
+    static int attr_done[64] = {0}, sm_count[64] = {0};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+        if (!attr_done[dev]) {
+            if ((e = cudaFuncSetAttribute(fwd_umma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return e;
+            if ((e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+            attr_done[dev] = 1;
+        }
+        sms = sm_count[dev];
+    }
+    const int tiles_per_seq = (a.N + kTM - 1) / kTM;
+    const long long n_tiles = (long long)a.B * a.H * tiles_per_seq;
+    if (n_tiles > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const int grid = (int)(n_tiles < (long long)sms ? n_tiles : (long long)sms);
+    fwd_umma_kernel<D><<<grid, kThreads, smem, s>>>(a, t, tiles_per_seq, (int)n_tiles, mq, mk, mv);
+    return cudaGetLastError();
+}
+
+}  // namespace dsqg

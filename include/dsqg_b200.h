@@ -64,11 +64,14 @@ int dsqg_version(void);
 /* Testing knob with no counterpart in the reference: 0 = choose kernels automatically
  * (default), 1 = always use the generic CUDA-core kernels, 2 = the tensor-core kernels (what the
  * automatic choice uses where they apply), 3 = the forward with TMA-staged V wherever it applies
- * (not chosen automatically: it measures slower on B200).  Process-wide state. */
+ * (not chosen automatically: it measures slower on B200), 4 = the forward whose dense window runs
+ * on tcgen05 tensor cores with accumulators in tensor memory, for offset sets without sparse taps
+ * (bf16, D = 32, offsets within 0..32; every other call goes to the automatic choice; not chosen
+ * automatically).  Process-wide state. */
 int dsqg_set_kernel_path(int path);
 
 /* Device-side error word of the current device (no counterpart in the reference).  The
- * kernels that wait on shared-memory barriers for the copy engine (kernel path 3) bound every
+ * kernels that wait on shared-memory barriers for the copy engine or the tensor cores (kernel paths 3 and 4) bound every
  * such wait; a wait that runs out records its site id here and the kernel returns with
  * unspecified output instead of hanging.  0 = no error, -1 = the word could not be read.
  * Synchronises the device.  reset != 0 clears the word after reading. */

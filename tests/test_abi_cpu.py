@@ -120,7 +120,8 @@ def test_python_wrappers_refuse_cpu_tensors():
 
 def test_kernel_path_knob(lib):
     assert lib.dsqg_set_kernel_path(1) == 0 and lib.dsqg_set_kernel_path(0) == 0
-    assert lib.dsqg_set_kernel_path(2) == 0 and lib.dsqg_set_kernel_path(3) == 0 and lib.dsqg_set_kernel_path(0) == 0
+    assert lib.dsqg_set_kernel_path(2) == 0 and lib.dsqg_set_kernel_path(3) == 0 and lib.dsqg_set_kernel_path(4) == 0
+    assert lib.dsqg_set_kernel_path(0) == 0
     assert lib.dsqg_set_kernel_path(5) == -8
 
 

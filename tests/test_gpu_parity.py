@@ -54,13 +54,14 @@ REF_SHAPES = [(1, 8, 64, 32), (2, 8, 512, 32), (2, 8, 2047, 32), (1, 4, 2047, 80
               (1, 2, 1700, 128), (1, 1, 1, 32), (1, 2, 33, 16)]
 
 
-@pytest.fixture(params=["auto", "generic", "mma", "tma"])
+@pytest.fixture(params=["auto", "generic", "mma", "tma", "tcgen05"])
 def kernel_path(request):
     """Runs a test with the automatic kernel choice, with the generic CUDA-core kernels forced, with
-    the tensor-core kernels, and with the forward that stages V through the copy engine (its
-    bounded waits must not have given up)."""
+    the tensor-core kernels, with the forward that stages V through the copy engine, and with the
+    tcgen05 forward (which takes dense-only offset sets and hands every other set to the tensor-core
+    kernels); no bounded wait may have given up."""
     lib = _lib.load()
-    lib.dsqg_set_kernel_path({"auto": 0, "generic": 1, "mma": 2, "tma": 3}[request.param])
+    lib.dsqg_set_kernel_path({"auto": 0, "generic": 1, "mma": 2, "tma": 3, "tcgen05": 4}[request.param])
     yield request.param
     lib.dsqg_set_kernel_path(0)
     assert lib.dsqg_device_error(1) == 0, "a bounded device-side wait gave up"
