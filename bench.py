@@ -339,7 +339,7 @@ def run_op_workload(args, cfg, rank, local_rank, world):
         "e2e": {"value": tokens_per_step / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": 4 * T, "d2h_bytes_per_step": 4 * T, "ms_per_step": e2e_ms,
                 "steps": e2e_steps, "host_copy_bandwidth": pcie},
-        "gpu_launches": ((3 if args.kernel_path in (0, 2) else 4) + (2 if se is not None and args.kernel_path in (0, 2) else 0)) * args.steps,   # other paths reduce in a 4th kernel
+        "gpu_launches": ((3 if args.kernel_path in (0, 2, 4) else 4) + (2 if se is not None and args.kernel_path in (0, 2, 4) else 0)) * args.steps,   # paths 1 and 3 reduce in a 4th kernel
         "roofline": {"bound": "hbm", "kernel": names[top], "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": ncu_traffic[top], "traffic_from": (
                          None if ncu_traffic[top] is None else f"profiles/dram_traffic.md, ncu capture of {ncu_kernel[top]}"),
