@@ -1,5 +1,5 @@
 // DSQG forward with the dense window on the 5th-generation tensor cores (tcgen05.mma, accumulators
-// in tensor memory, operands staged by the copy engine), bf16, D = 32, sm_100a.  Kernel path 4
+// in tensor memory, operands staged by the copy engine), bf16, D = 32 or 64, sm_100a.  Kernel path 4
 // (dsqg_set_kernel_path(4)); not chosen automatically.
 //
 // Reference math: kernels/dsqg_attention_v3.py:60-163 (scores, bias, causal mask, softmax over the
@@ -139,24 +139,27 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 constexpr int kSlots = 3;                // tiles in flight per thread block = softmax warp groups = tensor-memory slots
-constexpr int kBufs = 2 * kSlots;        // Q / K-band / V-band buffers in shared memory
+constexpr int kMaxBufs = 2 * kSlots;     // Q / K-band / V-band buffers in shared memory: six at D = 32, three at D = 64
 constexpr int kSlotCols = 160;           // tensor-memory columns per slot: S [0,160), then P over [0,80) and O over [128,160)
-constexpr int kOCol = 128;
 
 template <int D>
 struct Layout {
-    static constexpr int row_bytes = 2 * D;                       // 64
-    static constexpr int q_bytes = kTM * row_bytes;               // 8 KB
-    static constexpr int band_bytes = kBand * row_bytes;          // 10 KB
-    static constexpr int buf_bytes = q_bytes + 2 * band_bytes;    // 28 KB: Q | K band | V band
-    static constexpr int bm0 = kBufs * buf_bytes;
+    static constexpr int bufs = D == 32 ? kMaxBufs : kSlots;
+    static constexpr int row_bytes = 2 * D;                       // 64 / 128: one swizzle atom wide
+    static constexpr int swizzle = D == 32 ? 4 : 2;               // descriptor layout code: 64-byte / 128-byte swizzle
+    static constexpr int sbo = 8 * row_bytes;                     // distance of 8-row groups
+    static constexpr int o_col = kSlotCols - D;                   // O occupies the last D columns of a slot (P ends at 80)
+    static constexpr int q_bytes = kTM * row_bytes;               // 8 / 16 KB
+    static constexpr int band_bytes = kBand * row_bytes;          // 10 / 20 KB
+    static constexpr int buf_bytes = q_bytes + 2 * band_bytes;    // 28 / 56 KB: Q | K band | V band
+    static constexpr int bm0 = bufs * buf_bytes;
     static constexpr int bm_bytes = 32 * kBmPitch * 4;
     static constexpr int bars0 = bm0 + kSlots * bm_bytes;
     static constexpr int total = bars0 + 256;
 };
 
 // barrier slots (8 bytes each) behind the tables
-enum { kBarFull = 0, kBarEmpty = kBarFull + kBufs, kBarS = kBarEmpty + kBufs, kBarP = kBarS + kSlots,
+enum { kBarFull = 0, kBarEmpty = kBarFull + kMaxBufs, kBarS = kBarEmpty + kMaxBufs, kBarP = kBarS + kSlots,
        kBarO = kBarP + kSlots, kBarORead = kBarO + kSlots, kNumBars = kBarORead + kSlots };
 
 template <int D>
@@ -164,8 +167,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
                 const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v) {
-    static_assert(D == 32, "one 64-byte swizzle atom per row");
+    static_assert(D == 32 || D == 64, "a row is one 64-byte or 128-byte swizzle atom");
     using Lay = Layout<D>;
+    constexpr int kBufs = Lay::bufs, kOCol = Lay::o_col;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sb = smem_u32(smem);
@@ -228,7 +232,7 @@ fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
         // S(j) needs its operands in shared memory and its slot back from tile j - 3 (O read by the softmax group).
         if (lane == 0) {
             constexpr uint32_t kIdS = instr_desc(kTM, kBand, false);
-            const uint64_t desc0 = smem_desc(sb, 512, 4);       // tiles differ in the start-address field only (16-byte units)
+            const uint64_t desc0 = smem_desc(sb, Lay::sbo, Lay::swizzle);       // tiles differ in the start-address field only (16-byte units)
             for (int j = 0; j < my_tiles; ++j) {
                 const int slot = j % kSlots, buf = j % kBufs;
                 if (!mbar_wait(bars + 8 * (kBarFull + buf), (j / kBufs) & 1, abort_flag, 0x402)) break;
@@ -247,7 +251,7 @@ fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
         // P: 16 bf16 = 8 columns of tensor memory per step.  The second commit hands the shared-memory buffer back.
         if (lane == 0) {
             constexpr uint32_t kIdO = instr_desc(kTM, D, true);
-            const uint64_t desc0 = smem_desc(sb, 512, 4);
+            const uint64_t desc0 = smem_desc(sb, Lay::sbo, Lay::swizzle);
             for (int j = 0; j < my_tiles; ++j) {
                 const int slot = j % kSlots, buf = j % kBufs;
                 if (!mbar_wait(bars + 8 * (kBarP + slot), (j / kSlots) & 1, abort_flag, 0x403)) break;
@@ -339,8 +343,9 @@ fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
 
             if (!__all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBarO + grp), k & 1, abort_flag, 0x412))) break;
             tc_fence_after();
-            float o[32];
-            tmem_ld32(o, tS + kOCol);
+            float o[D];
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) tmem_ld32(*reinterpret_cast<float(*)[32]>(o + 32 * c), tS + kOCol + 32 * c);
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(bars + 8 * (kBarORead + grp));       // the slot may take the next tile's S
@@ -373,14 +378,13 @@ cudaError_t read_umma_error(int* value, bool reset) {
 }
 
 bool umma_supported(int dtype, int D, const Taps& t, bool has_scale_embed) {
-    return dtype == DSQG_DTYPE_BF16 && D == 32 && !has_scale_embed && t.n_sparse == 0 &&
+    return dtype == DSQG_DTYPE_BF16 && (D == 32 || D == 64) && !has_scale_embed && t.n_sparse == 0 &&
            t.d_lo + t.n_dense - 1 <= stg::kWB && stg::tensor_map_encoder_available();
 }
 
-cudaError_t launch_fwd_umma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
-    using namespace umma;
-    constexpr int D = 32;
-    if (a.strided || a.D != D) return cudaErrorInvalidValue;
+namespace umma {
+template <int D>
+cudaError_t fwd_launch(const FwdArgs& a, const Taps& t, cudaStream_t s) {
     const long long sn = D, sh = (long long)a.N * D, sbt = (long long)a.H * a.N * D;
     CUtensorMap mq, mk, mv;
     bool hf = false;
@@ -410,6 +414,14 @@ cudaError_t launch_fwd_umma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
     const int grid = (int)(n_tiles < (long long)sms ? n_tiles : (long long)sms);
     fwd_umma_kernel<D><<<grid, kThreads, smem, s>>>(a, t, tiles_per_seq, (int)n_tiles, mq, mk, mv);
     return cudaGetLastError();
+}
+}  // namespace umma
+
+cudaError_t launch_fwd_umma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
+    if (a.strided) return cudaErrorInvalidValue;
+    if (a.D == 32) return umma::fwd_launch<32>(a, t, s);
+    if (a.D == 64) return umma::fwd_launch<64>(a, t, s);
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace dsqg

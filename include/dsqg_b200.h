@@ -66,7 +66,7 @@ int dsqg_version(void);
  * automatic choice uses where they apply), 3 = the forward with TMA-staged V wherever it applies
  * (not chosen automatically: it measures slower on B200), 4 = the forward whose dense window runs
  * on tcgen05 tensor cores with accumulators in tensor memory, for offset sets without sparse taps
- * (bf16, D = 32, offsets within 0..32; every other call goes to the automatic choice; not chosen
+ * (bf16, D = 32 or 64, offsets within 0..32; every other call goes to the automatic choice; not chosen
  * automatically).  Process-wide state. */
 int dsqg_set_kernel_path(int path);
 

@@ -1,5 +1,5 @@
 """GPU tests of the forward whose dense window runs on tcgen05 tensor cores with accumulators in tensor
-memory (kernel path 4, csrc/dsqg_umma.cu): offset sets without sparse taps, bf16, D = 32.  Checked against
+memory (kernel path 4, csrc/dsqg_umma.cu): offset sets without sparse taps, bf16, D = 32 or 64.  Checked against
 the C oracle (reference math: kernels/dsqg_attention_v3.py:60-163 without scale_embed) and against the
 default kernels; offset sets the path does not take must give the bits of the default kernels."""
 import pytest
@@ -40,7 +40,8 @@ def _forward(path, q, k, v, pb, gain, offsets):
 
 
 @pytest.mark.parametrize("shape", [(1, 2, 256, 32), (2, 3, 1000, 32), (1, 1, 1, 32), (2, 2, 127, 32), (1, 3, 129, 32),
-                                   (3, 8, 2048, 32), (40, 8, 640, 32)])
+                                   (3, 8, 2048, 32), (40, 8, 640, 32),
+                                   (1, 2, 256, 64), (2, 3, 1000, 64), (1, 1, 1, 64), (1, 3, 129, 64), (20, 12, 640, 64)])
 @pytest.mark.parametrize("name", list(DENSE_SETS))
 def test_dense_window_forward_on_tcgen05_vs_oracle_and_default_kernels(shape, name):
     B, H, N, D = shape
