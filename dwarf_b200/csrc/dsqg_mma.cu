@@ -27,43 +27,6 @@ constexpr int kMaxSparse = DSQG_MAX_TAPS;   // any number of sparse taps (they a
 constexpr int kWarps = 4;
 constexpr int kRows = 16 * kWarps; // rows per CTA
 
-struct Lane {
-    int warp, lane, g, tig;
-    bool owner;          // holds the diagonal entries of rows g and g+8
-    int owner_lane;      // lane of this quad's owner
-    __device__ Lane() {
-        warp = threadIdx.x >> 5; lane = threadIdx.x & 31; g = lane >> 2; tig = lane & 3;
-        owner = tig == (g >> 1);
-        owner_lane = (lane & ~3) | (g >> 1);
-    }
-};
-
-// acc(rows g / g+8) += x_lo * f_lo, x_hi * f_hi for this thread's elements: the diagonal form of
-// "A.B with A = diag(x)" -- row g of the product only needs row g of B, which the thread holds
-// as a row fragment for exactly the elements d its accumulators cover.
-template <int D>
-__device__ __forceinline__ void diag_fma(float (&acc)[D / 8][4], float x_lo, float x_hi, const RowFrag<D>& f_lo,
-                                         const RowFrag<D>& f_hi) {
-    // packed fp32 FMA (fma.rn.f32x2, sm_100): one instruction updates the two accumulators a row has
-    // in an n-tile; measured 1 % off the step against scalar FMAs (cfg1: 284.8 against 287.6 us)
-    unsigned long long xl, xh;
-    asm("mov.b64 %0, {%1, %1};" : "=l"(xl) : "f"(x_lo));
-    asm("mov.b64 %0, {%1, %1};" : "=l"(xh) : "f"(x_hi));
-#pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
-        const uint32_t u0 = f_lo.r[j], u1 = f_hi.r[j];
-        unsigned long long v0, v1, c0, c1;
-        asm("mov.b64 %0, {%1, %2};" : "=l"(v0) : "r"(u0 << 16), "r"(u0 & 0xffff0000u));
-        asm("mov.b64 %0, {%1, %2};" : "=l"(v1) : "r"(u1 << 16), "r"(u1 & 0xffff0000u));
-        asm("mov.b64 %0, {%1, %2};" : "=l"(c0) : "f"(acc[j][0]), "f"(acc[j][1]));
-        asm("mov.b64 %0, {%1, %2};" : "=l"(c1) : "f"(acc[j][2]), "f"(acc[j][3]));
-        asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c0) : "l"(xl), "l"(v0));
-        asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c1) : "l"(xh), "l"(v1));
-        asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[j][0]), "=f"(acc[j][1]) : "l"(c0));
-        asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[j][2]), "=f"(acc[j][3]) : "l"(c1));
-    }
-}
-
 // ------------------------------------------------------------------------------ forward
 // Online softmax over the dense window, then over the sparse taps, with the per-element
 // bookkeeping moved out of the tile loop:
@@ -76,17 +39,6 @@ __device__ __forceinline__ void diag_fma(float (&acc)[D / 8][4], float x_lo, flo
 //     (log2 units): p stays below 2^kSlack, which fp32 sums and bf16 probabilities absorb;
 //   * lanes that do not own a diagonal entry subtract +1e30 instead of the maximum, so their
 //     probability is exactly zero without a select.
-constexpr float kSlack = 16.f;
-
-template <int D>
-__device__ __forceinline__ void load_row_at(RowFrag<D>& f, const __nv_bfloat16* p) {
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
-        const uint4 u = __ldg(reinterpret_cast<const uint4*>(p + 32 * c));
-        f.r[4 * c + 0] = u.x; f.r[4 * c + 1] = u.y; f.r[4 * c + 2] = u.z; f.r[4 * c + 3] = u.w;
-    }
-}
-
 // Shared-memory tables of the scale_embed variants (reference: kernels/dsqg_attention_v3.py:112-118,
 // s_j += q.scale_embed[j] / sqrt(D)).  se_hi + se_lo are the bf16 halves of scale_embed (their sum
 // carries 16 mantissa bits), pbs[j] = pos_bias[j,h] / scale, and qs (one tile per warp,

@@ -132,19 +132,18 @@ __host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool b_mn_major)
            ((uint32_t)(M >> 4) << 24);
 }
 
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
 constexpr int kSlots = 3;                // tiles in flight per thread block = softmax warp groups = tensor-memory slots
 constexpr int kMaxBufs = 2 * kSlots;     // Q / K-band / V-band buffers in shared memory: six at D = 32, three at D = 64
 constexpr int kSlotCols = 160;           // tensor-memory columns per slot: S [0,160), then P over [0,80) and O over [128,160)
 
-template <int D>
+constexpr int kMaxSparse = 16;           // sparse taps a tile can take (kernel path 4)
+
+// SP: the offset set has sparse taps; the softmax warps then also run them (register-fed MMAs on row
+// fragments read from global memory) and hand their partial results to the row threads through a
+// per-warp scratch tile.
+template <int D, bool SP>
 struct Layout {
-    static constexpr int bufs = D == 32 ? kMaxBufs : kSlots;
+    static constexpr int bufs = D == 32 ? (SP ? 4 : kMaxBufs) : kSlots;
     static constexpr int row_bytes = 2 * D;                       // 64 / 128: one swizzle atom wide
     static constexpr int swizzle = D == 32 ? 4 : 2;               // descriptor layout code: 64-byte / 128-byte swizzle
     static constexpr int sbo = 8 * row_bytes;                     // distance of 8-row groups
@@ -153,22 +152,54 @@ struct Layout {
     static constexpr int band_bytes = kBand * row_bytes;          // 10 / 20 KB
     static constexpr int buf_bytes = q_bytes + 2 * band_bytes;    // 28 / 56 KB: Q | K band | V band
     static constexpr int bm0 = bufs * buf_bytes;
-    static constexpr int bm_bytes = 32 * kBmPitch * 4;
-    static constexpr int bars0 = bm0 + kSlots * bm_bytes;
+    static constexpr int bm_bytes = 32 * kBmPitch * 4 + kMaxSparse * 8;      // bias/mask table | sparse taps {offset, bias}
+    static constexpr int sp_pitch = D + 4;                        // floats per scratch row: D partial sums, maximum, sum
+    static constexpr int sp_bytes = SP ? 32 * sp_pitch * 4 : 0;   // per softmax warp
+    static constexpr int sp0 = bm0 + kSlots * bm_bytes;
+    static constexpr int bars0 = sp0 + 4 * kSlots * sp_bytes;
     static constexpr int total = bars0 + 256;
 };
+
+// State of one 16-row half of a warp's rows during the sparse taps (rows g and g+8 per lane).
+template <int D>
+struct Half {
+    RowFrag<D> qa, qb;
+    float m_lo, m_hi, ms_lo, ms_hi, l_lo, l_hi;
+    float O[D / 8][4];
+};
+
+// One sparse tap into the running softmax of a half: x0 / x1 are the scores of rows g / g+8 (valid on
+// the lane that owns the diagonal entry), vf0 / vf1 the value rows they weight.
+template <int D>
+__device__ __forceinline__ void fold_tap(Half<D>& hf, const Lane& L, float x0, float x1, const RowFrag<D>& vf0,
+                                         const RowFrag<D>& vf1) {
+    if (__any_sync(0xffffffffu, x0 > hf.ms_lo + kSlack || x1 > hf.ms_hi + kSlack)) {
+        const float mn_lo = fmaxf(hf.m_lo, __shfl_sync(0xffffffffu, x0, L.owner_lane));
+        const float mn_hi = fmaxf(hf.m_hi, __shfl_sync(0xffffffffu, x1, L.owner_lane));
+        const float al_lo = ex2(hf.m_lo - mn_lo), al_hi = ex2(hf.m_hi - mn_hi);
+        hf.m_lo = mn_lo; hf.m_hi = mn_hi;
+        hf.ms_lo = L.owner ? mn_lo : 1.0e30f; hf.ms_hi = L.owner ? mn_hi : 1.0e30f;
+        hf.l_lo *= al_lo; hf.l_hi *= al_hi;
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) { hf.O[j][0] *= al_lo; hf.O[j][1] *= al_lo; hf.O[j][2] *= al_hi; hf.O[j][3] *= al_hi; }
+    }
+    const float p0 = ex2(x0 - hf.ms_lo), p1 = ex2(x1 - hf.ms_hi);       // exactly 0 on lanes that own no diagonal entry
+    hf.l_lo += p0; hf.l_hi += p1;
+    diag_fma<D>(hf.O, __shfl_sync(0xffffffffu, p0, L.owner_lane), __shfl_sync(0xffffffffu, p1, L.owner_lane), vf0, vf1);
+}
 
 // barrier slots (8 bytes each) behind the tables
 enum { kBarFull = 0, kBarEmpty = kBarFull + kMaxBufs, kBarS = kBarEmpty + kMaxBufs, kBarP = kBarS + kSlots,
        kBarO = kBarP + kSlots, kBarORead = kBarO + kSlots, kNumBars = kBarORead + kSlots };
 
-template <int D>
+template <int D, bool SP>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
                 const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v) {
     static_assert(D == 32 || D == 64, "a row is one 64-byte or 128-byte swizzle atom");
-    using Lay = Layout<D>;
+    static_assert(!SP || D == 32, "the scratch tiles of the sparse taps fit next to the operand buffers at D = 32 only");
+    using Lay = Layout<D, SP>;
     constexpr int kBufs = Lay::bufs, kOCol = Lay::o_col;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -270,6 +301,8 @@ fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
         // ================================================================= softmax groups: thread = query row
         const int grp = warp >> 2, wq = warp & 3, r = tid & (kTM - 1), l = lane;
         float* Bm = reinterpret_cast<float*>(smem + Lay::bm0 + grp * Lay::bm_bytes);
+        int2* tap_s = reinterpret_cast<int2*>(smem + Lay::bm0 + grp * Lay::bm_bytes + 32 * kBmPitch * 4);
+        float* scratch = reinterpret_cast<float*>(smem + Lay::sp0 + warp * Lay::sp_bytes);
         const uint32_t tS = tmem + kSlotCols * grp + ((uint32_t)(32 * wq) << 16);
         const float c2 = a.scale * kLog2e;
         const int d_lo = t.d_lo, d_hi = t.d_lo + t.n_dense - 1;
@@ -284,6 +317,8 @@ fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
                     const int ll = e >> 6, cc = e & 63, delta = ll + 32 - cc;
                     Bm[ll * kBmPitch + cc] = (delta >= d_lo && delta <= d_hi) ? a.pos_bias[(delta - d_lo) * H + h] * kLog2e : kNeg;
                 }
+                if (SP && r < t.n_sparse)
+                    tap_s[r] = make_int2(t.sparse[r], __float_as_int(a.pos_bias[(t.n_dense + r) * H + h] * kLog2e));
                 asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
                 cur_h = h;
             }
@@ -315,8 +350,8 @@ fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
                 m4[0] = fmaxf(m4[0], z[c]); m4[1] = fmaxf(m4[1], z[c + 1]);
                 m4[2] = fmaxf(m4[2], z[c + 2]); m4[3] = fmaxf(m4[3], z[c + 3]);
             }
-            float m = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-            m = m < kMinM ? 0.f : m;             // a row without a valid tap: every p becomes 0
+            const float m_raw = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            const float m = m_raw < kMinM ? 0.f : m_raw;      // a row without a valid tap: every p becomes 0
             // P (bf16 pairs) replaces S in tensor memory: band column c sits in 32-bit column c / 2, so the
             // row's window is columns 16 wq .. 16 wq + 31 of the 80; the other 48 are zeroed
             float s4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -341,6 +376,94 @@ fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
             tc_fence_before();
             mbar_arrive(bars + 8 * (kBarP + grp));
 
+            if constexpr (SP) {
+                // ---- sparse taps of the warp's two 16-row halves while the tensor cores form O: the default
+                // kernels' scheme (dsqg_mma.cu): Q and the tap's key rows as row fragments, the 16 x 16 score
+                // tile by mma.sync, its diagonal into an online softmax, P.V as a diagonal update.  The
+                // running maximum of a row starts at its dense-window maximum.
+                const Lane L;
+                const size_t seq = (size_t)bh * N * D;
+                const __nv_bfloat16* qg = static_cast<const __nv_bfloat16*>(a.q) + seq;
+                const __nv_bfloat16* kg = static_cast<const __nv_bfloat16*>(a.k) + seq + 8 * L.tig;
+                const __nv_bfloat16* vg = static_cast<const __nv_bfloat16*>(a.v) + seq + 8 * L.tig;
+                const int gw = n0 + 32 * wq;                  // first row of the warp
+                Half<D> hs[2];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int row_lo = gw + 16 * hh + L.g, row_hi = row_lo + 8;
+                    load_row(hs[hh].qa, qg + (size_t)row_lo * D, L.tig, row_lo < N);
+                    load_row(hs[hh].qb, qg + (size_t)row_hi * D, L.tig, row_hi < N);
+                    hs[hh].m_lo = fmaxf(__shfl_sync(0xffffffffu, m_raw, 16 * hh + L.g), kMinM);
+                    hs[hh].m_hi = fmaxf(__shfl_sync(0xffffffffu, m_raw, 16 * hh + L.g + 8), kMinM);
+                    hs[hh].ms_lo = L.owner ? hs[hh].m_lo : 1.0e30f; hs[hh].ms_hi = L.owner ? hs[hh].m_hi : 1.0e30f;
+                    hs[hh].l_lo = 0.f; hs[hh].l_hi = 0.f;
+#pragma unroll
+                    for (int jj = 0; jj < D / 8; ++jj) { hs[hh].O[jj][0] = 0.f; hs[hh].O[jj][1] = 0.f; hs[hh].O[jj][2] = 0.f; hs[hh].O[jj][3] = 0.f; }
+                }
+                const int ns = t.n_sparse;
+#pragma unroll 1
+                for (int si = 0; si < ns; ++si) {
+                    const int2 tp = tap_s[si];
+                    const int delta = tp.x;
+                    const float pbv = __int_as_float(tp.y);
+                    if (gw + 31 < delta) break;                  // taps ascend: no row of the warp reaches back that far
+                    if (gw >= delta && gw + 32 <= N) {
+                        // all 32 key rows exist: no predicates, the eight row loads in flight together
+                        const __nv_bfloat16* kp = kg + (ptrdiff_t)(gw + L.g - delta) * D;
+                        const __nv_bfloat16* vp = vg + (ptrdiff_t)(gw + L.g - delta) * D;
+                        RowFrag<D> kf[4], vf[4];
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) { load_row_at(kf[q4], kp + 8 * q4 * D); load_row_at(vf[q4], vp + 8 * q4 * D); }
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            float s0[4], s1[4];
+                            mma_rows_z(s0, hs[hh].qa, hs[hh].qb, kf[2 * hh]);
+                            mma_rows_z(s1, hs[hh].qa, hs[hh].qb, kf[2 * hh + 1]);
+                            const float d0 = (L.g & 1) ? s0[1] : s0[0], d1 = (L.g & 1) ? s1[3] : s1[2];
+                            fold_tap(hs[hh], L, fmaf(d0, c2, pbv), fmaf(d1, c2, pbv), vf[2 * hh], vf[2 * hh + 1]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            const int g0 = gw + 16 * hh;
+                            if (g0 + 15 < delta || g0 >= N) continue;
+                            const int kr0 = g0 + L.g - delta, kr1 = kr0 + 8;
+                            const bool v0 = kr0 >= 0 && kr0 < N, v1 = kr1 >= 0 && kr1 < N;
+                            RowFrag<D> kf0, kf1, vf0, vf1;
+                            load_row(kf0, kg + (ptrdiff_t)kr0 * D - 8 * L.tig, L.tig, v0);
+                            load_row(kf1, kg + (ptrdiff_t)kr1 * D - 8 * L.tig, L.tig, v1);
+                            load_row(vf0, vg + (ptrdiff_t)kr0 * D - 8 * L.tig, L.tig, v0);
+                            load_row(vf1, vg + (ptrdiff_t)kr1 * D - 8 * L.tig, L.tig, v1);
+                            float s0[4], s1[4];
+                            mma_rows_z(s0, hs[hh].qa, hs[hh].qb, kf0);
+                            mma_rows_z(s1, hs[hh].qa, hs[hh].qb, kf1);
+                            const float d0 = (L.g & 1) ? s0[1] : s0[0], d1 = (L.g & 1) ? s1[3] : s1[2];
+                            fold_tap(hs[hh], L, v0 ? fmaf(d0, c2, pbv) : kNeg, v1 ? fmaf(d1, c2, pbv) : kNeg, vf0, vf1);
+                        }
+                    }
+                }
+                // partial sums, maximum and sum of each row to the row's thread through the warp's scratch tile
+                // (accumulator tile 4 c + i, columns 2 tig, 2 tig + 1 = elements 32 c + 8 tig + 2 i, + 1)
+                __syncwarp();
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    float* lo = scratch + (16 * hh + L.g) * Lay::sp_pitch;
+                    float* hi = lo + 8 * Lay::sp_pitch;
+#pragma unroll
+                    for (int jj = 0; jj < D / 8; ++jj) {
+                        const int col = 32 * (jj >> 2) + 8 * L.tig + 2 * (jj & 3);
+                        *reinterpret_cast<float2*>(lo + col) = make_float2(hs[hh].O[jj][0], hs[hh].O[jj][1]);
+                        *reinterpret_cast<float2*>(hi + col) = make_float2(hs[hh].O[jj][2], hs[hh].O[jj][3]);
+                    }
+                    const float sl = quad_sum(hs[hh].l_lo), sh = quad_sum(hs[hh].l_hi);
+                    if (L.tig == 0) {
+                        *reinterpret_cast<float2*>(lo + D) = make_float2(hs[hh].m_lo, sl);
+                        *reinterpret_cast<float2*>(hi + D) = make_float2(hs[hh].m_hi, sh);
+                    }
+                }
+                __syncwarp();
+            }
+
             if (!__all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBarO + grp), k & 1, abort_flag, 0x412))) break;
             tc_fence_after();
             float o[D];
@@ -349,15 +472,29 @@ fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(bars + 8 * (kBarORead + grp));       // the slot may take the next tile's S
+            float m_out = m, l_out = lsum;
+            if constexpr (SP) {
+                // this row's sparse partials: weights relative to ms >= the dense maximum
+                const float* row = scratch + l * Lay::sp_pitch;
+                const float2 st = *reinterpret_cast<const float2*>(row + D);
+                const float ad = lsum > 0.f ? ex2(m - st.x) : 0.f;
+#pragma unroll
+                for (int c = 0; c < D / 4; ++c) {
+                    const float4 sp4 = *reinterpret_cast<const float4*>(row + 4 * c);
+                    o[4 * c + 0] = fmaf(o[4 * c + 0], ad, sp4.x); o[4 * c + 1] = fmaf(o[4 * c + 1], ad, sp4.y);
+                    o[4 * c + 2] = fmaf(o[4 * c + 2], ad, sp4.z); o[4 * c + 3] = fmaf(o[4 * c + 3], ad, sp4.w);
+                }
+                m_out = st.x; l_out = fmaf(lsum, ad, st.y);
+            }
             if (n < N) {
                 const float gain = a.head_gain ? a.head_gain[h] : 1.f;
-                const float sc = lsum > 0.f ? __fdividef(gain, lsum) : 0.f;
+                const float sc = l_out > 0.f ? __fdividef(gain, l_out) : 0.f;
                 uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + ((size_t)bh * N + n) * D);
 #pragma unroll
                 for (int c = 0; c < D / 8; ++c)
                     dst[c] = make_uint4(pack_bf16x2(o[8 * c] * sc, o[8 * c + 1] * sc), pack_bf16x2(o[8 * c + 2] * sc, o[8 * c + 3] * sc),
                                         pack_bf16x2(o[8 * c + 4] * sc, o[8 * c + 5] * sc), pack_bf16x2(o[8 * c + 6] * sc, o[8 * c + 7] * sc));
-                a.lse[(size_t)bh * N + n] = lsum > 0.f ? (m + __log2f(lsum)) * kLn2 : -INFINITY;
+                a.lse[(size_t)bh * N + n] = l_out > 0.f ? (m_out + __log2f(l_out)) * kLn2 : -INFINITY;
             }
         }
     }
@@ -378,12 +515,13 @@ cudaError_t read_umma_error(int* value, bool reset) {
 }
 
 bool umma_supported(int dtype, int D, const Taps& t, bool has_scale_embed) {
-    return dtype == DSQG_DTYPE_BF16 && (D == 32 || D == 64) && !has_scale_embed && t.n_sparse == 0 &&
+    return dtype == DSQG_DTYPE_BF16 && (D == 32 || (D == 64 && t.n_sparse == 0)) && !has_scale_embed &&
+           t.n_sparse <= umma::kMaxSparse &&
            t.d_lo + t.n_dense - 1 <= stg::kWB && stg::tensor_map_encoder_available();
 }
 
 namespace umma {
-template <int D>
+template <int D, bool SP>
 cudaError_t fwd_launch(const FwdArgs& a, const Taps& t, cudaStream_t s) {
     const long long sn = D, sh = (long long)a.N * D, sbt = (long long)a.H * a.N * D;
     CUtensorMap mq, mk, mv;
@@ -392,7 +530,7 @@ cudaError_t fwd_launch(const FwdArgs& a, const Taps& t, cudaStream_t s) {
         !stg::make_map(&mk, &hf, a.k, a.B, a.H, a.N, D, sbt, sh, sn, kBand) || hf ||
         !stg::make_map(&mv, &hf, a.v, a.B, a.H, a.N, D, sbt, sh, sn, kBand) || hf)
         return cudaErrorInvalidValue;
-    const int smem = Layout<D>::total + 1024;
+    const int smem = Layout<D, SP>::total + 1024;
     int dev = 0, sms = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
@@ -402,7 +540,7 @@ cudaError_t fwd_launch(const FwdArgs& a, const Taps& t, cudaStream_t s) {
         std::lock_guard<std::mutex> lock(mu);
         if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
         if (!attr_done[dev]) {
-            if ((e = cudaFuncSetAttribute(fwd_umma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return e;
+            if ((e = cudaFuncSetAttribute(fwd_umma_kernel<D, SP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return e;
             if ((e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
             attr_done[dev] = 1;
         }
@@ -412,15 +550,15 @@ cudaError_t fwd_launch(const FwdArgs& a, const Taps& t, cudaStream_t s) {
     const long long n_tiles = (long long)a.B * a.H * tiles_per_seq;
     if (n_tiles > 0x7fffffffLL) return cudaErrorInvalidValue;
     const int grid = (int)(n_tiles < (long long)sms ? n_tiles : (long long)sms);
-    fwd_umma_kernel<D><<<grid, kThreads, smem, s>>>(a, t, tiles_per_seq, (int)n_tiles, mq, mk, mv);
+    fwd_umma_kernel<D, SP><<<grid, kThreads, smem, s>>>(a, t, tiles_per_seq, (int)n_tiles, mq, mk, mv);
     return cudaGetLastError();
 }
 }  // namespace umma
 
 cudaError_t launch_fwd_umma(const FwdArgs& a, const Taps& t, cudaStream_t s) {
     if (a.strided) return cudaErrorInvalidValue;
-    if (a.D == 32) return umma::fwd_launch<32>(a, t, s);
-    if (a.D == 64) return umma::fwd_launch<64>(a, t, s);
+    if (a.D == 32) return t.n_sparse ? umma::fwd_launch<32, true>(a, t, s) : umma::fwd_launch<32, false>(a, t, s);
+    if (a.D == 64 && t.n_sparse == 0) return umma::fwd_launch<64, false>(a, t, s);
     return cudaErrorInvalidValue;
 }
 

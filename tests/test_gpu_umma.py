@@ -90,13 +90,57 @@ def test_backward_after_the_tcgen05_forward_matches_the_oracle():
         assert_bf16_close(t.grad.float().cpu(), ref[nm], nm)
 
 
-def test_sets_with_sparse_taps_fall_through_to_the_default_kernels():
-    B, H, N, D = 1, 2, 1700, 32
-    g = torch.Generator().manual_seed(5)
+@pytest.mark.parametrize("shape", [(1, 2, 256, 32), (2, 3, 1000, 32), (1, 1, 1, 32), (2, 2, 127, 32), (1, 3, 129, 32),
+                                   (2, 8, 2048, 32), (1, 2, 1700, 32), (20, 8, 640, 32)])
+@pytest.mark.parametrize("offsets", [O.OFFSETS_43, O.OFFSETS_44, tuple(range(1, 30)) + (40, 77, 1500),
+                                     tuple(range(33)) + tuple(range(33, 49))],
+                         ids=["J43", "J44", "odd", "16-sparse"])
+def test_forward_with_sparse_taps_on_the_tcgen05_path_vs_oracle(shape, offsets):
+    """Offset sets with sparse taps at D = 32: dense window on tcgen05, sparse taps by the softmax warps."""
+    B, H, N, D = shape
+    g = torch.Generator().manual_seed(17 + N + len(offsets))
     q, k, v = (bf16_valued(B, H, N, D, scale=0.5, gen=g) for _ in range(3))
-    pb = synth.log_linear_pos_bias(O.OFFSETS_43, H)
+    pb = synth.log_linear_pos_bias(offsets, H) + torch.randn(len(offsets), H, generator=g) * 0.05
+    gain = torch.rand(H, generator=g) * 0.4 + 0.8
+    ref = oracle_fwd_bwd(q, k, v, pb, None, None, gain, offsets)
+    dev = torch.device("cuda", 0)
+    args = [t.bfloat16().to(dev) for t in (q, k, v)] + [pb.to(dev), gain.to(dev)]
+    out4, lse4 = _forward(4, *args, offsets)
+    out2, lse2 = _forward(2, *args, offsets)
+    assert not torch.isnan(out4).any()
+    assert_bf16_close(out4.float().cpu(), ref["out"], "out")
+    empty = torch.isinf(lse2)
+    assert torch.equal(torch.isinf(lse4), empty)
+    if (~empty).any():
+        assert (lse4[~empty] - lse2[~empty]).abs().max().item() <= 2e-3
+        assert (lse4[~empty].cpu() - ref["lse"][~empty.cpu()]).abs().max().item() <= 2e-3
+
+
+def test_large_sparse_scores_move_the_running_maximum():
+    """A sparse tap far above the dense window's maximum (rescale path of the online softmax)."""
+    B, H, N, D = 1, 2, 1600, 32
+    offsets = O.OFFSETS_43
+    g = torch.Generator().manual_seed(23)
+    q, k, v = (bf16_valued(B, H, N, D, scale=0.5, gen=g) for _ in range(3))
+    pb = synth.log_linear_pos_bias(offsets, H)
+    pb[40] += 60.0                                   # offset 768 dominates wherever it is valid
+    pb[35] += 25.0
+    ref = oracle_fwd_bwd(q, k, v, pb, None, None, None, offsets)
     dev = torch.device("cuda", 0)
     args = [t.bfloat16().to(dev) for t in (q, k, v)] + [pb.to(dev), None]
-    out4, lse4 = _forward(4, *args, O.OFFSETS_43)
-    out0, lse0 = _forward(0, *args, O.OFFSETS_43)
-    assert torch.equal(out4, out0) and torch.equal(lse4, lse0)
+    out4, lse4 = _forward(4, *args, offsets)
+    assert_bf16_close(out4.float().cpu(), ref["out"], "out")
+    assert (lse4.cpu() - ref["lse"]).abs().max().item() <= 2e-3 * max(1.0, ref["lse"].abs().max().item())
+
+
+def test_what_the_path_does_not_take_falls_through_to_the_default_kernels():
+    """D = 64 with sparse taps, dense windows wider than 32: the bits of the automatic choice."""
+    dev = torch.device("cuda", 0)
+    for (B, H, N, D), offsets in (((1, 2, 1700, 64), O.OFFSETS_43), ((1, 2, 300, 32), tuple(range(41)) + (128,))):
+        g = torch.Generator().manual_seed(5)
+        q, k, v = (bf16_valued(B, H, N, D, scale=0.5, gen=g) for _ in range(3))
+        pb = synth.log_linear_pos_bias(offsets, H)
+        args = [t.bfloat16().to(dev) for t in (q, k, v)] + [pb.to(dev), None]
+        out4, lse4 = _forward(4, *args, offsets)
+        out0, lse0 = _forward(0, *args, offsets)
+        assert torch.equal(out4, out0) and torch.equal(lse4, lse0)
