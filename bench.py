@@ -688,7 +688,7 @@ def main():
     ap.add_argument("--decode-layers", type=int, default=0, help="cfg3: number of layers (default: the 10 of the configuration)")
     ap.add_argument("--kernel-path", type=int, default=0,
                     help="dsqg_set_kernel_path value for A/B runs: 0 automatic (default), 1 generic, 2 tensor-core, "
-                         "3 forward with TMA-staged V, 4 forward with the dense window on tcgen05 (dense-only offset sets)")
+                         "3 forward with TMA-staged V, 4 forward with the dense window on tcgen05 and tensor memory")
     ap.add_argument("--dense-window-only", action="store_true",
                     help="op workloads: keep only the offsets 0..32 of the configuration's set (A/B measurement of the "
                          "dense-window part of the kernels; not a configuration of the specification)")

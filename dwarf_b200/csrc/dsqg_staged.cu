@@ -35,11 +35,6 @@ constexpr int kWarps = kRows / 16;
 constexpr int kThreads = kWarps * 32;
 constexpr uint32_t kOnes = 0x3F803F80u;    // bf16x2 {1, 1}
 
-struct Lane {
-    int warp, lane, g, tig;
-    __device__ Lane() { warp = threadIdx.x >> 5; lane = threadIdx.x & 31; g = lane >> 2; tig = lane & 3; }
-};
-
 // Shared-memory carve-up (byte offsets from a 1024-byte boundary).
 //   y : staged partner tiles     stage : kRows x D output staging tiles (n_stage of them)     tab : tables
 template <int D>
@@ -110,16 +105,6 @@ __device__ __forceinline__ void issue_copies(const Plan& pl, int lane, int n_rea
     __syncwarp();
     if (lane < pl.n_box && pl.box_seg[lane] < n_reach)
         ty.load(sy + (uint32_t)pl.box_row0[lane] * RB, bars + 8 * pl.box_seg[lane], own0 + pl.box_rel[lane], h, b);
-}
-
-// this thread's 16-byte chunks of a row that is known to exist (p points at the thread's first chunk)
-template <int D>
-__device__ __forceinline__ void load_row_at(RowFrag<D>& f, const __nv_bfloat16* p) {
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
-        const uint4 u = __ldg(reinterpret_cast<const uint4*>(p + 32 * c));
-        f.r[4 * c + 0] = u.x; f.r[4 * c + 1] = u.y; f.r[4 * c + 2] = u.z; f.r[4 * c + 3] = u.w;
-    }
 }
 
 // ------------------------------------------------------------------------------ forward

@@ -65,9 +65,9 @@ int dsqg_version(void);
  * (default), 1 = always use the generic CUDA-core kernels, 2 = the tensor-core kernels (what the
  * automatic choice uses where they apply), 3 = the forward with TMA-staged V wherever it applies
  * (not chosen automatically: it measures slower on B200), 4 = the forward whose dense window runs
- * on tcgen05 tensor cores with accumulators in tensor memory, for offset sets without sparse taps
- * (bf16, D = 32 or 64, offsets within 0..32; every other call goes to the automatic choice; not chosen
- * automatically).  Process-wide state. */
+ * on tcgen05 tensor cores with accumulators in tensor memory (bf16, no scale_embed, dense window
+ * within offsets 0..32; D = 32 with up to 16 sparse taps, D = 64 without sparse taps; every other
+ * call goes to the automatic choice; not chosen automatically).  Process-wide state. */
 int dsqg_set_kernel_path(int path);
 
 /* Device-side error word of the current device (no counterpart in the reference).  The

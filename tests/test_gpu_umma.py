@@ -93,7 +93,7 @@ def test_backward_after_the_tcgen05_forward_matches_the_oracle():
 @pytest.mark.parametrize("shape", [(1, 2, 256, 32), (2, 3, 1000, 32), (1, 1, 1, 32), (2, 2, 127, 32), (1, 3, 129, 32),
                                    (2, 8, 2048, 32), (1, 2, 1700, 32), (20, 8, 640, 32)])
 @pytest.mark.parametrize("offsets", [O.OFFSETS_43, O.OFFSETS_44, tuple(range(1, 30)) + (40, 77, 1500),
-                                     tuple(range(33)) + tuple(range(33, 49))],
+                                     tuple(range(32)) + tuple(range(40, 40 + 16 * 24, 24))],
                          ids=["J43", "J44", "odd", "16-sparse"])
 def test_forward_with_sparse_taps_on_the_tcgen05_path_vs_oracle(shape, offsets):
     """Offset sets with sparse taps at D = 32: dense window on tcgen05, sparse taps by the softmax warps."""
@@ -109,6 +109,8 @@ def test_forward_with_sparse_taps_on_the_tcgen05_path_vs_oracle(shape, offsets):
     out2, lse2 = _forward(2, *args, offsets)
     assert not torch.isnan(out4).any()
     assert_bf16_close(out4.float().cpu(), ref["out"], "out")
+    if N >= 1000:       # other arithmetic than the default kernels: equal bits would mean the path was not taken
+        assert not torch.equal(out4, out2)
     empty = torch.isinf(lse2)
     assert torch.equal(torch.isinf(lse4), empty)
     if (~empty).any():
