@@ -5,15 +5,21 @@
 // Reference math: kernels/dsqg_attention_v3.py:60-163 (scores, bias, causal mask, softmax over the
 // taps, weighted sum of the value rows) without scale_embed.
 //
-// A thread block is persistent and walks a contiguous range of 128-row tiles.  Per tile
-//   producer (warp 4, one lane):  copies Q[128 x D], the key band K[n0-32, n0+128) and the value
-//       band into shared memory (cp.async.bulk.tensor, double buffered, one tile ahead), then issues
-//       S = Q . Kband^T        (M 128, N 160, K = D)  -> tensor memory columns [0, 160)
-//       O = P . Vband          (M 128, N D,  K = 160) -> tensor memory columns [160, 160 + D)
-//   softmax (warps 0-3, one thread per query row = tensor-memory lane): reads its row's 64-column
-//       window of S (tcgen05.ld), adds the bias / mask table, takes the row maximum and
-//       the exponentials, writes P as bf16 pairs over S in tensor memory (the A operand of the second
-//       product; zero outside the row's window), later reads O, scales by gain / sum and stores the row.
+// One persistent thread block per SM walks a contiguous range of 128-row tiles, three tiles in flight
+// (tile j uses tensor-memory slot j % 3, a 160-column third of the SM's 512 columns, softmax group
+// j % 3, and one of the Q / K-band / V-band buffers in shared memory):
+//   copy warp (one lane):  Q[128 x D], the key band K[n0-32, n0+128) and the value band of a tile into
+//       a free buffer (cp.async.bulk.tensor; rows outside the sequence arrive as zeros);
+//   S warp (one lane):     S = Q . Kband^T   (tcgen05.mma M 128, N 160, K 16 per step) -> slot columns [0, 160)
+//   softmax group (4 warps, one thread per query row = tensor-memory lane): reads its row's 64-column
+//       window of S (tcgen05.ld), adds the bias / mask table, takes the row maximum and the
+//       exponentials, writes P as bf16 pairs over S (tcgen05.st: the A operand of the second product;
+//       zero outside the row's window), [runs the sparse taps, see Half / fold_tap], reads O, scales by
+//       gain / sum and stores the row;
+//   O warp (one lane):     O = P . Vband     (M 128, N D, K 16 per step, A from tensor memory, B MN-major
+//       from shared memory) -> the last D columns of the slot, dead once S has been read.
+// Every hand-over is an mbarrier: copies -> S warp (full), tcgen05.commit -> softmax (S ready), softmax ->
+// O warp (P written), commit -> softmax (O ready) and -> copy warp (buffer free), softmax -> S warp (O read).
 // Row r of warp w (r = 32 w + l) needs band columns c = r + 32 - delta, delta = 0..32, i.e.
 // c - 32 w in [l, l + 32]: a window of 64 columns per warp holds them, and the bias/mask table
 // Bm[l][c - 32 w] (pos_bias[delta, h] * log2 e inside the window, "minus infinity" outside) is
