@@ -407,63 +407,45 @@ fwd_umma_kernel(const FwdArgs a, const Taps t, int tiles_per_seq, int n_tiles,
                     for (int jj = 0; jj < D / 8; ++jj) { hs[hh].O[jj][0] = 0.f; hs[hh].O[jj][1] = 0.f; hs[hh].O[jj][2] = 0.f; hs[hh].O[jj][3] = 0.f; }
                 }
                 const int ns = t.n_sparse;
-                // Taps ascend, so the taps whose 32 key rows all exist are a prefix of the list: they run without
-                // predicates and software-pipelined (the eight row loads of the next tap are in flight while
-                // this one is folded in); the few that reach across row 0 or N follow, predicated.
-                int n_full = 0;
-                if (gw + 32 <= N)
-                    while (n_full < ns && tap_s[n_full].x <= gw) ++n_full;
-                auto load_tap = [&](int si, RowFrag<D> (&kx)[4], RowFrag<D> (&vx)[4]) {
-                    const ptrdiff_t off = (ptrdiff_t)(gw + L.g - tap_s[si].x) * D;
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) { load_row_at(kx[q4], kg + off + 8 * q4 * D); load_row_at(vx[q4], vg + off + 8 * q4 * D); }
-                };
-                auto fold_full = [&](int si, const RowFrag<D> (&kx)[4], const RowFrag<D> (&vx)[4]) {
-                    const float pbv = __int_as_float(tap_s[si].y);
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        float s0[4], s1[4];
-                        mma_rows_z(s0, hs[hh].qa, hs[hh].qb, kx[2 * hh]);
-                        mma_rows_z(s1, hs[hh].qa, hs[hh].qb, kx[2 * hh + 1]);
-                        const float d0 = (L.g & 1) ? s0[1] : s0[0], d1 = (L.g & 1) ? s1[3] : s1[2];
-                        fold_tap(hs[hh], L, fmaf(d0, c2, pbv), fmaf(d1, c2, pbv), vx[2 * hh], vx[2 * hh + 1]);
-                    }
-                };
-                {
-                    RowFrag<D> ka[4], va[4], kb[4], vb[4];
-                    if (n_full > 0) load_tap(0, ka, va);
-                    int si = 0;
 #pragma unroll 1
-                    for (; si + 1 < n_full; si += 2) {
-                        load_tap(si + 1, kb, vb);
-                        fold_full(si, ka, va);
-                        if (si + 2 < n_full) load_tap(si + 2, ka, va);
-                        fold_full(si + 1, kb, vb);
-                    }
-                    if (si < n_full) fold_full(si, ka, va);
-                }
-#pragma unroll 1
-                for (int si = n_full; si < ns; ++si) {
+                for (int si = 0; si < ns; ++si) {
                     const int2 tp = tap_s[si];
                     const int delta = tp.x;
                     const float pbv = __int_as_float(tp.y);
                     if (gw + 31 < delta) break;                  // taps ascend: no row of the warp reaches back that far
+                    if (gw >= delta && gw + 32 <= N) {
+                        // all 32 key rows exist: no predicates, the eight row loads in flight together
+                        const __nv_bfloat16* kp = kg + (ptrdiff_t)(gw + L.g - delta) * D;
+                        const __nv_bfloat16* vp = vg + (ptrdiff_t)(gw + L.g - delta) * D;
+                        RowFrag<D> kf[4], vf[4];
 #pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        const int g0 = gw + 16 * hh;
-                        if (g0 + 15 < delta || g0 >= N) continue;
-                        const int kr0 = g0 + L.g - delta, kr1 = kr0 + 8;
-                        const bool v0 = kr0 >= 0 && kr0 < N, v1 = kr1 >= 0 && kr1 < N;
-                        RowFrag<D> kf0, kf1, vf0, vf1;
-                        load_row(kf0, kg + (ptrdiff_t)kr0 * D - 8 * L.tig, L.tig, v0);
-                        load_row(kf1, kg + (ptrdiff_t)kr1 * D - 8 * L.tig, L.tig, v1);
-                        load_row(vf0, vg + (ptrdiff_t)kr0 * D - 8 * L.tig, L.tig, v0);
-                        load_row(vf1, vg + (ptrdiff_t)kr1 * D - 8 * L.tig, L.tig, v1);
-                        float s0[4], s1[4];
-                        mma_rows_z(s0, hs[hh].qa, hs[hh].qb, kf0);
-                        mma_rows_z(s1, hs[hh].qa, hs[hh].qb, kf1);
-                        const float d0 = (L.g & 1) ? s0[1] : s0[0], d1 = (L.g & 1) ? s1[3] : s1[2];
-                        fold_tap(hs[hh], L, v0 ? fmaf(d0, c2, pbv) : kNeg, v1 ? fmaf(d1, c2, pbv) : kNeg, vf0, vf1);
+                        for (int q4 = 0; q4 < 4; ++q4) { load_row_at(kf[q4], kp + 8 * q4 * D); load_row_at(vf[q4], vp + 8 * q4 * D); }
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            float s0[4], s1[4];
+                            mma_rows_z(s0, hs[hh].qa, hs[hh].qb, kf[2 * hh]);
+                            mma_rows_z(s1, hs[hh].qa, hs[hh].qb, kf[2 * hh + 1]);
+                            const float d0 = (L.g & 1) ? s0[1] : s0[0], d1 = (L.g & 1) ? s1[3] : s1[2];
+                            fold_tap(hs[hh], L, fmaf(d0, c2, pbv), fmaf(d1, c2, pbv), vf[2 * hh], vf[2 * hh + 1]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            const int g0 = gw + 16 * hh;
+                            if (g0 + 15 < delta || g0 >= N) continue;
+                            const int kr0 = g0 + L.g - delta, kr1 = kr0 + 8;
+                            const bool v0 = kr0 >= 0 && kr0 < N, v1 = kr1 >= 0 && kr1 < N;
+                            RowFrag<D> kf0, kf1, vf0, vf1;
+                            load_row(kf0, kg + (ptrdiff_t)kr0 * D - 8 * L.tig, L.tig, v0);
+                            load_row(kf1, kg + (ptrdiff_t)kr1 * D - 8 * L.tig, L.tig, v1);
+                            load_row(vf0, vg + (ptrdiff_t)kr0 * D - 8 * L.tig, L.tig, v0);
+                            load_row(vf1, vg + (ptrdiff_t)kr1 * D - 8 * L.tig, L.tig, v1);
+                            float s0[4], s1[4];
+                            mma_rows_z(s0, hs[hh].qa, hs[hh].qb, kf0);
+                            mma_rows_z(s1, hs[hh].qa, hs[hh].qb, kf1);
+                            const float d0 = (L.g & 1) ? s0[1] : s0[0], d1 = (L.g & 1) ? s1[3] : s1[2];
+                            fold_tap(hs[hh], L, v0 ? fmaf(d0, c2, pbv) : kNeg, v1 ? fmaf(d1, c2, pbv) : kNeg, vf0, vf1);
+                        }
                     }
                 }
                 // partial sums, maximum and sum of each row to the row's thread through the warp's scratch tile
