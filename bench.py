@@ -211,6 +211,46 @@ def small_op_line(cfg, dev, world, steps, warmup, x=None):
             "frac": 12 * T / (ms * 1e-3) / 1e9 / peak, "l2_flushed": flushed}
 
 
+def forward_paths_line(dev, restore_path, steps=20, warmup=5):
+    """Forward only, default register-fed kernel (path 2) against the forward whose dense window runs on
+    tcgen05 tensor cores with tensor-memory accumulators (path 4, csrc/dsqg_umma.cu): the dense window
+    alone (offsets 0..31) at the cfg1 and cfg2 shapes, and the whole cfg1 forward.  CUDA events around
+    every call, L2 flushed between calls; us per forward (median)."""
+    import dataclasses
+    from dwarf_b200 import _lib, synth
+    lib = _lib.load()
+    res = {"what": "forward only: path 2 = register-fed mma.sync kernel (default), path 4 = dense window on tcgen05 / "
+                   "tensor memory; us per call, median, L2 flushed"}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    cases = [("cfg1_dense_window", "cfg1", True), ("cfg2_dense_window", "cfg2", True), ("cfg1_all_offsets", "cfg1", False)]
+    try:
+        for name, base, dense in cases:
+            cfg = synth.OP_CONFIGS[base]
+            if dense:
+                cfg = dataclasses.replace(cfg, offsets=tuple(o for o in cfg.offsets if o <= 32))
+            prob = OpProblem(cfg, dev, synth.make_op_inputs(cfg))
+            row = {"offsets": len(cfg.offsets)}
+            for path, key in ((2, "mma_sync_us"), (4, "tcgen05_us")):
+                _lib.check(lib.dsqg_set_kernel_path(path), "dsqg_set_kernel_path")
+                for _ in range(warmup):
+                    prob.fwd()
+                ts = []
+                for i in range(steps):
+                    flush.fill_(i & 0xff)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(prob.stream); prob.fwd(); e1.record(prob.stream)
+                    torch.cuda.synchronize()
+                    ts.append(e0.elapsed_time(e1) * 1e3)
+                row[key] = sorted(ts)[len(ts) // 2]
+            res[name] = row
+            del prob
+            torch.cuda.empty_cache()
+        res["device_error"] = lib.dsqg_device_error(1)
+    finally:
+        lib.dsqg_set_kernel_path(restore_path)
+    return res
+
+
 def api_line(cfg, dev, world, steps, warmup, x):
     """fwd+bwd through the operator a reference script calls (dsqg_attention -> DSQGFunction, the
     replacement of kernels/dsqg_attention_v3.py:445-456): device-resident tensors, result tensors
@@ -378,8 +418,10 @@ def run_op_workload(args, cfg, rank, local_rank, world):
         line["decode"] = {"workload": d["config"]["workload"], "tokens_per_s": d["value"], "ms_per_step": d["ms_per_step"],
                           "ms_per_step_eager": d["ms_per_step_eager"], "ring_gbs": d["roofline"]["achieved"],
                           "frac": d["roofline"]["frac"], "steps": dargs.steps, "launch": d["config"]["launch"]}
+        if world == 1:
+            line["forward_paths"] = forward_paths_line(dev, args.kernel_path)
         if rank == 0:
-            line["extras_clocks"] = sampler2.stop()      # clocks while api / strong / cfg2 / cfg2_4k / decode ran
+            line["extras_clocks"] = sampler2.stop()      # clocks while api / strong / cfg2 / cfg2_4k / decode / forward paths ran
     return line
 
 
