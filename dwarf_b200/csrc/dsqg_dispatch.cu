@@ -8,14 +8,23 @@
 
 namespace dsqg {
 
-// 0 = automatic, 1 = always the generic kernels, 2 = the tensor-core kernels (what the automatic
-// choice uses where they apply), 3 = the forward with TMA-staged V wherever it applies
+// 0 = automatic, 1 = always the generic kernels, 2 = the register-fed tensor-core kernels (what the
+// automatic choice uses where they apply, except for the one case in umma_pays()), 3 = the forward with TMA-staged V wherever it applies
 // (dsqg_staged.cu; not chosen automatically: it measures slower on B200), 4 = the forward with the
 // dense window on tcgen05 / tensor memory wherever it applies (dsqg_umma.cu; not chosen automatically).
 static std::atomic<int> g_path{0};
 
+// Where the tcgen05 forward measures faster than the register-fed one: 128-byte rows (D = 64), no sparse
+// taps, and enough 128-row tiles to keep one persistent block per SM busy (cfg2 shape, offsets 0..31:
+// 46.4 us against 56.1 us on B200).
+static bool umma_pays(const FwdArgs& a, const Taps& t, int dtype) {
+    return a.D == 64 && t.n_sparse == 0 && !a.strided &&
+           (long long)a.B * a.H * ((a.N + 127) / 128) >= 2 * 148 && umma_supported(dtype, a.D, t, a.scale_embed != nullptr);
+}
+
 cudaError_t launch_fwd(const FwdArgs& a, const Taps& t, int dtype, cudaStream_t s) {
     const int path = g_path.load();
+    if (path == 0 && umma_pays(a, t, dtype)) return launch_fwd_umma(a, t, s);
     if (path == 4 && !a.strided && umma_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_umma(a, t, s);
     if (path == 3 && staged_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_staged(a, t, s);
     if (path != 1 && mma_fwd_supported(dtype, a.D, t, a.scale_embed != nullptr)) return launch_fwd_mma(a, t, s);

@@ -67,7 +67,8 @@ int dsqg_version(void);
  * (not chosen automatically: it measures slower on B200), 4 = the forward whose dense window runs
  * on tcgen05 tensor cores with accumulators in tensor memory (bf16, no scale_embed, dense window
  * within offsets 0..32; D = 32 with up to 16 sparse taps, D = 64 without sparse taps; every other
- * call goes to the automatic choice; not chosen automatically).  Process-wide state. */
+ * call goes to the automatic choice; chosen automatically only where it measures faster: D = 64,
+ * no sparse taps, at least 296 tiles of 128 rows).  Process-wide state. */
 int dsqg_set_kernel_path(int path);
 
 /* Device-side error word of the current device (no counterpart in the reference).  The

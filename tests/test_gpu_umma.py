@@ -146,3 +146,20 @@ def test_what_the_path_does_not_take_falls_through_to_the_default_kernels():
         out4, lse4 = _forward(4, *args, offsets)
         out0, lse0 = _forward(0, *args, offsets)
         assert torch.equal(out4, out0) and torch.equal(lse4, lse0)
+
+
+def test_the_automatic_choice_takes_the_tcgen05_forward_where_it_measures_faster():
+    """D = 64, no sparse taps, at least 296 tiles of 128 rows: the bits of kernel path 4, not of the
+    register-fed kernel; a smaller problem of the same kind stays on the register-fed kernel."""
+    dev = torch.device("cuda", 0)
+    offsets = DENSE_SETS["0..32"]
+    for (B, H, N, D), uses_tcgen05 in (((5, 12, 640, 64), True), ((4, 12, 640, 64), False)):
+        g = torch.Generator().manual_seed(9)
+        q, k, v = (bf16_valued(B, H, N, D, scale=0.5, gen=g) for _ in range(3))
+        pb = synth.log_linear_pos_bias(offsets, H)
+        args = [t.bfloat16().to(dev) for t in (q, k, v)] + [pb.to(dev), None]
+        out0, _ = _forward(0, *args, offsets)
+        out2, _ = _forward(2, *args, offsets)
+        out4, _ = _forward(4, *args, offsets)
+        assert not torch.equal(out2, out4), "the two kernels round differently somewhere in a problem of this size"
+        assert torch.equal(out0, out4 if uses_tcgen05 else out2), (B, H, N, D)
