@@ -6,7 +6,7 @@
 // What it needs from the other side of the attention ("partner rows": value rows n - delta for a
 // query row n; the plan also covers the mirrored case, rows m + delta for a key row m) is fetched
 // ONCE per block by the copy engine (cp.async.bulk.tensor, plain per-block loads from this GPU's
-// own memory, no multicast):
+// own memory, every block fetching for itself):
 //   * the dense window of all 64 rows is one contiguous band of 64 + 32 partner rows;
 //   * every sparse tap is a 64-row tile shifted by its offset; taps whose tiles overlap or touch
 //     the band or each other are merged into one contiguous "segment", so a partner row that
