@@ -283,7 +283,7 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
 
 // Tuning per head dimension (measured on B200): warps per CTA, sparse taps folded together,
 // resident CTAs per SM the register budget is set for.
-template <int D> struct FwdTune { static constexpr int warps = 4, group = D == 32 ? 2 : (D == 64 ? 3 : 1), ctas = D == 32 ? 5 : (D == 64 ? 4 : (D == 96 ? 3 : 2)); };
+template <int D> struct FwdTune { static constexpr int warps = 4, group = D <= 64 ? 2 : 1, ctas = D == 32 ? 5 : (D == 64 ? 4 : (D == 96 ? 3 : 2)); };
 
 // Fills the shared tables of the scale_embed variants (all threads of the CTA; the caller syncs).
 // smem layout: se_hi [Jp][D] bf16 | se_lo [Jp][D] bf16 | pbs [Jp] f32 | off [NT*32] int4 | qs [warps][16*pitch+4] f32
@@ -378,7 +378,7 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
 template <int D> struct BwdTune {
     static constexpr int dq_group = D == 32 ? 2 : 1, dq_ctas = D == 32 ? 4 : (D == 64 ? 4 : 2);   // D = 32: 105.4 us against 107.5 with group 1 / 5 CTAs
     static constexpr int dq_ctas_se = D == 32 ? 4 : 3;      // with scale_embed: more shared memory and registers per CTA
-    static constexpr int dkdv_group = D == 32 ? 2 : 1, dkdv_ctas = D == 32 ? 4 : (D == 64 ? 3 : 2);
+    static constexpr int dkdv_group = D <= 64 ? 2 : 1, dkdv_ctas = D == 32 ? 4 : (D == 64 ? 3 : 2);
 };
 constexpr int kStagePitch = kRows + 4;      // 68: no bank conflicts on the scattered writes; the column sums rotate their start
 constexpr int kStagePitchSe = kRows + 4;    // 68 with scale_embed: rows are read back as 8-byte pairs by the dS MMAs
