@@ -377,7 +377,8 @@ fwd_mma_kernel(const FwdArgs a, const Taps t) {
 // resident CTAs per SM the register budget is set for (spills against warps in flight).
 template <int D> struct BwdTune {
     static constexpr int dq_group = D == 32 ? 2 : 1, dq_ctas = D == 32 ? 4 : (D == 64 ? 4 : 2);   // D = 32: 105.4 us against 107.5 with group 1 / 5 CTAs
-    static constexpr int dq_ctas_se = D == 32 ? 4 : 3;      // with scale_embed: more shared memory and registers per CTA
+    static constexpr int dq_group_se = 1, dq_ctas_se = D == 32 ? 5 : 4;      // with scale_embed: more shared memory and registers per CTA
+    static constexpr int dkdv_group_se = D <= 64 ? 2 : 1, dkdv_ctas_se = D == 32 ? 4 : 3;
     static constexpr int dkdv_group = D <= 64 ? 2 : 1, dkdv_ctas = D == 32 ? 4 : (D == 64 ? 3 : 2);
 };
 constexpr int kStagePitch = kRows + 4;      // 68: no bank conflicts on the scattered writes; the column sums rotate their start
@@ -1158,7 +1159,7 @@ cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stag
             se_prep_kernel<D><<<1, 1024, 0, s>>>(a.scale_embed, a.pos_bias, a.scale, t.J, a.H, t.d_lo, t.n_dense, WB, a.se_pre);
             if ((e = cudaGetLastError()) != cudaSuccess) return e;
         }
-        auto kern = bwd_dq_mma_kernel<D, WB, T::dq_group, SE ? T::dq_ctas_se : T::dq_ctas, SE, ST>;
+        auto kern = bwd_dq_mma_kernel<D, WB, SE ? T::dq_group_se : T::dq_group, SE ? T::dq_ctas_se : T::dq_ctas, SE, ST>;
         const size_t smem = dq_smem_bytes(t.J, t.n_sparse, D, NT, SE);
         static int seen[64] = {0};
         if ((e = ensure_dynamic_smem(kern, smem, seen)) != cudaSuccess) return e;
@@ -1176,7 +1177,7 @@ cudaError_t bwd_launch_mma_se(BwdArgs a, const Taps& t, cudaStream_t s, int stag
     const bool fuse = (stages & DSQG_BWD_STAGE_DKDV) && (stages & DSQG_BWD_STAGE_REDUCE) &&
                       (long long)grid.x * grid.y >= n_out;
     if (stages & DSQG_BWD_STAGE_DKDV) {
-        auto kern = bwd_dkdv_mma_kernel<D, WB, T::dkdv_group, T::dkdv_ctas, SE, ST>;
+        auto kern = bwd_dkdv_mma_kernel<D, WB, SE ? T::dkdv_group_se : T::dkdv_group, SE ? T::dkdv_ctas_se : T::dkdv_ctas, SE, ST>;
         const size_t smem = dkdv_smem_bytes(t.n_dense, WB, SE);
         static int seen[64] = {0};
         if ((e = ensure_dynamic_smem(kern, smem, seen)) != cudaSuccess) return e;
