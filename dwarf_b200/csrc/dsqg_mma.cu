@@ -283,7 +283,10 @@ __device__ __forceinline__ void fwd_tile(const FwdArgs& a, const float4* init_s,
 
 // Tuning per head dimension (measured on B200): warps per CTA, sparse taps folded together,
 // resident CTAs per SM the register budget is set for.
-template <int D> struct FwdTune { static constexpr int warps = 4, group = D <= 64 ? 2 : 1, ctas = D == 32 ? 5 : (D == 64 ? 4 : (D == 96 ? 3 : 2)); };
+template <int D> struct FwdTune {
+    static constexpr int warps = 4, group = D <= 64 ? 2 : 1, ctas = D == 32 ? 5 : (D == 64 ? 4 : (D == 96 ? 3 : 2));
+    static constexpr int group_se = D <= 64 ? 2 : 1, ctas_se = D == 32 ? 5 : 4;       // with scale_embed
+};
 
 // Fills the shared tables of the scale_embed variants (all threads of the CTA; the caller syncs).
 // smem layout: se_hi [Jp][D] bf16 | se_lo [Jp][D] bf16 | pbs [Jp] f32 | off [NT*32] int4 | qs [warps][16*pitch+4] f32
@@ -338,9 +341,9 @@ __host__ __device__ inline size_t se_tables_bytes(int J, int D, int NT, int warp
 // elements; any batch / head / row strides), e.g. the un-permuted output of a fused qkv projection
 // and a token-major result; with a gate tensor the epilogue multiplies by sigmoid(gate).
 template <int D, int WB, bool SE, bool ST>
-__global__ void __launch_bounds__(FwdTune<D>::warps * 32, FwdTune<D>::ctas)
+__global__ void __launch_bounds__(FwdTune<D>::warps * 32, SE ? FwdTune<D>::ctas_se : FwdTune<D>::ctas)
 fwd_mma_kernel(const FwdArgs a, const Taps t) {
-    constexpr int W = FwdTune<D>::warps, G = FwdTune<D>::group;
+    constexpr int W = FwdTune<D>::warps, G = SE ? FwdTune<D>::group_se : FwdTune<D>::group;
     constexpr int NT = (WB + 16) / 8;
     extern __shared__ __align__(16) unsigned char se_smem[];
     __shared__ float4 init_s[SE ? 1 : NT * 32];
